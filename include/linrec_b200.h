@@ -1,0 +1,142 @@
+/*
+ * linrec_b200 -- C ABI of the B200 (sm_100a) linear-recurrence scan library.
+ *
+ *     y[i] = y[i-1] * c[i] + x[i]        along the last dimension, forward or reversed,
+ *     and its backward:  dx = scan of dy in the opposite direction with the coefficients
+ *     shifted by one, dc[i] = dx[i] * y[i-+1].
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no torch types.  Every function works
+ * on device memory laid out as `numseq` rows of `seqlen` elements, element (r, i) at
+ * r*row_stride + i (row_stride >= seqlen, in elements), launches on the caller's stream
+ * (passed as a void* holding a cudaStream_t) and returns immediately; the return value is
+ * LINREC_OK or a negative LINREC_ERR_* code.  The library keeps no global mutable state except
+ * a launch counter; calls are re-entrant across host threads as long as each concurrent call has
+ * its own workspace.
+ *
+ * Each entry point names the interface of the reference (safelix/linrec, paths relative to that
+ * project) that it stands in for.
+ */
+#ifndef LINREC_B200_H
+#define LINREC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define LINREC_API
+#else
+#define LINREC_API __attribute__((visibility("default")))
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+#define LINREC_OK                   0
+#define LINREC_ERR_INVALID_ARG     (-1)  /* null pointer, negative size, stride < seqlen, ...  */
+#define LINREC_ERR_WORKSPACE       (-2)  /* workspace missing, misaligned or too small          */
+#define LINREC_ERR_NOT_IMPLEMENTED (-3)  /* option name or value that no compiled variant has   */
+#define LINREC_ERR_CUDA            (-4)  /* a CUDA runtime/driver call failed                   */
+#define LINREC_ERR_TIMEOUT         (-5)  /* a bounded device-side wait gave up (see _status)    */
+#define LINREC_ERR_TOO_LONG        (-6)  /* tile-only call and the row does not fit one tile    */
+#define LINREC_ERR_UNALIGNED       (-7)  /* bulk-copy path forced on pointers/strides it cannot take */
+
+/* ---- element storage types (arithmetic is always fp32) -------------------------------------- */
+#define LINREC_DTYPE_F32   0
+#define LINREC_DTYPE_BF16  1
+
+/* ---- which family of kernels a call may use --------------------------------------------------
+ * The reference exposes three operator families with one signature
+ * (linrec/impl/cuda/linrec.h:17-57); the same three are kept:
+ *   REF   one thread walks one row sequentially     (linrec_ref_fwd/bwd,  linrec_ref.cu:11-95)
+ *   TILE  the whole row must fit one tile           (linrec_tile_fwd/bwd, linrec_tile.cu:17-177)
+ *   PIPE  any length; rows longer than a tile are chained with look-back carries
+ *                                                   (linrec_pipe_fwd/bwd, linrec_pipe.cu:16-174) */
+#define LINREC_KIND_REF   0
+#define LINREC_KIND_TILE  1
+#define LINREC_KIND_PIPE  2
+
+/* Options are passed the way the reference passes its **kwargs -> std::map<std::string,int>
+ * (linrec/impl/cuda/extension.cpp:20-31): parallel arrays of names and integer values.  Known
+ * names are listed by linrec_b200_config_names(); an unknown name or a value without a compiled
+ * variant gives LINREC_ERR_NOT_IMPLEMENTED (the reference raises NotImplementedError from
+ * dispatch.h:70-71).  n_opts may be 0, in which case the regime selector chooses. */
+typedef struct linrec_opts {
+    int n_opts;
+    const char* const* names;
+    const int* values;
+} linrec_opts;
+
+/* Bytes of scratch a call on this shape may need (look-back descriptors, ticket counter and the
+ * status word).  Always > 0 and a multiple of 256; the buffer must be 256-byte aligned device
+ * memory.  Replaces nothing in the reference (its kernels never leave one CTA per row). */
+LINREC_API size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype);
+
+/* Forward scan.  Replaces linrec_{ref,tile,pipe}_fwd (linrec/impl/cuda/linrec.h:17-19,28-31,44-47).
+ * `kind` is one of LINREC_KIND_*; `reverse` scans from the last element down. */
+LINREC_API int linrec_b200_fwd(int kind, const void* x, const void* c, void* y,
+                               int64_t numseq, int64_t seqlen, int64_t row_stride,
+                               int reverse, int dtype, const linrec_opts* opts,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward.  Replaces linrec_{ref,tile,pipe}_bwd (linrec/impl/cuda/linrec.h:21-25,33-38,49-54).
+ * `reverse` is the flag the forward pass was run with. */
+LINREC_API int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y,
+                               void* dx, void* dc,
+                               int64_t numseq, int64_t seqlen, int64_t row_stride,
+                               int reverse, int dtype, const linrec_opts* opts,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device-side status word of the last call that used `workspace`: synchronises `stream`, reads
+ * the word and returns LINREC_OK or LINREC_ERR_TIMEOUT.  The bounded waits inside the kernels
+ * (look-back on a predecessor tile, arrival of a bulk copy) never trap and never spin forever;
+ * when one gives up the kernel finishes with wrong numbers and sets this word.
+ * No counterpart in the reference (its kernels contain no inter-CTA wait). */
+LINREC_API int linrec_b200_status(const void* workspace, void* stream);
+
+/* Kernel attributes of the variant that the options select, as parallel name/value arrays
+ * written into caller storage (at most `cap` entries; returns the number written or a negative
+ * error).  Replaces linrec_{tile,pipe}_attrs (linrec/impl/cuda/linrec_pipe.cu:177-212) together
+ * with cudaFuncAttributesAsMap (linrec/impl/cuda/cuhelpers.cuh:36-55). */
+LINREC_API int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts,
+                                 const char** names, int* values, int cap);
+
+/* Introspection of the compiled variants.  Replaces CONFIG_NAMES / CONFIG_LIST
+ * (linrec/impl/cuda/linrec.h:8-13) as exported through extension.cpp:46-47.
+ * config_names: returns the number of option names, writes up to `cap` pointers.
+ * config_list : returns the number of variants; writes up to cap_rows rows of n_names ints. */
+LINREC_API int linrec_b200_config_names(const char** names, int cap);
+LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
+
+/* Sequence sharding (one row split over several GPUs).  No counterpart in the reference, which
+ * is single-device.
+ *   linrec_b200_fwd_carry  : local forward scan of this shard with zero carry-in; also writes
+ *                            per row the pair (P = product of c over the shard, Y = last local y
+ *                            in scan order) to carry_out[2*r], carry_out[2*r+1] (fp32).
+ *   linrec_b200_fixup      : given all shards' pairs gathered in rank order
+ *                            (carries[(rank*numseq + r)*2 + {0,1}]), folds the pairs of the
+ *                            shards that precede `rank` in scan order and adds
+ *                            Y_in * prod(c) to this shard's y in place.  The walk along a row
+ *                            stops as soon as the running product is exactly zero. */
+LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* carry_out,
+                                     int64_t numseq, int64_t seqlen, int64_t row_stride,
+                                     int reverse, int dtype, const linrec_opts* opts,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+LINREC_API int linrec_b200_fixup(void* y, const void* c, const float* carries,
+                                 int rank, int world, int64_t numseq, int64_t seqlen,
+                                 int64_t row_stride, int reverse, int dtype, void* stream);
+
+/* Number of kernels this library has launched in this process (all threads). */
+LINREC_API uint64_t linrec_b200_launch_count(void);
+
+/* Text for a status code. */
+LINREC_API const char* linrec_b200_strerror(int code);
+
+/* Library version, e.g. 100 for 0.1.0. */
+LINREC_API int linrec_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LINREC_B200_H */

@@ -1,0 +1,81 @@
+"""In-tree build of the CUDA library (and of the standalone harness) for sm_100a.
+
+    python -m linrec_b200.build [--force] [--exe]
+
+The library is a plain C-ABI shared object built by nvcc alone: no torch headers, no Python
+headers.  The reference builds its extension just-in-time with torch's cpp_extension and no
+architecture flag (linrec/impl/cuda/build.py:15-80); here the architecture is pinned and the
+result lives next to the sources so that it travels with the tree.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+INCLUDE = os.path.join(ROOT, "include")
+LIB_PATH = os.path.join(PKG, "liblinrec_b200.so")
+EXE_PATH = os.path.join(PKG, "_build", "linrec_cli")
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found: the CUDA library of linrec_b200 cannot be built")
+    return exe
+
+
+def _sources(*names):
+    return [os.path.join(CSRC, n) for n in names]
+
+
+def _stale(target: str, deps) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def _all_deps():
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    deps.append(os.path.join(INCLUDE, "linrec_b200.h"))
+    deps.append(os.path.abspath(__file__))
+    return deps
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    if not force and not _stale(LIB_PATH, _all_deps()):
+        return LIB_PATH
+    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-shared", "-I", INCLUDE, "-o", LIB_PATH,
+           *_sources("capi.cu")]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    subprocess.run(cmd, check=True)
+    return LIB_PATH
+
+
+def build_executable(force: bool = False) -> str:
+    """The standalone verify/bench harness (counterpart of linrec/impl/cuda/executable.cpp)."""
+    lib = build_library(force=force)
+    src = os.path.join(CSRC, "linrec_cli.cu")
+    if not force and not _stale(EXE_PATH, _all_deps()):
+        return EXE_PATH
+    os.makedirs(os.path.dirname(EXE_PATH), exist_ok=True)
+    cmd = [_nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-I", INCLUDE, "-o", EXE_PATH, src,
+           lib, "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."]
+    subprocess.run(cmd, check=True)
+    return EXE_PATH
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    print(build_library(force=force, verbose="--verbose" in sys.argv))
+    if "--exe" in sys.argv:
+        print(build_executable(force=force))

@@ -1,0 +1,614 @@
+// Host side of the library: argument checks, regime selection, tensor-map construction,
+// workspace preparation and kernel launches, behind the C ABI of include/linrec_b200.h.
+//
+// Replaces the reference's host launchers and compile-time dispatch
+// (linrec/impl/cuda/linrec_pipe.cu:16-212, linrec_tile.cu:17-215, linrec_ref.cu:11-95,
+// dispatch.h:53-108) and the selection procedure of eval/tune.py:58-134, which there only prints
+// tables: here a closed-form selector picks the variant from (rows, length, dtype, alignment).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/linrec_b200.h"
+#include "scan_kernels.cuh"
+
+namespace {
+
+using linrec::ScanParams;
+using linrec::TileDesc;
+
+std::atomic<uint64_t> g_launches{0};
+
+// ---- options -------------------------------------------------------------------------------------
+// Compile-time configuration names (the counterpart of CONFIG_NAMES, linrec/impl/cuda/linrec.h:8).
+const char* const kConfigNames[] = {"kElemsPerThread", "kThreadsPerBlock", "kStages", "kOutBuffers", "memcode"};
+constexpr int kNumConfigNames = 5;
+// memcode: 0 = plain coalesced loads/stores staged through shared memory (any alignment),
+//          1 = tiled bulk-tensor copies (TMA) through an mbarrier ring.
+
+struct Options {
+    int E = -1, NT = -1, S = -1, OB = -1, memcode = -1;
+    int wait_budget_ms = 2000;   // budget of every device-side wait
+    int ctas_per_sm = 0;         // 0 = as many as fit
+    int first_ticket = 0;        // diagnostics only: tickets start here instead of 0
+};
+
+int parse_options(const linrec_opts* o, Options& out)
+{
+    if (!o || o->n_opts == 0) return LINREC_OK;
+    if (o->n_opts < 0 || !o->names || !o->values) return LINREC_ERR_INVALID_ARG;
+    for (int i = 0; i < o->n_opts; ++i) {
+        const char* n = o->names[i];
+        const int v = o->values[i];
+        if (!n) return LINREC_ERR_INVALID_ARG;
+        if (!strcmp(n, "kElemsPerThread")) out.E = v;
+        else if (!strcmp(n, "kThreadsPerBlock")) out.NT = v;
+        else if (!strcmp(n, "kStages")) out.S = v;
+        else if (!strcmp(n, "kOutBuffers")) out.OB = v;
+        else if (!strcmp(n, "memcode")) out.memcode = v;
+        else if (!strcmp(n, "waitBudgetMs")) out.wait_budget_ms = v;
+        else if (!strcmp(n, "ctasPerSm")) out.ctas_per_sm = v;
+        else if (!strcmp(n, "firstTicket")) out.first_ticket = v;
+        else return LINREC_ERR_NOT_IMPLEMENTED;
+    }
+    return LINREC_OK;
+}
+
+// ---- compiled variants ---------------------------------------------------------------------------
+using TmaFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                       const CUtensorMap, const ScanParams);
+using GenericFn = void (*)(const ScanParams);
+
+struct TmaVariant {
+    int E, NT, S, OB;
+    size_t smem[2][2];      // [dtype][bwd]
+    TmaFn fn[2][2][2];      // [dtype][bwd][asc]
+};
+
+template <int E, int NT, int S, int OB>
+TmaVariant make_tma_variant()
+{
+    using namespace linrec;
+    TmaVariant v{};
+    v.E = E; v.NT = NT; v.S = S; v.OB = OB;
+    v.smem[0][0] = TmaLayout<float, E, NT, S, OB, false>::kDynSmem;
+    v.smem[0][1] = TmaLayout<float, E, NT, S, OB, true>::kDynSmem;
+    v.smem[1][0] = TmaLayout<__nv_bfloat16, E, NT, S, OB, false>::kDynSmem;
+    v.smem[1][1] = TmaLayout<__nv_bfloat16, E, NT, S, OB, true>::kDynSmem;
+    v.fn[0][0][0] = linrec_tma_kernel<float, E, NT, S, OB, false, false>;
+    v.fn[0][0][1] = linrec_tma_kernel<float, E, NT, S, OB, false, true>;
+    v.fn[0][1][0] = linrec_tma_kernel<float, E, NT, S, OB, true, false>;
+    v.fn[0][1][1] = linrec_tma_kernel<float, E, NT, S, OB, true, true>;
+    v.fn[1][0][0] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, false, false>;
+    v.fn[1][0][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, false, true>;
+    v.fn[1][1][0] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, false>;
+    v.fn[1][1][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, true>;
+    return v;
+}
+
+struct GenericVariant {
+    int E, NT;
+    GenericFn fn[2][2][2];  // [dtype][bwd][asc]
+};
+
+template <int E, int NT>
+GenericVariant make_generic_variant()
+{
+    using namespace linrec;
+    GenericVariant v{};
+    v.E = E; v.NT = NT;
+    v.fn[0][0][0] = linrec_generic_kernel<float, E, NT, false, false>;
+    v.fn[0][0][1] = linrec_generic_kernel<float, E, NT, false, true>;
+    v.fn[0][1][0] = linrec_generic_kernel<float, E, NT, true, false>;
+    v.fn[0][1][1] = linrec_generic_kernel<float, E, NT, true, true>;
+    v.fn[1][0][0] = linrec_generic_kernel<__nv_bfloat16, E, NT, false, false>;
+    v.fn[1][0][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, false, true>;
+    v.fn[1][1][0] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, false>;
+    v.fn[1][1][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, true>;
+    return v;
+}
+
+const std::vector<TmaVariant>& tma_variants()
+{
+    static const std::vector<TmaVariant> v = {
+        make_tma_variant<16, 256, 2, 1>(),
+        make_tma_variant<16, 256, 3, 1>(),
+        make_tma_variant<16, 256, 2, 2>(),
+        make_tma_variant<16, 128, 3, 1>(),
+        make_tma_variant<16, 128, 4, 2>(),
+        make_tma_variant<16, 128, 2, 1>(),
+        make_tma_variant<8, 256, 3, 1>(),
+        make_tma_variant<16, 512, 2, 1>(),
+    };
+    return v;
+}
+
+const std::vector<GenericVariant>& generic_variants()
+{
+    static const std::vector<GenericVariant> v = {
+        make_generic_variant<16, 128>(),
+        make_generic_variant<8, 128>(),
+    };
+    return v;
+}
+
+// ---- per-device facts and per-kernel launch facts ------------------------------------------------
+struct DeviceInfo {
+    int sm_count = 0;
+    int clock_khz = 0;
+    int max_smem_optin = 0;
+};
+
+std::mutex g_mutex;
+std::unordered_map<int, DeviceInfo> g_devices;
+
+struct KernelKey {
+    const void* fn;
+    int device;
+    bool operator==(const KernelKey& o) const { return fn == o.fn && device == o.device; }
+};
+struct KernelKeyHash {
+    size_t operator()(const KernelKey& k) const { return std::hash<const void*>()(k.fn) ^ (size_t)k.device * 0x9e3779b97f4a7c15ull; }
+};
+std::unordered_map<KernelKey, int, KernelKeyHash> g_occupancy;   // resident CTAs per SM
+
+int device_info(DeviceInfo& out)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_devices.find(dev);
+    if (it == g_devices.end()) {
+        DeviceInfo d;
+        if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LINREC_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&d.clock_khz, cudaDevAttrClockRate, dev) != cudaSuccess) return LINREC_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return LINREC_ERR_CUDA;
+        it = g_devices.emplace(dev, d).first;
+    }
+    out = it->second;
+    return LINREC_OK;
+}
+
+// Resident CTAs per SM for a kernel with `smem` bytes of dynamic shared memory; the first query on
+// a device also raises the kernel's dynamic shared-memory limit.
+int occupancy(const void* fn, int threads, size_t smem, int& out)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const KernelKey key{fn, dev};
+    auto it = g_occupancy.find(key);
+    if (it == g_occupancy.end()) {
+        if (smem > 48 * 1024) {
+            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                cudaGetLastError();
+                return LINREC_ERR_CUDA;
+            }
+        }
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem) != cudaSuccess) {
+            cudaGetLastError();
+            return LINREC_ERR_CUDA;
+        }
+        it = g_occupancy.emplace(key, n).first;
+    }
+    out = it->second;
+    return out > 0 ? LINREC_OK : LINREC_ERR_CUDA;
+}
+
+// ---- tensor maps ---------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Rank-3 view (elements of a 128-byte line, lines of a row, rows) of a row-major matrix with a
+// 128-byte swizzle; box = (one line, `box_lines`, `box_rows`).
+int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64_t seqlen,
+             int64_t row_stride, int box_lines, int box_rows)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return LINREC_ERR_CUDA;
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    const cuuint64_t epl = 128 / sz;
+    const cuuint64_t dims[3] = {epl, (cuuint64_t)(seqlen / (int64_t)epl), (cuuint64_t)numseq};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)row_stride * (cuuint64_t)sz};
+    const cuuint32_t box[3] = {(cuuint32_t)epl, (cuuint32_t)box_lines, (cuuint32_t)box_rows};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, dtype == LINREC_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                           3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LINREC_OK : LINREC_ERR_CUDA;
+}
+
+// ---- planning ------------------------------------------------------------------------------------
+struct Plan {
+    bool tma = false;
+    const TmaVariant* tv = nullptr;
+    const GenericVariant* gv = nullptr;
+    int E = 0, NT = 0, T = 0;
+    int chain = 0, slots_per_row = 0, rows_per_tile = 1, chunks_per_row = 1;
+    long long ntiles = 0;
+};
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+bool tma_eligible(int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride, const void* const* ptrs, int nptrs)
+{
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    if ((seqlen * sz) % 128 != 0) return false;
+    if ((row_stride * sz) % 16 != 0) return false;
+    if (numseq > 0x7fffffffLL || seqlen / (128 / sz) > 0x7fffffffLL) return false;
+    if ((uint64_t)row_stride * sz >= (1ull << 40)) return false;
+    for (int i = 0; i < nptrs; ++i)
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
+    return true;
+}
+
+// Tile-shape bookkeeping shared by both loaders.
+void shape_plan(Plan& pl, int dtype, int64_t numseq, int64_t seqlen)
+{
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    const int64_t lp = pl.tma ? seqlen : round_up(seqlen, pl.E);
+    if (lp > pl.T) {
+        pl.chain = 1;
+        pl.chunks_per_row = (int)ceil_div(seqlen, pl.T);
+        pl.rows_per_tile = 1;
+        pl.slots_per_row = pl.T;
+        pl.ntiles = numseq * pl.chunks_per_row;
+    } else {
+        pl.chain = 0;
+        pl.chunks_per_row = 1;
+        pl.slots_per_row = (int)lp;
+        int64_t r = pl.T / lp;
+        if (pl.tma && r > 256) r = 256;          // box dimensions are limited to 256
+        if (r > numseq) r = numseq;
+        (void)sz;
+        pl.rows_per_tile = (int)r;
+        pl.ntiles = ceil_div(numseq, r);
+    }
+}
+
+// The regime selector.  `kind` TILE refuses rows that do not fit one tile, as the reference's
+// tile operator does (linrec/impl/cuda/linrec_tile.cu:60).
+int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride,
+              const void* const* ptrs, int nptrs, const Options& opt)
+{
+    const bool can_tma = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, nptrs);
+    int memcode = opt.memcode;
+    if (memcode < 0) memcode = can_tma ? 1 : 0;
+    if (memcode != 0 && memcode != 1) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (memcode == 1 && !can_tma) return LINREC_ERR_UNALIGNED;
+    pl.tma = memcode == 1;
+    if (pl.tma) {
+        // defaults of the selector; every field can be overridden
+        int E = opt.E, NT = opt.NT, S = opt.S, OB = opt.OB;
+        if (E < 0 && NT < 0 && S < 0 && OB < 0) {
+            if (!bwd) { E = 16; NT = 256; S = 2; OB = 1; }
+            else      { E = 16; NT = 128; S = 3; OB = 1; }
+        }
+        for (const TmaVariant& v : tma_variants()) {
+            if ((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S) && (OB < 0 || v.OB == OB)) {
+                pl.tv = &v;
+                break;
+            }
+        }
+        if (!pl.tv) return LINREC_ERR_NOT_IMPLEMENTED;
+        pl.E = pl.tv->E; pl.NT = pl.tv->NT;
+    } else {
+        if (opt.S > 1 || opt.OB > 0) return LINREC_ERR_NOT_IMPLEMENTED;
+        for (const GenericVariant& v : generic_variants()) {
+            if ((opt.E < 0 || v.E == opt.E) && (opt.NT < 0 || v.NT == opt.NT)) {
+                pl.gv = &v;
+                break;
+            }
+        }
+        if (!pl.gv) return LINREC_ERR_NOT_IMPLEMENTED;
+        pl.E = pl.gv->E; pl.NT = pl.gv->NT;
+    }
+    pl.T = pl.E * pl.NT;
+    shape_plan(pl, dtype, numseq, seqlen);
+    if (kind == LINREC_KIND_TILE && pl.chain) return LINREC_ERR_TOO_LONG;
+    if (pl.ntiles >= 0x7ff00000LL) return LINREC_ERR_INVALID_ARG;   // tickets are 32-bit
+    return LINREC_OK;
+}
+
+size_t workspace_need(const Plan& pl)
+{
+    size_t n = linrec::kHeaderBytes;
+    if (pl.chain) n += (size_t)pl.ntiles * sizeof(TileDesc);
+    return n;
+}
+
+int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seqlen, int64_t row_stride, int dtype)
+{
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (numseq < 0 || seqlen < 0) return LINREC_ERR_INVALID_ARG;
+    if (numseq == 0 || seqlen == 0) return LINREC_OK;
+    if (row_stride < seqlen) return LINREC_ERR_INVALID_ARG;
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    for (int i = 0; i < nptrs; ++i) {
+        if (!ptrs[i]) return LINREC_ERR_INVALID_ARG;
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) % sz != 0) return LINREC_ERR_INVALID_ARG;
+    }
+    return LINREC_OK;
+}
+
+// The one launcher behind forward, backward and the carry-emitting forward.
+int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
+                float* carry_out, int open_start, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
+                void* stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const void* ptrs[5] = {in0, c, out0, bwd ? yin : in0, bwd ? out1 : out0};
+    int rc = check_common(ptrs, 5, numseq, seqlen, row_stride, dtype);
+    if (rc != LINREC_OK) return rc;
+    if (kind != LINREC_KIND_REF && kind != LINREC_KIND_TILE && kind != LINREC_KIND_PIPE) return LINREC_ERR_INVALID_ARG;
+    Options opt;
+    rc = parse_options(opts, opt);
+    if (rc != LINREC_OK) return rc;
+    if (numseq == 0 || seqlen == 0) return LINREC_OK;
+
+    DeviceInfo dev;
+    rc = device_info(dev);
+    if (rc != LINREC_OK) return rc;
+
+    ScanParams p{};
+    p.in0 = in0; p.c = c; p.yin = yin; p.out0 = out0; p.out1 = out1;
+    p.numseq = numseq; p.seqlen = seqlen; p.row_stride = row_stride;
+    p.carry_out = carry_out;
+    p.open_start = open_start;
+    p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
+    // the gradient scan runs against the direction of the forward pass
+    const bool asc = bwd ? (reverse != 0) : (reverse == 0);
+
+    if (kind == LINREC_KIND_REF) {
+        if (carry_out) return LINREC_ERR_NOT_IMPLEMENTED;
+        const int threads = 128;
+        const unsigned blocks = (unsigned)ceil_div(numseq, threads);
+        if (di == 0) {
+            if (bwd) linrec::linrec_seq_kernel<float, true><<<blocks, threads, 0, stream>>>(p, reverse);
+            else     linrec::linrec_seq_kernel<float, false><<<blocks, threads, 0, stream>>>(p, reverse);
+        } else {
+            if (bwd) linrec::linrec_seq_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(p, reverse);
+            else     linrec::linrec_seq_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(p, reverse);
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+    }
+
+    Plan pl;
+    rc = make_plan(pl, kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt);
+    if (rc != LINREC_OK) return rc;
+
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < workspace_need(pl))
+        return LINREC_ERR_WORKSPACE;
+    p.header = static_cast<uint32_t*>(workspace);
+    p.desc = reinterpret_cast<TileDesc*>(static_cast<char*>(workspace) + linrec::kHeaderBytes);
+    p.chain = pl.chain;
+    p.slots_per_row = pl.slots_per_row;
+    p.rows_per_tile = pl.rows_per_tile;
+    p.chunks_per_row = pl.chunks_per_row;
+    p.ntiles = pl.ntiles;
+
+    const void* fn = pl.tma ? reinterpret_cast<const void*>(pl.tv->fn[di][bwd][asc])
+                            : reinterpret_cast<const void*>(pl.gv->fn[di][bwd][asc]);
+    const size_t smem = pl.tma ? pl.tv->smem[di][bwd] : 0;
+    if (smem > (size_t)dev.max_smem_optin) return LINREC_ERR_NOT_IMPLEMENTED;
+    int occ = 0;
+    rc = occupancy(fn, pl.NT, smem, occ);
+    if (rc != LINREC_OK) return rc;
+    if (opt.ctas_per_sm > 0 && opt.ctas_per_sm < occ) occ = opt.ctas_per_sm;
+    long long grid = (long long)dev.sm_count * occ;
+    if (grid > pl.ntiles) grid = pl.ntiles;
+
+    // workspace: ticket counter and status word by a one-thread kernel, descriptors by a memset
+    linrec::linrec_init_header_kernel<<<1, 32, 0, stream>>>(p.header, (uint32_t)opt.first_ticket);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (pl.chain) {
+        if (cudaMemsetAsync(p.desc, 0, (size_t)pl.ntiles * sizeof(TileDesc), stream) != cudaSuccess) {
+            cudaGetLastError();
+            return LINREC_ERR_CUDA;
+        }
+    }
+
+    if (pl.tma) {
+        CUtensorMap m[5];
+        const int box_lines = pl.chain ? pl.T / (128 / (di == 0 ? 4 : 2)) : (int)(seqlen / (128 / (di == 0 ? 4 : 2)));
+        const int box_rows = pl.chain ? 1 : pl.rows_per_tile;
+        const void* src[5] = {in0, c, bwd ? yin : c, out0, bwd ? out1 : out0};
+        for (int i = 0; i < 5; ++i) {
+            rc = make_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows);
+            if (rc != LINREC_OK) return rc;
+        }
+        pl.tv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
+    } else {
+        pl.gv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, 0, stream>>>(p);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+}
+
+}  // namespace
+
+// =================================================================================================
+//  C ABI
+// =================================================================================================
+extern "C" {
+
+size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype)
+{
+    (void)dtype;
+    size_t n = linrec::kHeaderBytes;
+    if (numseq > 0 && seqlen > 0) {
+        // the smallest tile any variant uses bounds the number of chained tiles from above
+        int tmin = 1 << 30;
+        for (const TmaVariant& v : tma_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
+        for (const GenericVariant& v : generic_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
+        if (seqlen > tmin) n += (size_t)numseq * (size_t)ceil_div(seqlen, tmin) * sizeof(TileDesc);
+    }
+    return (size_t)round_up((int64_t)n, 256);
+}
+
+int linrec_b200_fwd(int kind, const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen,
+                    int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
+                    size_t workspace_bytes, void* stream)
+{
+    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, numseq, seqlen, row_stride, reverse,
+                       dtype, opts, workspace, workspace_bytes, stream);
+}
+
+int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y, void* dx, void* dc, int64_t numseq,
+                    int64_t seqlen, int64_t row_stride, int reverse, int dtype, const linrec_opts* opts,
+                    void* workspace, size_t workspace_bytes, void* stream)
+{
+    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype, opts,
+                       workspace, workspace_bytes, stream);
+}
+
+int linrec_b200_status(const void* workspace, void* stream)
+{
+    if (!workspace) return LINREC_ERR_INVALID_ARG;
+    uint32_t words[2] = {0, 0};
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return LINREC_ERR_CUDA;
+    if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return LINREC_ERR_CUDA;
+    return words[1] == 0 ? LINREC_OK : LINREC_ERR_TIMEOUT;
+}
+
+int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, const char** names, int* values, int cap)
+{
+    if (!names || !values || cap <= 0) return LINREC_ERR_INVALID_ARG;
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16) return LINREC_ERR_NOT_IMPLEMENTED;
+    Options opt;
+    int rc = parse_options(opts, opt);
+    if (rc != LINREC_OK) return rc;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
+    const bool bwd = !fwd;
+    const void* fn = nullptr;
+    int E = 0, NT = 0, S = 0, OB = 0, memcode = 0;
+    size_t dyn = 0;
+    if (kind == LINREC_KIND_REF) {
+        fn = di == 0 ? (bwd ? (const void*)linrec::linrec_seq_kernel<float, true> : (const void*)linrec::linrec_seq_kernel<float, false>)
+                     : (bwd ? (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, true> : (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, false>);
+        E = 1; NT = 128;
+    } else {
+        // attributes are reported for an aligned problem unless memcode=0 is asked for
+        Plan pl;
+        Options o2 = opt;
+        if (o2.memcode < 0) o2.memcode = 1;
+        static const double dummy_align[2] = {0, 0};
+        const void* ptrs[1] = {reinterpret_cast<const void*>((reinterpret_cast<uintptr_t>(dummy_align) + 15) & ~(uintptr_t)15)};
+        rc = make_plan(pl, LINREC_KIND_PIPE, bwd, dtype, 1024, 1 << 20, 1 << 20, ptrs, 0, o2);
+        if (rc != LINREC_OK) return rc;
+        if (pl.tma) {
+            fn = reinterpret_cast<const void*>(pl.tv->fn[di][bwd][1]);
+            E = pl.tv->E; NT = pl.tv->NT; S = pl.tv->S; OB = pl.tv->OB; memcode = 1;
+            dyn = pl.tv->smem[di][bwd];
+        } else {
+            fn = reinterpret_cast<const void*>(pl.gv->fn[di][bwd][1]);
+            E = pl.gv->E; NT = pl.gv->NT; S = 1; OB = 0; memcode = 0;
+        }
+    }
+    cudaFuncAttributes a;
+    if (cudaFuncGetAttributes(&a, fn) != cudaSuccess) {
+        cudaGetLastError();
+        return LINREC_ERR_CUDA;
+    }
+    int occ = 0;
+    if (occupancy(fn, NT, dyn, occ) != LINREC_OK) occ = 0;
+    const char* nm[] = {"sharedSizeBytes", "constSizeBytes", "localSizeBytes", "maxThreadsPerBlock", "numRegs",
+                        "ptxVersion", "binaryVersion", "maxDynamicSharedSizeBytes", "dynamicSharedSizeBytes",
+                        "residentBlocksPerSM", "kElemsPerThread", "kThreadsPerBlock", "kStages", "kOutBuffers", "memcode"};
+    const int vl[] = {(int)a.sharedSizeBytes, (int)a.constSizeBytes, (int)a.localSizeBytes, a.maxThreadsPerBlock, a.numRegs,
+                      a.ptxVersion, a.binaryVersion, a.maxDynamicSharedSizeBytes, (int)dyn, occ, E, NT, S, OB, memcode};
+    const int n = (int)(sizeof(vl) / sizeof(vl[0]));
+    int w = 0;
+    for (; w < n && w < cap; ++w) {
+        names[w] = nm[w];
+        values[w] = vl[w];
+    }
+    return w;
+}
+
+int linrec_b200_config_names(const char** names, int cap)
+{
+    if (names)
+        for (int i = 0; i < kNumConfigNames && i < cap; ++i) names[i] = kConfigNames[i];
+    return kNumConfigNames;
+}
+
+int linrec_b200_config_list(int* values, int cap_rows)
+{
+    int row = 0;
+    auto put = [&](int E, int NT, int S, int OB, int memcode) {
+        if (values && row < cap_rows) {
+            int* r = values + (size_t)row * kNumConfigNames;
+            r[0] = E; r[1] = NT; r[2] = S; r[3] = OB; r[4] = memcode;
+        }
+        ++row;
+    };
+    for (const TmaVariant& v : tma_variants()) put(v.E, v.NT, v.S, v.OB, 1);
+    for (const GenericVariant& v : generic_variants()) put(v.E, v.NT, 1, 0, 0);
+    return row;
+}
+
+int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* carry_out, int64_t numseq, int64_t seqlen,
+                          int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
+                          size_t workspace_bytes, void* stream)
+{
+    if (!carry_out && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, carry_out, 1, numseq, seqlen, row_stride,
+                       reverse, dtype, opts, workspace, workspace_bytes, stream);
+}
+
+int linrec_b200_fixup(void* y, const void* c, const float* carries, int rank, int world, int64_t numseq,
+                      int64_t seqlen, int64_t row_stride, int reverse, int dtype, void* stream)
+{
+    (void)y; (void)c; (void)carries; (void)rank; (void)world; (void)numseq; (void)seqlen; (void)row_stride;
+    (void)reverse; (void)dtype; (void)stream;
+    return LINREC_ERR_NOT_IMPLEMENTED;
+}
+
+uint64_t linrec_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* linrec_b200_strerror(int code)
+{
+    switch (code) {
+        case LINREC_OK: return "ok";
+        case LINREC_ERR_INVALID_ARG: return "invalid argument";
+        case LINREC_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case LINREC_ERR_NOT_IMPLEMENTED: return "no compiled variant for these options";
+        case LINREC_ERR_CUDA: return "a CUDA call failed";
+        case LINREC_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case LINREC_ERR_TOO_LONG: return "row does not fit one tile";
+        case LINREC_ERR_UNALIGNED: return "bulk-copy path needs 16-byte aligned rows whose length is a multiple of 128 bytes";
+        default: return "unknown status";
+    }
+}
+
+int linrec_b200_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,431 @@
+// Device-side building blocks of the linear-recurrence scan, shared by the bulk-copy (TMA)
+// pipeline kernel and the any-alignment kernel.
+//
+// Replaces, from scratch, the reference's in-register block scan
+// (linrec/impl/cuda/linrec_tile.cuh:33-114) and its tile loaders (linrec/impl/cuda/memio.cuh:12-198).
+//
+// Data model of one tile
+// ----------------------
+// A tile is T = E*NT "slots" held in shared memory, one array per operand.  Thread t owns the E
+// consecutive slots [t*E, (t+1)*E).  Slots are stored in 16-byte chunks whose position inside
+// each 128-byte line is XOR-ed with the line number modulo 8 -- exactly the layout the TMA unit
+// produces with its 128-byte swizzle -- so that the per-thread 16-byte reads of a blocked
+// arrangement are free of bank conflicts (8 consecutive threads hit 8 different chunk columns).
+//
+// A tile covers either a contiguous piece of ONE row ("chain" mode, rows longer than a tile, the
+// pieces are linked by look-back carries) or several whole rows of `slots_per_row` slots each
+// ("multi-row" mode).  In both modes a thread's slots never straddle two rows.
+//
+// Scan order.  ASC scans walk memory upwards, descending scans downwards; everything below is
+// phrased in scan order (s = thread rank in scan order, k = number of threads of the same row
+// that precede this thread inside the tile).
+#pragma once
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace linrec {
+
+// ---- workspace layout ---------------------------------------------------------------------------
+constexpr int kHeaderBytes = 256;            // [0] ticket counter, [1] status word, rest reserved
+constexpr uint32_t kStatusLookbackTimeout = 1u;
+constexpr uint32_t kStatusCopyTimeout = 2u;
+
+// One look-back descriptor per chained tile (32 bytes = one DRAM sector).
+struct __align__(32) TileDesc {
+    float2 agg;        // (Y, P) of the tile alone               valid once status >= 1
+    float2 inc;        // (Y, P) of the row up to and including   valid once status == 2
+    uint32_t status;   // 0 nothing, 1 aggregate, 2 inclusive
+    uint32_t pad[3];
+};
+
+// ---- the associative operator -------------------------------------------------------------------
+// A segment of the recurrence maps a carry-in v to  v*P + Y.  Composition "far then near":
+//   (Y_f, P_f) o (Y_n, P_n) = (Y_f*P_n + Y_n, P_f*P_n);  identity (0, 1).
+// (the reference's operator: linrec/impl/cuda/linrec_tile.cuh:53-54,74-75)
+struct Pair {
+    float y, p;
+};
+__device__ __forceinline__ Pair pair_identity() { return Pair{0.0f, 1.0f}; }
+__device__ __forceinline__ Pair combine(Pair far, Pair near)
+{
+    return Pair{fmaf(far.y, near.p, near.y), far.p * near.p};
+}
+
+// ---- kernel parameters --------------------------------------------------------------------------
+struct ScanParams {
+    const void* in0;   // forward: x        backward: dy
+    const void* c;     // coefficients
+    const void* yin;   // backward only: outputs of the forward pass
+    void* out0;        // forward: y        backward: dx
+    void* out1;        // backward only: dc
+    long long numseq, seqlen, row_stride;
+    long long ntiles;
+    int chain;           // 1: rows are longer than a tile and are chained
+    int slots_per_row;   // multi-row mode: slots one row occupies (multiple of E)
+    int rows_per_tile;   // multi-row mode
+    int chunks_per_row;  // chain mode
+    uint32_t* header;    // workspace header (ticket counter, status word)
+    TileDesc* desc;      // chain mode: one descriptor per tile, zeroed before the launch
+    long long wait_budget;  // clock ticks any device-side wait may last
+    float* carry_out;    // optional: per row (P, Y) of the whole row, for sequence sharding
+    int open_start;      // 1: the rows continue an earlier shard, so their first coefficient counts
+};
+
+// ---- storage-type helpers -----------------------------------------------------------------------
+template <typename ST>
+struct Storage;
+
+template <>
+struct Storage<float> {
+    static constexpr int kPerChunk = 4;
+    __device__ static __forceinline__ void unpack(const uint4& q, float* v)
+    {
+        v[0] = __uint_as_float(q.x);
+        v[1] = __uint_as_float(q.y);
+        v[2] = __uint_as_float(q.z);
+        v[3] = __uint_as_float(q.w);
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v)
+    {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
+                          __float_as_uint(v[3]));
+    }
+    __device__ static __forceinline__ float to_float(float v) { return v; }
+    __device__ static __forceinline__ float from_float(float v) { return v; }
+};
+
+template <>
+struct Storage<__nv_bfloat16> {
+    static constexpr int kPerChunk = 8;
+    __device__ static __forceinline__ void unpack(const uint4& q, float* v)
+    {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v)
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Byte offset of slot `i` inside a swizzled tile buffer (buffer base 1024-byte aligned).
+template <typename ST>
+__device__ __forceinline__ uint32_t slot_byte_offset(uint32_t i)
+{
+    const uint32_t b = i * (uint32_t)sizeof(ST);
+    const uint32_t chunk = b >> 4;
+    const uint32_t phys = chunk ^ ((chunk >> 3) & 7u);
+    return (phys << 4) | (b & 15u);
+}
+
+template <typename ST>
+__device__ __forceinline__ float read_slot(const ST* buf, int i)
+{
+    const char* p = reinterpret_cast<const char*>(buf) + slot_byte_offset<ST>((uint32_t)i);
+    return Storage<ST>::to_float(*reinterpret_cast<const ST*>(p));
+}
+
+template <typename ST>
+__device__ __forceinline__ void write_slot(ST* buf, int i, float v)
+{
+    char* p = reinterpret_cast<char*>(buf) + slot_byte_offset<ST>((uint32_t)i);
+    *reinterpret_cast<ST*>(p) = Storage<ST>::from_float(v);
+}
+
+// Thread t's E slots, as E floats in memory order (16-byte shared loads, conflict free).
+template <typename ST, int E>
+__device__ __forceinline__ void load_run(const ST* buf, int t, float (&v)[E])
+{
+    constexpr int PC = Storage<ST>::kPerChunk;
+    constexpr int CH = E / PC;
+    static_assert(E % PC == 0, "a thread's run must be whole 16-byte chunks");
+    const uint4* b4 = reinterpret_cast<const uint4*>(buf);
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int cj = t * CH + j;
+        const uint4 q = b4[cj ^ ((cj >> 3) & 7)];
+        Storage<ST>::unpack(q, &v[j * PC]);
+    }
+}
+
+template <typename ST, int E>
+__device__ __forceinline__ void store_run(ST* buf, int t, const float (&v)[E])
+{
+    constexpr int PC = Storage<ST>::kPerChunk;
+    constexpr int CH = E / PC;
+    uint4* b4 = reinterpret_cast<uint4*>(buf);
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int cj = t * CH + j;
+        b4[cj ^ ((cj >> 3) & 7)] = Storage<ST>::pack(&v[j * PC]);
+    }
+}
+
+// ---- per-thread geometry (does not change from tile to tile) ------------------------------------
+struct Geometry {
+    int t;            // thread index = memory rank of the thread's run inside the tile
+    int s;            // thread rank in scan order
+    int lane;         // hardware lane
+    int ls;           // lane rank in scan order
+    int ws;           // warp rank in scan order
+    int m;            // memory rank of the run inside its row (multi-row) or tile (chain)
+    int k;            // number of same-row threads that precede in scan order inside the tile
+    int tpr;          // threads per row (multi-row) or NT (chain)
+    int row_in_tile;  // multi-row: which row of the tile; chain: 0
+    int start_warp;   // first warp (scan rank) that holds a piece of the row crossing into this warp
+    bool need_wp;     // the thread's row began in an earlier warp
+    bool has_excl;    // the scan-predecessor lane holds the same row
+    bool lo_in_tile;  // slot just below the run belongs to the same row and tile
+    bool hi_in_tile;  // slot just above the run belongs to the same row and tile
+};
+
+template <int E, int NT, bool ASC>
+__device__ __forceinline__ Geometry make_geometry(const ScanParams& p)
+{
+    constexpr int NW = NT / 32;
+    Geometry g;
+    g.t = (int)threadIdx.x;
+    g.lane = g.t & 31;
+    const int w = g.t >> 5;
+    g.ls = ASC ? g.lane : 31 - g.lane;
+    g.ws = ASC ? w : NW - 1 - w;
+    g.s = ASC ? g.t : NT - 1 - g.t;
+    const int s = g.s;
+    if (p.chain) {
+        g.tpr = NT;
+        g.m = g.t;
+        g.k = s;
+        g.row_in_tile = 0;
+    } else {
+        g.tpr = p.slots_per_row / E;
+        g.row_in_tile = g.t / g.tpr;
+        g.m = g.t - g.row_in_tile * g.tpr;
+        g.k = ASC ? g.m : g.tpr - 1 - g.m;
+    }
+    g.lo_in_tile = g.m > 0;
+    g.hi_in_tile = g.m < g.tpr - 1;
+    g.has_excl = (g.ls >= 1) && (g.k >= 1);
+    g.need_wp = g.k > g.ls;
+    // k of the warp's scan-first lane tells where the row that crosses into this warp began
+    const int k0 = __shfl_sync(0xffffffffu, g.k, ASC ? 0 : 31);
+    // (threads past the last whole row of a multi-row tile form a fragment whose k may overshoot;
+    //  their results are never stored, the clamp only keeps their reads inside the array)
+    g.start_warp = max(0, (g.ws * 32 - k0) >> 5);
+    return g;
+}
+
+// ---- operands of one thread ----------------------------------------------------------------------
+template <int E, bool BWD>
+struct Operands {
+    float x[E];                 // additive term, memory order
+    float c[E];                 // coefficient applied to the carry entering each slot
+    float ysh[BWD ? E : 1];     // backward: forward output at the scan successor
+};
+
+// Reads the thread's operands from the tile buffers.
+//   forward : x, c straight from the buffers.
+//   backward: the coefficient of slot i is c at its scan PREDECESSOR and the multiplier for dc is
+//             y at its scan SUCCESSOR (linrec/impl/python/ops.py:32-40).  For the slot at the end
+//             of the thread's run the neighbour is the adjacent slot of the tile when that slot
+//             belongs to the same row, otherwise the caller supplies it: `pred_c_outside` /
+//             `succ_y_outside` are the halo words at a tile edge inside a row and the edge values
+//             (0 unless the row continues on another shard) at a row end.
+// `valid` is the number of slots of this tile that lie inside the row (chain mode; < T only for
+// the piece at the row's memory end; T in multi-row mode).  A neighbour slot at or beyond it is
+// outside the row, so the caller's outside value is used for it as well.  With PATCH set, the coefficients of slots beyond it are
+// forced to 1: bulk copies fill them with 0, which would wipe the row's running product.
+template <typename ST, int E, int NT, bool BWD, bool ASC, bool PATCH>
+__device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geometry& g,
+                                              const ST* b_in0, const ST* b_c, const ST* b_y,
+                                              float pred_c_outside, float succ_y_outside, int valid,
+                                              bool zero_first)
+{
+    constexpr int T = E * NT;
+    load_run<ST, E>(b_in0, g.t, op.x);
+    float craw[E];
+    load_run<ST, E>(b_c, g.t, craw);
+    const int a = g.t * E;
+    if (!BWD) {
+#pragma unroll
+        for (int j = 0; j < E; ++j) op.c[j] = craw[j];
+    } else {
+        float yraw[E];
+        load_run<ST, E>(b_y, g.t, yraw);
+        const int lo = a - 1, hi = a + E;
+        if (ASC) {   // predecessor = slot below, successor = slot above
+            const float c_pred = g.lo_in_tile ? read_slot<ST>(b_c, lo) : pred_c_outside;
+            const float y_succ = (g.hi_in_tile && hi < valid) ? read_slot<ST>(b_y, hi) : succ_y_outside;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                op.c[j] = (j == 0) ? c_pred : craw[j - 1];
+                op.ysh[j] = (j == E - 1) ? y_succ : yraw[j + 1];
+            }
+        } else {     // predecessor = slot above, successor = slot below
+            const float c_pred = (g.hi_in_tile && hi < valid) ? read_slot<ST>(b_c, hi) : pred_c_outside;
+            const float y_succ = g.lo_in_tile ? read_slot<ST>(b_y, lo) : succ_y_outside;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                op.c[j] = (j == E - 1) ? c_pred : craw[j + 1];
+                op.ysh[j] = (j == 0) ? y_succ : yraw[j - 1];
+            }
+        }
+    }
+    // Slots past the end of the row are identity elements (x = 0 already, c = 1).
+    if (PATCH && valid < T) {
+#pragma unroll
+        for (int j = 0; j < E; ++j)
+            if (a + j >= valid) op.c[j] = 1.0f;
+    }
+    // Nothing precedes the first element of a row: its coefficient is defined away, as in the
+    // reference kernels that start with y[s] = x[s] (linrec/impl/cuda/linrec_ref.cuh:63).
+    if (zero_first) op.c[ASC ? 0 : E - 1] = 0.0f;
+}
+
+// ---- scan state carried between the phases of one tile -----------------------------------------
+struct ThreadScan {
+    Pair agg;    // the thread's own E slots
+    Pair excl;   // same-row lanes of this warp that precede the thread (identity if none)
+};
+
+// Phase 1: thread aggregate, then a segmented Kogge-Stone scan across the warp in scan order.
+// The scan-last lane of every warp leaves the warp's inclusive value in wagg[ws].
+template <int E, int NT, bool BWD, bool ASC>
+__device__ __forceinline__ ThreadScan scan_thread_and_warp(const Operands<E, BWD>& op,
+                                                           const Geometry& g, Pair* wagg)
+{
+    ThreadScan ts;
+    Pair a = pair_identity();
+#pragma unroll
+    for (int jj = 0; jj < E; ++jj) {
+        const int j = ASC ? jj : E - 1 - jj;
+        a.y = fmaf(a.y, op.c[j], op.x[j]);
+        a.p = a.p * op.c[j];
+    }
+    ts.agg = a;
+    Pair inc = a;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int src = ASC ? g.lane - d : g.lane + d;
+        Pair far;
+        far.y = __shfl_sync(0xffffffffu, inc.y, src);
+        far.p = __shfl_sync(0xffffffffu, inc.p, src);
+        if (g.ls >= d && g.k >= d) inc = combine(far, inc);
+    }
+    Pair ex;
+    {
+        const int src = ASC ? g.lane - 1 : g.lane + 1;
+        ex.y = __shfl_sync(0xffffffffu, inc.y, src);
+        ex.p = __shfl_sync(0xffffffffu, inc.p, src);
+    }
+    ts.excl = g.has_excl ? ex : pair_identity();
+    if (g.ls == 31) wagg[g.ws] = inc;
+    return ts;
+}
+
+// Phase 2a (after a block barrier): what the earlier warps contribute to this thread's row.
+__device__ __forceinline__ Pair cross_warp_prefix(const Geometry& g, const Pair* wagg)
+{
+    Pair wp = pair_identity();
+    for (int w = g.start_warp; w < g.ws; ++w) wp = combine(wp, wagg[w]);
+    return wp;
+}
+
+// Ordered reduction across a warp: lane 0 ends with v[31] o v[30] o ... o v[0]
+// (higher lanes are FARTHER back in scan order).
+__device__ __forceinline__ Pair warp_reduce_far_to_near(Pair v, int lane)
+{
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        Pair far;
+        far.y = __shfl_down_sync(0xffffffffu, v.y, d);
+        far.p = __shfl_down_sync(0xffffffffu, v.p, d);
+        if (lane + d < 32) v = combine(far, v);
+    }
+    return v;
+}
+
+// Phase 2b, chain mode, run by ONE warp: decoupled look-back over the predecessor tiles of the
+// same row.  Tile (row r, scan piece q) has ticket q*numseq + r, so its predecessor is `numseq`
+// tickets back.  Returns (on every lane) the exclusive prefix of this tile.  Each poll is bounded
+// by p.wait_budget clock ticks; on expiry the status word is flagged and the missing predecessor
+// is treated as an inclusive identity so that the walk terminates.
+__device__ __forceinline__ Pair lookback(const ScanParams& p, long long ticket, int q, int lane)
+{
+    Pair acc = pair_identity();
+    int j0 = 1;
+    while (true) {
+        const int pq = q - j0 - lane;
+        Pair v = pair_identity();
+        uint32_t st = 2u;
+        if (pq >= 0) {
+            const TileDesc* d = p.desc + (ticket - (long long)(j0 + lane) * p.numseq);
+            st = ptx::ld_acquire_u32(&d->status);
+            if (st == 0u) {
+                const long long t0 = clock64();
+                unsigned ns = 32;
+                while ((st = ptx::ld_acquire_u32(&d->status)) == 0u) {
+                    if (clock64() - t0 > p.wait_budget) break;
+                    __nanosleep(ns);
+                    if (ns < 1024) ns <<= 1;
+                }
+            }
+            if (st == 0u) {
+                atomicOr(p.header + 1, kStatusLookbackTimeout);
+                st = 2u;   // give up: pretend an inclusive identity so that the walk ends
+            } else {
+                const float2 f = ptx::ld_relaxed_f32x2(st == 2u ? &d->inc : &d->agg);
+                v = Pair{f.x, f.y};
+            }
+        }
+        const uint32_t ball = __ballot_sync(0xffffffffu, st == 2u);
+        const int first = ball ? (__ffs(ball) - 1) : 31;   // nearest predecessor holding an inclusive value
+        if (lane > first) v = pair_identity();
+        const Pair win = warp_reduce_far_to_near(v, lane);
+        Pair w0;
+        w0.y = __shfl_sync(0xffffffffu, win.y, 0);
+        w0.p = __shfl_sync(0xffffffffu, win.p, 0);
+        acc = combine(w0, acc);   // this window lies farther back than what was gathered so far
+        if (ball) break;
+        j0 += 32;
+    }
+    return acc;
+}
+
+// Publishes a tile's aggregate or inclusive value (one lane calls this).
+__device__ __forceinline__ void publish(TileDesc* d, Pair v, bool inclusive)
+{
+    ptx::st_relaxed_f32x2(inclusive ? &d->inc : &d->agg, make_float2(v.y, v.p));
+    ptx::st_release_u32(&d->status, inclusive ? 2u : 1u);
+}
+
+// Phase 3: rerun the recurrence through the thread's slots from the true carry-in, which makes
+// every output the result of the same fused multiply-adds a sequential walk would perform from
+// that carry.
+template <int E, bool BWD, bool ASC>
+__device__ __forceinline__ void apply_carry(const Operands<E, BWD>& op, float carry_in,
+                                            float (&o0)[E], float (&o1)[BWD ? E : 1])
+{
+    float v = carry_in;
+#pragma unroll
+    for (int jj = 0; jj < E; ++jj) {
+        const int j = ASC ? jj : E - 1 - jj;
+        v = fmaf(v, op.c[j], op.x[j]);
+        o0[j] = v;
+        if (BWD) o1[j] = v * op.ysh[j];
+    }
+}
+
+}  // namespace linrec

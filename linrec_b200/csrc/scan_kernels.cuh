@@ -1,0 +1,419 @@
+// The scan kernels.
+//
+//   linrec_tma_kernel      persistent CTAs, tiles handed out by an atomic ticket, operands brought
+//                          in by tiled bulk-tensor copies (TMA, 128-byte swizzle) through an
+//                          S-stage shared-memory ring with mbarriers, results staged in shared
+//                          memory and written back with bulk-tensor stores.
+//   linrec_generic_kernel  same tile algebra, but plain coalesced loads and stores with bounds
+//                          checks: any length, any (element-aligned) pointer, any row stride.
+//   linrec_seq_kernel      one thread walks one row (the slow, obviously-right operator that the
+//                          reference exposes as linrec_ref: linrec/impl/cuda/linrec_ref.cuh:53-94).
+//   linrec_fixup_kernel    sequence sharding: adds carry_in * running product of c to a shard.
+//
+// Replaces linrec/impl/cuda/linrec_pipe.cuh:8-143 and linrec/impl/cuda/linrec_tile.cuh:158-249.
+#pragma once
+#include "scan_core.cuh"
+
+namespace linrec {
+
+// Ticket -> tile coordinates.
+struct TileCoord {
+    long long row;     // first row of the tile
+    int q;             // chain: piece index in scan order
+    int piece;         // chain: piece index in memory order
+    int valid;         // chain: slots of the tile that lie inside the row
+};
+
+template <int T, bool ASC>
+__device__ __forceinline__ TileCoord decode_ticket(const ScanParams& p, uint32_t tk)
+{
+    TileCoord tc;
+    if (p.chain) {
+        const uint32_t ns = (uint32_t)p.numseq;
+        tc.q = (int)(tk / ns);
+        tc.row = (long long)(tk - (uint32_t)tc.q * ns);
+        tc.piece = ASC ? tc.q : p.chunks_per_row - 1 - tc.q;
+        const long long left = p.seqlen - (long long)tc.piece * T;
+        tc.valid = left < T ? (int)left : T;
+    } else {
+        tc.q = 0;
+        tc.piece = 0;
+        tc.row = (long long)tk * p.rows_per_tile;
+        tc.valid = T;
+    }
+    return tc;
+}
+
+// Everything that happens between "operands are in registers" and "results are in registers",
+// shared by both tile kernels.  `sync_a` has to be a block barrier after which the operand
+// buffers and wagg may be reused; it is passed in because the pipelined kernel refills its ring
+// at exactly that point.
+template <int E, int NT, bool BWD, bool ASC, typename AfterRead>
+__device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g,
+                                          const Operands<E, BWD>& op, const TileCoord& tc,
+                                          uint32_t tk, Pair* wagg, Pair* tprefix,
+                                          float (&o0)[E], float (&o1)[BWD ? E : 1],
+                                          AfterRead&& after_read)
+{
+    constexpr int NW = NT / 32;
+    const ThreadScan ts = scan_thread_and_warp<E, NT, BWD, ASC>(op, g, wagg);
+    if (!after_read()) return;   // contains the block barrier; false = the CTA is bailing out
+    const Pair wp = cross_warp_prefix(g, wagg);
+    Pair pre = pair_identity();
+    if (p.chain) {
+        if (g.ws == NW - 1) {   // the scan-last warp links the tile to its predecessors
+            const Pair bagg = combine(wp, wagg[NW - 1]);
+            Pair tp = pair_identity();
+            TileDesc* d = p.desc + tk;
+            const bool last_piece = (tc.q == p.chunks_per_row - 1);
+            if (tc.q == 0) {
+                if (g.lane == 0 && !last_piece) publish(d, bagg, true);
+            } else {
+                if (g.lane == 0 && !last_piece) publish(d, bagg, false);
+                tp = lookback(p, (long long)tk, tc.q, g.lane);
+                if (g.lane == 0 && !last_piece) publish(d, combine(tp, bagg), true);
+            }
+            if (g.lane == 0) {
+                *tprefix = tp;
+                if (last_piece && p.carry_out) {
+                    const Pair tot = combine(tp, bagg);
+                    p.carry_out[2 * tc.row] = tot.p;
+                    p.carry_out[2 * tc.row + 1] = tot.y;
+                }
+            }
+        }
+        __syncthreads();
+        pre = *tprefix;
+    }
+    if (g.need_wp) pre = combine(pre, wp);
+    pre = combine(pre, ts.excl);
+    if (!p.chain && p.carry_out && g.k == g.tpr - 1 && g.row_in_tile < p.rows_per_tile) {
+        const long long row = tc.row + g.row_in_tile;
+        if (row < p.numseq) {
+            const Pair tot = combine(pre, ts.agg);
+            p.carry_out[2 * row] = tot.p;
+            p.carry_out[2 * row + 1] = tot.y;
+        }
+    }
+    apply_carry<E, BWD, ASC>(op, pre.y, o0, o1);
+}
+
+// =================================================================================================
+//  Bulk-copy pipeline kernel
+// =================================================================================================
+template <typename ST, int E, int NT, int S, int OB, bool BWD>
+struct TmaLayout {
+    static constexpr int T = E * NT;
+    static constexpr int NIN = BWD ? 3 : 2;
+    static constexpr int NOUT = BWD ? 2 : 1;
+    static constexpr size_t kTileBytes = (size_t)T * sizeof(ST);
+    static constexpr size_t kDynSmem = kTileBytes * (S * NIN + OB * NOUT) + 1024;   // + alignment slack
+    static_assert(kTileBytes % 1024 == 0, "tile buffers must keep 1024-byte alignment");
+};
+
+template <typename ST, int E, int NT, int S, int OB, bool BWD, bool ASC>
+__global__ void __launch_bounds__(NT)
+linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_constant__ CUtensorMap tm_c,
+                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_out0,
+                  const __grid_constant__ CUtensorMap tm_out1, const ScanParams p)
+{
+    using L = TmaLayout<ST, E, NT, S, OB, BWD>;
+    constexpr int T = L::T, NW = NT / 32, NIN = L::NIN, NOUT = L::NOUT;
+    constexpr int EPL = 128 / (int)sizeof(ST);   // elements per 128-byte line
+    constexpr int LINES = T / EPL;
+
+    extern __shared__ uint8_t dyn_smem[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~(uintptr_t)1023);
+    auto in_buf = [&](int s, int a) { return reinterpret_cast<ST*>(base + (size_t)(s * NIN + a) * L::kTileBytes); };
+    auto out_buf = [&](int o, int a) {
+        return reinterpret_cast<ST*>(base + (size_t)(S * NIN + o * NOUT + a) * L::kTileBytes);
+    };
+
+    __shared__ __align__(8) uint64_t full[S];
+    __shared__ uint32_t tile_of_stage[S];
+    __shared__ uint32_t halo[S][2];      // backward, chain mode: raw 4-byte words around the tile
+    __shared__ Pair wagg[NW];
+    __shared__ Pair tprefix;
+    __shared__ int abort_flag;
+
+    const Geometry g = make_geometry<E, NT, ASC>(p);
+    const int tid = g.t;
+    const uint32_t ntiles = (uint32_t)p.ntiles;
+    const bool with_halo = BWD && p.chain;
+    const uint32_t stage_bytes =
+        (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
+                                 : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tm_in0);
+        ptx::prefetch_tensormap(&tm_c);
+        ptx::prefetch_tensormap(&tm_out0);
+        if (BWD) {
+            ptx::prefetch_tensormap(&tm_y);
+            ptx::prefetch_tensormap(&tm_out1);
+        }
+    }
+    __syncthreads();
+
+    // Thread 0 only: start the copies of ticket `tk` into ring slot `s`.
+    auto issue = [&](int s, uint32_t tk) {
+        const TileCoord tc = decode_ticket<T, ASC>(p, tk);
+        const int c1 = tc.piece * LINES;
+        const int c2 = (int)tc.row;
+        if (with_halo) {
+            // words just below and just above the piece; at a row end the edge value 0
+            const ST* crow = reinterpret_cast<const ST*>(p.c) + tc.row * p.row_stride;
+            const ST* yrow = reinterpret_cast<const ST*>(p.yin) + tc.row * p.row_stride;
+            const long long lo = (long long)tc.piece * T - 1;
+            const long long hi = (long long)tc.piece * T + T;
+            const ST* csrc = ASC ? crow + lo : crow + hi;   // coefficient at the scan predecessor
+            const ST* ysrc = ASC ? yrow + hi : yrow + lo;   // output at the scan successor
+            const bool c_ok = ASC ? (lo >= 0) : (hi < p.seqlen);
+            const bool y_ok = ASC ? (hi < p.seqlen) : (lo >= 0);
+            // 4-byte copies from the 4-byte-aligned word that contains the element
+            if (c_ok) ptx::cp_async_4(&halo[s][0], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(csrc) & ~(uintptr_t)3));
+            else halo[s][0] = 0u;
+            if (y_ok) ptx::cp_async_4(&halo[s][1], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ysrc) & ~(uintptr_t)3));
+            else halo[s][1] = 0u;
+            ptx::cp_async_mbar_arrive_noinc(&full[s]);
+        }
+        ptx::mbar_arrive_expect_tx(&full[s], stage_bytes);
+        ptx::tma_load_3d(in_buf(s, 0), &tm_in0, &full[s], 0, c1, c2);
+        ptx::tma_load_3d(in_buf(s, 1), &tm_c, &full[s], 0, c1, c2);
+        if (BWD) ptx::tma_load_3d(in_buf(s, 2), &tm_y, &full[s], 0, c1, c2);
+    };
+
+    uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket drawn one step ahead
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            const uint32_t tk = atomicAdd(p.header, 1u);
+            tile_of_stage[s] = tk;
+            if (tk < ntiles) issue(s, tk);
+        }
+        next_ticket = atomicAdd(p.header, 1u);
+    }
+    __syncthreads();
+
+    uint32_t it = 0;
+    for (;; ++it) {
+        const int s = (int)(it % S);
+        const uint32_t tk = tile_of_stage[s];
+        if (tk >= ntiles) break;
+        const TileCoord tc = decode_ticket<T, ASC>(p, tk);
+
+        if (!ptx::mbar_wait_bounded(&full[s], (it / S) & 1u, p.wait_budget)) {
+            atomicOr(p.header + 1, kStatusCopyTimeout);
+            abort_flag = 1;
+        }
+
+        float pred_c = 0.0f, succ_y = 0.0f;
+        if (with_halo) {
+            // the halo word holds the element in its low or high half for 2-byte storage
+            const uint32_t wc = halo[s][0], wy = halo[s][1];
+            if (sizeof(ST) == 4) {
+                pred_c = __uint_as_float(wc);
+                succ_y = __uint_as_float(wy);
+            } else {
+                // element below the piece has an odd index (upper half), above it an even one
+                const bool c_upper = ASC, y_upper = !ASC;
+                pred_c = __uint_as_float(c_upper ? (wc & 0xffff0000u) : (wc << 16));
+                succ_y = __uint_as_float(y_upper ? (wy & 0xffff0000u) : (wy << 16));
+            }
+        }
+        const bool zero_first =
+            !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
+
+        Operands<E, BWD> op;
+        load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1),
+                                                 BWD ? in_buf(s, 2) : in_buf(s, 1), pred_c, succ_y,
+                                                 tc.valid, zero_first);
+        float o0[E], o1[BWD ? E : 1];
+        bool alive = true;
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, wagg, &tprefix, o0, o1, [&]() -> bool {
+            // the output buffer about to be reused must have been drained by its bulk store
+            if (tid == 0) ptx::tma_wait_group_read<OB - 1>();
+            __syncthreads();
+            if (abort_flag) {
+                alive = false;
+                return false;
+            }
+            if (tid == 0) {   // ring slot s is free again: refill it with the ticket drawn earlier
+                tile_of_stage[s] = next_ticket;
+                if (next_ticket < ntiles) issue(s, next_ticket);
+                next_ticket = atomicAdd(p.header, 1u);
+            }
+            return true;
+        });
+        if (!alive) break;
+
+        const int ob = (int)(it % OB);
+        store_run<ST, E>(out_buf(ob, 0), g.t, o0);
+        if constexpr (BWD) store_run<ST, E>(out_buf(ob, 1), g.t, o1);
+        ptx::fence_proxy_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            const int c1 = tc.piece * LINES;
+            const int c2 = (int)tc.row;
+            ptx::tma_store_3d(&tm_out0, out_buf(ob, 0), 0, c1, c2);
+            if (BWD) ptx::tma_store_3d(&tm_out1, out_buf(ob, 1), 0, c1, c2);
+            ptx::tma_commit_group();
+        }
+    }
+
+    if (tid == 0) {
+        if (abort_flag) {
+            // best effort: let copies already in flight land before the CTA gives its memory back
+            for (uint32_t j = 1; j < (uint32_t)S; ++j) {
+                const uint32_t jt = it + j;
+                if (tile_of_stage[jt % S] < ntiles)
+                    (void)ptx::mbar_wait_bounded(&full[jt % S], (jt / S) & 1u, p.wait_budget);
+            }
+        }
+        ptx::tma_wait_group<0>();
+    }
+}
+
+// =================================================================================================
+//  Any-alignment kernel
+// =================================================================================================
+template <typename ST, int E, int NT, bool BWD, bool ASC>
+__global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
+{
+    constexpr int T = E * NT, NW = NT / 32;
+    __shared__ __align__(1024) ST buf_in0[T];
+    __shared__ __align__(1024) ST buf_c[T];
+    __shared__ __align__(1024) ST buf_y[BWD ? T : 8];
+    __shared__ float halo[2];
+    __shared__ Pair wagg[NW];
+    __shared__ Pair tprefix;
+    __shared__ uint32_t ticket_s;
+
+    const Geometry g = make_geometry<E, NT, ASC>(p);
+    const int tid = g.t;
+    const uint32_t ntiles = (uint32_t)p.ntiles;
+    const ST* gin0 = reinterpret_cast<const ST*>(p.in0);
+    const ST* gc = reinterpret_cast<const ST*>(p.c);
+    const ST* gy = reinterpret_cast<const ST*>(p.yin);
+    ST* gout0 = reinterpret_cast<ST*>(p.out0);
+    ST* gout1 = reinterpret_cast<ST*>(p.out1);
+    const int spr = p.chain ? T : p.slots_per_row;
+
+    for (;;) {
+        if (tid == 0) ticket_s = atomicAdd(p.header, 1u);
+        __syncthreads();   // also: everybody has finished storing the previous tile
+        const uint32_t tk = ticket_s;
+        if (tk >= ntiles) break;
+        const TileCoord tc = decode_ticket<T, ASC>(p, tk);
+        const long long col0 = (long long)tc.piece * T;
+
+        // ---- cooperative, coalesced load with identity fill ------------------------------------
+        for (int i = tid; i < T; i += NT) {
+            const int j = p.chain ? 0 : i / spr;
+            const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
+            const long long row = tc.row + j;
+            const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+            const long long off = row * p.row_stride + col;
+            write_slot<ST>(buf_in0, i, ok ? Storage<ST>::to_float(gin0[off]) : 0.0f);
+            write_slot<ST>(buf_c, i, ok ? Storage<ST>::to_float(gc[off]) : 1.0f);
+            if (BWD) write_slot<ST>(buf_y, i, ok ? Storage<ST>::to_float(gy[off]) : 0.0f);
+        }
+        if (BWD && p.chain && tid < 2) {
+            const long long lo = col0 - 1, hi = col0 + T;
+            const long long rb = tc.row * p.row_stride;
+            if (tid == 0) {   // coefficient at the scan predecessor of the piece
+                const long long ci = ASC ? lo : hi;
+                halo[0] = (ci >= 0 && ci < p.seqlen) ? Storage<ST>::to_float(gc[rb + ci]) : 0.0f;
+            } else {          // output at the scan successor of the piece
+                const long long yi = ASC ? hi : lo;
+                halo[1] = (yi >= 0 && yi < p.seqlen) ? Storage<ST>::to_float(gy[rb + yi]) : 0.0f;
+            }
+        }
+        __syncthreads();
+
+        const bool zero_first =
+            !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
+        Operands<E, BWD> op;
+        load_operands<ST, E, NT, BWD, ASC, false>(op, g, buf_in0, buf_c, buf_y,
+                                                  (BWD && p.chain) ? halo[0] : 0.0f,
+                                                  (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
+        float o0[E], o1[BWD ? E : 1];
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, wagg, &tprefix, o0, o1, [&]() -> bool {
+            __syncthreads();
+            return true;
+        });
+        // every thread holds its operands in registers, so the input buffers can take the results
+        store_run<ST, E>(buf_in0, g.t, o0);
+        if constexpr (BWD) store_run<ST, E>(buf_y, g.t, o1);
+        __syncthreads();
+
+        // ---- cooperative, coalesced store ------------------------------------------------------
+        for (int i = tid; i < T; i += NT) {
+            const int j = p.chain ? 0 : i / spr;
+            const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
+            const long long row = tc.row + j;
+            const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+            if (ok) {
+                const long long off = row * p.row_stride + col;
+                gout0[off] = Storage<ST>::from_float(read_slot<ST>(buf_in0, i));
+                if (BWD) gout1[off] = Storage<ST>::from_float(read_slot<ST>(buf_y, i));
+            }
+        }
+    }
+}
+
+// =================================================================================================
+//  Sequential operator: one thread per row
+// =================================================================================================
+template <typename ST, bool BWD>
+__global__ void linrec_seq_kernel(const ScanParams p, int reverse)
+{
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= p.numseq) return;
+    const long long L = p.seqlen;
+    const long long rb = r * p.row_stride;
+    const ST* in0 = reinterpret_cast<const ST*>(p.in0) + rb;
+    const ST* c = reinterpret_cast<const ST*>(p.c) + rb;
+    ST* out0 = reinterpret_cast<ST*>(p.out0) + rb;
+    if (!BWD) {
+        const bool asc = !reverse;
+        float v = 0.0f;
+        for (long long n = 0; n < L; ++n) {
+            const long long i = asc ? n : L - 1 - n;
+            const float x = Storage<ST>::to_float(in0[i]);
+            v = (n == 0) ? x : fmaf(v, Storage<ST>::to_float(c[i]), x);
+            out0[i] = Storage<ST>::from_float(v);
+        }
+    } else {
+        const ST* y = reinterpret_cast<const ST*>(p.yin) + rb;
+        ST* out1 = reinterpret_cast<ST*>(p.out1) + rb;
+        const bool asc = reverse != 0;   // the gradient scan runs against the forward direction
+        float v = 0.0f;
+        for (long long n = 0; n < L; ++n) {
+            const long long i = asc ? n : L - 1 - n;
+            const long long ip = asc ? i - 1 : i + 1;   // scan predecessor
+            const long long is = asc ? i + 1 : i - 1;   // scan successor
+            const float dy = Storage<ST>::to_float(in0[i]);
+            v = (n == 0) ? dy : fmaf(v, Storage<ST>::to_float(c[ip]), dy);
+            out0[i] = Storage<ST>::from_float(v);
+            const float ys = (n == L - 1) ? 0.0f : Storage<ST>::to_float(y[is]);
+            out1[i] = Storage<ST>::from_float(v * ys);
+        }
+    }
+}
+
+// =================================================================================================
+//  Workspace header initialisation
+// =================================================================================================
+__global__ void linrec_init_header_kernel(uint32_t* header, uint32_t first_ticket)
+{
+    if (threadIdx.x == 0) {
+        header[0] = first_ticket;
+        header[1] = 0u;
+    }
+}
+
+}  // namespace linrec

@@ -1,0 +1,318 @@
+"""Parity of the CUDA path with the CPU oracle (GPU only; every call goes through the C ABI).
+
+Tolerances (from the task definition): fp32  rtol 1e-4, atol 1e-5 against the fp32 oracle;
+bf16 storage  rtol 2^-7, atol 1e-5 against the fp32 oracle run on the bf16-rounded inputs.
+dc = dx * y_shifted carries the rounding of both factors, so its absolute tolerance is doubled.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import GOLDEN_CASES
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-4, 1e-5
+SEED = 12334567890
+
+
+def _ops():
+    import linrec_b200
+    return linrec_b200
+
+
+def _data(shape, clo=0.0, chi=1.0, seed=SEED, bwd=False):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    c = clo + (chi - clo) * torch.rand(shape, generator=g)
+    dy = torch.randn(shape, generator=g)
+    return x, c, dy
+
+
+def _check_fwd_bwd(x, c, dy, rev, family="pipe", rtol=RTOL, atol=ATOL, **kw):
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    fwd = getattr(lb._C, f"linrec_{family}_fwd")
+    bwd = getattr(lb._C, f"linrec_{family}_bwd")
+    xd, cd, dyd = x.to(dev), c.to(dev), dy.to(dev)
+    y = fwd(inputs=xd, coeffs=cd, reverse=rev, **kw)
+    y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+    np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=rtol, atol=atol)
+    # backward from the oracle's forward outputs, so that the two checks are independent
+    yd = torch.from_numpy(y_ref).to(dev)
+    dx, dc = bwd(d_outputs=dyd, coeffs=cd, outputs=yd, reverse=rev, **kw)
+    dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+    np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=rtol, atol=atol)
+    np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=rtol, atol=2 * atol)
+    lb.check_status()
+
+
+# ---- golden fixtures recorded from the reference ---------------------------------------------------
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+@pytest.mark.parametrize("rev", [False, True])
+@pytest.mark.parametrize("family", ["ref", "tile", "pipe"])
+def test_golden(golden, name, rev, family):
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = (torch.from_numpy(golden[f"{name}/{k}"]).to(dev) for k in ("x", "c", "dy"))
+    tag = f"{name}/rev{int(rev)}"
+    y = getattr(lb._C, f"linrec_{family}_fwd")(inputs=x, coeffs=c, reverse=rev)
+    np.testing.assert_allclose(y.cpu().numpy(), golden[f"{tag}/y"], rtol=RTOL, atol=ATOL)
+    yg = torch.from_numpy(golden[f"{tag}/y"]).to(dev)
+    dx, dc = getattr(lb._C, f"linrec_{family}_bwd")(d_outputs=dy, coeffs=c, outputs=yg, reverse=rev)
+    np.testing.assert_allclose(dx.cpu().numpy(), golden[f"{tag}/dx"], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(dc.cpu().numpy(), golden[f"{tag}/dc"], rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()
+
+
+# ---- shapes: short, ragged, tile-sized, chained, with every direction ------------------------------
+SHAPES = [
+    (1, 1), (7, 1), (5, 2), (3, 15), (3, 16), (3, 17), (4, 31), (9, 32), (9, 33), (2, 64), (11, 96),
+    (6, 100), (300, 128), (37, 160), (129, 256), (5, 1000), (64, 1024), (3, 2047), (3, 2048), (3, 2049),
+    (17, 4096), (2, 4097), (5, 4128), (3, 6144), (4, 8192), (2, 12288 + 32), (3, 20000), (2, 65536),
+    (1, 1 << 18),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_pipe_shapes(shape, rev):
+    x, c, dy = _data(shape)
+    _check_fwd_bwd(x, c, dy, rev)
+
+
+@pytest.mark.parametrize("shape", [(512, 4096)], ids=["cfg1_512x4096"])
+def test_config1_forward(shape):
+    """The reference's own CPU-runnable case: forward, reverse=False, (512, 4096)."""
+    x, c, dy = _data(shape)
+    _check_fwd_bwd(x, c, dy, False)
+
+
+@pytest.mark.parametrize("rev", [False, True])
+def test_slow_decay_coefficients(rev):
+    """c ~ U(0.9, 1): carries survive for thousands of steps, so chained tiles really matter."""
+    x, c, dy = _data((6, 3 * 8192), clo=0.9, chi=1.0)
+    _check_fwd_bwd(x, c, dy, rev)
+
+
+def test_three_dim_batch_autograd():
+    """(batch, channel, length) through autograd, against the oracle's analytic backward."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((3, 5, 777), clo=0.9, chi=1.0)
+    for rev in (False, True):
+        xd = x.to(dev).requires_grad_(True)
+        cd = c.to(dev).requires_grad_(True)
+        y = lb.linrec(xd, cd, reverse=rev)
+        gx, gc = torch.autograd.grad(y, (xd, cd), dy.to(dev))
+        y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+        dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
+
+
+# ---- every compiled variant ------------------------------------------------------------------------
+def _variants():
+    lb = _ops()
+    return lb._C.config_names, lb._C.config_list
+
+
+@pytest.mark.parametrize("shape", [(40, 512), (3, 4096 * 5), (2, 8192 * 3 + 4096)], ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_all_variants(shape, rev):
+    names, configs = _variants()
+    x, c, dy = _data(shape, clo=0.5, chi=1.0)
+    assert len(configs) >= 4
+    for cfg in configs:
+        _check_fwd_bwd(x, c, dy, rev, **dict(zip(names, cfg)))
+
+
+# ---- layouts ---------------------------------------------------------------------------------------
+def test_unaligned_base_and_row_stride():
+    """Views that start one element into an allocation and rows with padding between them."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(7)
+    for (rows, L, stride, off) in [(5, 256, 256, 1), (5, 256, 300, 0), (4, 4096, 4100, 3), (3, 9000, 9001, 1)]:
+        big_x = torch.randn(rows * stride + off + 8, generator=g)
+        big_c = torch.rand(rows * stride + off + 8, generator=g)
+        xv = torch.as_strided(big_x.to(dev), (rows, L), (stride, 1), off)
+        cv = torch.as_strided(big_c.to(dev), (rows, L), (stride, 1), off)
+        xh = torch.as_strided(big_x, (rows, L), (stride, 1), off).contiguous()
+        ch = torch.as_strided(big_c, (rows, L), (stride, 1), off).contiguous()
+        for rev in (False, True):
+            y = lb.linrec(xv, cv, reverse=rev)
+            np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(xh.numpy(), ch.numpy(), reverse=rev),
+                                       rtol=RTOL, atol=ATOL)
+
+
+def test_permuted_batch_dims():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, _ = _data((4, 6, 200))
+    xp, cp = x.to(dev).permute(1, 0, 2), c.to(dev).permute(1, 0, 2)
+    y = lb.linrec(xp, cp)
+    ref = oracle.fwd_f32(x.permute(1, 0, 2).contiguous().numpy(), c.permute(1, 0, 2).contiguous().numpy())
+    np.testing.assert_allclose(y.cpu().numpy(), ref, rtol=RTOL, atol=ATOL)
+
+
+def test_guard_bands_untouched():
+    """Outputs are written into the middle of a sentinel-filled allocation through the C ABI; the
+    bytes before and after every row block must keep the sentinel (no out-of-row writes)."""
+    import ctypes
+    from linrec_b200 import _capi
+    dev = torch.device("cuda:0")
+    for (rows, L, stride) in [(7, 100, 100), (5, 4096, 4096), (3, 8192 + 64, 8192 + 64), (6, 333, 340)]:
+        for bwd in (False, True):
+            for rev in (False, True):
+                x, c, dy = _data((rows, stride))
+                pad = 1024
+                n = rows * stride
+                outs = [torch.full((n + 2 * pad,), -777.0, device=dev) for _ in range(2)]
+                xd, cd, dyd = x.to(dev), c.to(dev), dy.to(dev)
+                ws_bytes = _capi.lib.linrec_b200_workspace_size(rows, L, 0)
+                ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+                stream = torch.cuda.current_stream().cuda_stream
+                o0 = outs[0].data_ptr() + 4 * pad
+                o1 = outs[1].data_ptr() + 4 * pad
+                if not bwd:
+                    rc = _capi.lib.linrec_b200_fwd(_capi.KIND_PIPE, xd.data_ptr(), cd.data_ptr(), o0, rows, L, stride,
+                                                   int(rev), 0, None, ws.data_ptr(), ws_bytes, stream)
+                else:
+                    rc = _capi.lib.linrec_b200_bwd(_capi.KIND_PIPE, dyd.data_ptr(), cd.data_ptr(), xd.data_ptr(), o0, o1,
+                                                   rows, L, stride, int(rev), 0, None, ws.data_ptr(), ws_bytes, stream)
+                assert rc == 0
+                torch.cuda.synchronize()
+                for o in outs[: 2 if bwd else 1]:
+                    body = o[pad:pad + n].view(rows, stride)
+                    assert torch.all(o[:pad] == -777.0) and torch.all(o[pad + n:] == -777.0)
+                    if stride > L:
+                        assert torch.all(body[:, L:] == -777.0)
+                    assert not torch.any(body[:, :L] == -777.0)
+
+
+# ---- the three operator families and their error behaviour ------------------------------------------
+def test_tile_family_refuses_long_rows():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x = torch.zeros(2, 1 << 16, device=dev)
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_tile_fwd(inputs=x, coeffs=x)
+    y = lb._C.linrec_tile_fwd(inputs=x[:, :1024].contiguous(), coeffs=x[:, :1024].contiguous())
+    assert y.shape == (2, 1024)
+
+
+def test_unknown_option_is_not_implemented():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x = torch.zeros(2, 64, device=dev)
+    with pytest.raises(NotImplementedError):
+        lb._C.linrec_pipe_fwd(inputs=x, coeffs=x, kElemsPerThread=5)
+    with pytest.raises(NotImplementedError):
+        lb._C.linrec_pipe_fwd(inputs=x, coeffs=x, noSuchOption=1)
+
+
+def test_precondition_errors():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    a = torch.zeros(2, 64, device=dev)
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_pipe_fwd(inputs=a, coeffs=torch.zeros(2, 32, device=dev))
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_pipe_fwd(inputs=a, coeffs=a.double())
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_pipe_fwd(inputs=a.t(), coeffs=a.t())
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_pipe_fwd(inputs=a.cpu(), coeffs=a.cpu())
+
+
+def test_empty_inputs():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    for shape in [(0, 5), (3, 0)]:
+        z = torch.zeros(shape, device=dev)
+        assert lb.linrec(z, z).shape == shape
+
+
+def test_attrs_and_configs():
+    lb = _ops()
+    names, configs = _variants()
+    assert names[0] == "kElemsPerThread" and len(set(configs)) == len(configs)
+    a = lb._C.linrec_pipe_attrs(True)
+    assert a["numRegs"] > 0 and a["binaryVersion"] >= 100 and a["localSizeBytes"] == 0
+    b = lb._C.linrec_pipe_attrs(False, **dict(zip(names, configs[0])))
+    assert b["numRegs"] > 0 and b["residentBlocksPerSM"] >= 1
+
+
+def test_inf_in_first_coefficient_is_ignored():
+    """c at the scan start has no effect, even when it is not finite (linrec_ref.cuh:63)."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, _ = _data((3, 5000))
+    c[:, 0] = float("inf")
+    y = lb.linrec(x.to(dev), c.to(dev))
+    c2 = c.clone()
+    c2[:, 0] = 0.0
+    np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(x.numpy(), c2.numpy()), rtol=RTOL, atol=ATOL)
+
+
+# ---- bounded waits -----------------------------------------------------------------------------------
+def test_lookback_wait_gives_up_with_status():
+    """Tickets are started past the first piece of every row, so the pieces that run wait for a
+    predecessor that never publishes.  The wait must end by itself and leave a status code; the
+    context must stay usable."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x = torch.ones(2, 4096 * 4, device=dev)
+    lb._C.linrec_pipe_fwd(inputs=x, coeffs=x, firstTicket=2, waitBudgetMs=20)
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        lb.check_status()
+    # the next call resets the status word and works
+    y = lb.linrec(x, x * 0.5)
+    lb.check_status()
+    assert torch.isfinite(y).all()
+
+
+# ---- against the reference's own CUDA kernels, where the checker library was built -------------------
+def _refcuda():
+    import ctypes
+    import os
+    path = os.path.join(os.path.dirname(oracle.__file__), "_ref", "liblinrec_refcuda.so")
+    if not os.path.exists(path):
+        pytest.skip("reference CUDA checker not built on this machine")
+    L = ctypes.CDLL(path)
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    L.refcuda_fwd_f32.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    L.refcuda_bwd_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, vp]
+    return L
+
+
+@pytest.mark.parametrize("shape", [(64, 512), (16, 65536)], ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_against_reference_cuda_kernels(shape, rev):
+    R = _refcuda()
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.9, chi=1.0)
+    xd, cd, dyd = x.to(dev), c.to(dev), dy.to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    y_ref = torch.empty_like(xd)
+    assert R.refcuda_fwd_f32(xd.data_ptr(), cd.data_ptr(), y_ref.data_ptr(), shape[0], shape[1], int(rev), stream) == 0
+    y = lb.linrec(xd, cd, reverse=rev)
+    torch.testing.assert_close(y, y_ref, rtol=RTOL, atol=ATOL)
+    dx_ref, dc_ref = torch.empty_like(xd), torch.empty_like(xd)
+    assert R.refcuda_bwd_f32(dyd.data_ptr(), cd.data_ptr(), y_ref.data_ptr(), dx_ref.data_ptr(), dc_ref.data_ptr(),
+                             shape[0], shape[1], int(rev), stream) == 0
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dyd, coeffs=cd, outputs=y_ref, reverse=rev)
+    torch.testing.assert_close(dx, dx_ref, rtol=RTOL, atol=ATOL)
+    if rev:
+        # the reference's reverse backward lets two blocks race on column 0 of rows >= 1
+        torch.testing.assert_close(dc[:, 1:], dc_ref[:, 1:], rtol=RTOL, atol=2 * ATOL)
+        torch.testing.assert_close(dc[0], dc_ref[0], rtol=RTOL, atol=2 * ATOL)
+    else:
+        torch.testing.assert_close(dc, dc_ref, rtol=RTOL, atol=2 * ATOL)
+    # our own sequential operator against the reference's, same algorithm: tight agreement
+    y_seq = lb._C.linrec_ref_fwd(inputs=xd, coeffs=cd, reverse=rev)
+    torch.testing.assert_close(y_seq, y_ref, rtol=1e-6, atol=1e-6)
