@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the linear-recurrence scan hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  A "step" is one forward plus one backward pass of the scan over one batch
+of synthetic input.  Workload: the autograd configuration of the task definition -- x ~ N(0,1),
+c ~ U(0.9, 1), dy ~ N(0,1), fp32, shape (16, 2048, 8192), scanning the last dimension -- per GPU;
+with N GPUs every rank holds its own batch of that shape (channel sharding of a (16*N, 2048, 8192)
+batch, no collective on the data path), i.e. weak scaling.
+
+metric   linrec fwd+bwd achieved HBM GB/s: algorithmic bytes (12 B/element forward + 20 B/element
+         backward for fp32, the byte model of the reference's eval/utils.py:48-60) of all ranks
+         divided by the slowest rank's device time for the K steps.
+value    inputs resident in HBM, operators called through the C ABI.
+e2e      the same step through the public API (`linrec_b200.linrec` + autograd) starting from
+         pinned HOST buffers: host->device copies of x, c, dy and device->host copies of y, dx, dc
+         are inside the timed region.
+roofline the backward operator (the larger of the two kernels of a step): algorithmic bytes per
+         launch / mean CUDA-event duration of the launches inside the timed region, against the
+         measured copy bandwidth of MEASURED_PEAKS.json (fallback 6650 GB/s).
+cpu_baseline  the reference's CPU path (a torch restatement of its Python loop, oracle.pyloop_*)
+         timed on this machine's host cores on a bounded sample of the same workload.
+
+--impl reference times that CPU path alone, with all host threads, and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "linrec fwd+bwd achieved HBM GB/s"
+SHAPE = (16, 2048, 8192)          # per GPU
+C_RANGE = (0.9, 1.0)
+BYTES_PER_ELEM_FWD, BYTES_PER_ELEM_BWD = 12, 20
+SEED = 12334567890
+FALLBACK_PEAK_GBS = 6650.0
+
+# DRAM traffic of the backward kernel measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum
+# per launch, divided by the elements of the captured launch); the capture and its command are in
+# profiles/.  None until a capture exists.
+NCU_DRAM_BYTES_PER_ELEM_BWD = None
+
+
+def _peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_PEAK_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML from a thread while the timed region runs.
+
+    NVML is initialised and the first sample is taken BEFORE the timed region: attaching a
+    monitoring client to the GPU (which is what starting `nvidia-smi` does) stalls kernel launches
+    for tens of milliseconds, which must not land inside the measurement."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period, self.rows = index, period_s, []
+        self.active = threading.Event()
+        self.done = threading.Event()
+        self.nvml = None
+        self.handle = None
+        self.thread = None
+
+    def _sample(self):
+        n = self.nvml
+        sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        return sm, mx, int(get(self.handle))
+
+    def prepare(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            # NVML enumerates physical devices; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in vis.split(",") if v.strip().isdigit()]
+            phys = int(ids[self.index]) if self.index < len(ids) else self.index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self._sample()
+        except Exception:
+            self.nvml = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _loop(self):
+        while not self.done.is_set():
+            if self.active.is_set():
+                try:
+                    self.rows.append(self._sample())
+                except Exception:
+                    pass
+            time.sleep(self.period)
+
+    def start(self):
+        self.active.set()
+
+    def stop(self):
+        self.active.clear()
+        self.done.set()
+        if self.nvml is None or not self.rows:
+            return None
+        sm = [r[0] for r in self.rows]
+        mask = 0
+        for r in self.rows:
+            mask |= r[2]
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": max(r[1] for r in self.rows),
+                "reasons": sorted(v for k, v in self.REASONS.items() if mask & k), "samples": len(sm)}
+
+
+def _cpu_reference_run(steps: int, warmup: int, rows: int):
+    """The reference's CPU path on `rows` rows of the workload; returns (seconds per step, info)."""
+    import torch
+
+    import oracle
+    L = SHAPE[-1]
+    g = torch.Generator(device="cpu").manual_seed(SEED)
+    x = torch.randn((rows, L), generator=g)
+    c = C_RANGE[0] + (C_RANGE[1] - C_RANGE[0]) * torch.rand((rows, L), generator=g)
+    dy = torch.randn((rows, L), generator=g)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        y = oracle.pyloop_fwd(x, c)
+        dx, dc = oracle.pyloop_bwd(dy, c, y)
+        t1 = time.perf_counter()
+        if i >= warmup:
+            times.append(t1 - t0)
+    sec = statistics.median(times)
+    # the C restatement with OpenMP over the rows, for context (a far tighter CPU loop than the
+    # reference has)
+    xn, cn, dyn = x.numpy(), c.numpy(), dy.numpy()
+    t0 = time.perf_counter()
+    yn = oracle.fwd_f32(xn, cn)
+    oracle.bwd_f32(dyn, cn, yn)
+    c_sec = time.perf_counter() - t0
+    info = {"rows": rows, "seqlen": L, "torch_threads": torch.get_num_threads(), "os_cpu_count": os.cpu_count(),
+            "c_port_openmp_gbs": rows * L * 32 / c_sec / 1e9, "c_port_threads": oracle.threads()}
+    return sec, info
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    rows = 1024
+    sec, info = _cpu_reference_run(args.steps, max(args.warmup, 1), rows)
+    gbs = rows * SHAPE[-1] * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD) / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "autograd fwd+bwd, x~N(0,1), c~U(0.9,1), fp32, (16,2048,8192) per GPU",
+                   "timing": "host wall clock, CPU path"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": info["torch_threads"], "kind": "port",
+                         "sample": f"{rows} of 32768 rows x {SHAPE[-1]} (fwd+bwd), torch restatement of the "
+                                   "reference's Python loop", **info},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import linrec_b200
+    C = linrec_b200._C
+
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    x = torch.randn(SHAPE, device=dev, generator=g)
+    c = C_RANGE[0] + (C_RANGE[1] - C_RANGE[0]) * torch.rand(SHAPE, device=dev, generator=g)
+    dy = torch.randn(SHAPE, device=dev, generator=g)
+    n_elem = x.numel()
+
+    def step():
+        y = C.linrec_pipe_fwd(inputs=x, coeffs=c, reverse=False)
+        dx, dc = C.linrec_pipe_bwd(d_outputs=dy, coeffs=c, outputs=y, reverse=False)
+        return y, dx, dc
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.prepare()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    linrec_b200.check_status()
+
+    # ---- device-resident timing: K steps, events around the whole region and around every operator
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        step()
+    barrier()
+    if sampler:
+        sampler.start()
+    launches0 = C.launch_count()
+    start.record()
+    for i in range(args.steps):
+        ev[i][0].record()
+        y = C.linrec_pipe_fwd(inputs=x, coeffs=c, reverse=False)
+        ev[i][1].record()
+        dx, dc = C.linrec_pipe_bwd(d_outputs=dy, coeffs=c, outputs=y, reverse=False)
+        ev[i][2].record()
+    stop.record()
+    barrier()
+    launches = C.launch_count() - launches0
+    total_ms = start.elapsed_time(stop)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    step_ms = [e[0].elapsed_time(e[2]) for e in ev]
+    clocks = sampler.stop() if sampler else None
+    linrec_b200.check_status()
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    step_bytes = n_elem * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD)
+    value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+
+    # ---- end to end from pinned host buffers through the public API -----------------------------
+    e2e_steps = max(1, min(args.steps, 3))
+    hx, hc, hdy = (torch.empty(SHAPE, pin_memory=True) for _ in range(3))
+    hy, hdx, hdc = (torch.empty(SHAPE, pin_memory=True) for _ in range(3))
+    hx.copy_(x); hc.copy_(c); hdy.copy_(dy)
+
+    def e2e_step():
+        xd = hx.to(dev, non_blocking=True).requires_grad_(True)
+        cd = hc.to(dev, non_blocking=True).requires_grad_(True)
+        dyd = hdy.to(dev, non_blocking=True)
+        yd = linrec_b200.linrec(xd, cd, reverse=False)
+        gx, gc = torch.autograd.grad(yd, (xd, cd), dyd)
+        hy.copy_(yd.detach(), non_blocking=True)
+        hdx.copy_(gx, non_blocking=True)
+        hdc.copy_(gc, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    e2e_ok = bool(torch.equal(hy, y.cpu()))   # same numbers as the device-resident step
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = _peak()
+    achieved = n_elem * BYTES_PER_ELEM_BWD / (bwd_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": "linrec_tma_kernel<float,16,128,2,1,bwd> (backward operator)",
+            "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": (NCU_DRAM_BYTES_PER_ELEM_BWD * n_elem) if NCU_DRAM_BYTES_PER_ELEM_BWD else None,
+            "algorithmic_bytes_per_launch": n_elem * BYTES_PER_ELEM_BWD, "ms_per_launch": bwd_ms,
+            "frac_of_nominal_8TBs": achieved / 8000.0,
+            "forward": {"achieved": n_elem * BYTES_PER_ELEM_FWD / (fwd_ms * 1e-3) / 1e9, "ms_per_launch": fwd_ms,
+                        "frac": n_elem * BYTES_PER_ELEM_FWD / (fwd_ms * 1e-3) / 1e9 / peak}}
+
+    cpu = None
+    if world == 1:
+        rows = 1024
+        sec, info = _cpu_reference_run(3, 1, rows)
+        cpu = {"value": rows * SHAPE[-1] * 32 / sec / 1e9, "unit": "GB/s", "cores": info["torch_threads"],
+               "kind": "port",
+               "sample": f"{rows} of 32768 rows x {SHAPE[-1]} (fwd+bwd), torch restatement of the reference's "
+                         "Python loop on the host cores", **info}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "autograd fwd+bwd, x~N(0,1), c~U(0.9,1), fp32, (16,2048,8192) per GPU "
+                               "(numseq 32768, seqlen 8192)",
+                   "sharding": "channel (rows) sharded, no data-path collective",
+                   "l2": "inputs larger than L2 (1 GiB per tensor, 6 tensors)",
+                   "elements_per_gpu": n_elem, "bytes_per_element": 32},
+        "step_ms_median": statistics.median(step_ms), "step_ms_max": max(step_ms),
+        "gelem_per_s": world * n_elem * args.steps / (total_ms * 1e-3) / 1e9,
+        "frac_of_measured_peak": value / (world * peak),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 3 * n_elem * 4,
+                "d2h_bytes_per_step": 3 * n_elem * 4, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "matches_device_run": e2e_ok},
+        "gpu_launches": int(launches),
+        "roofline": roof,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -124,7 +124,10 @@ const std::vector<TmaVariant>& tma_variants()
         make_tma_variant<16, 128, 4, 2>(),
         make_tma_variant<16, 128, 2, 1>(),
         make_tma_variant<8, 256, 3, 1>(),
+        make_tma_variant<8, 256, 2, 1>(),
+        make_tma_variant<8, 512, 2, 1>(),
         make_tma_variant<16, 512, 2, 1>(),
+        make_tma_variant<16, 512, 1, 1>(),
     };
     return v;
 }
@@ -293,7 +296,7 @@ void shape_plan(Plan& pl, int dtype, int64_t numseq, int64_t seqlen)
 // The regime selector.  `kind` TILE refuses rows that do not fit one tile, as the reference's
 // tile operator does (linrec/impl/cuda/linrec_tile.cu:60).
 int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride,
-              const void* const* ptrs, int nptrs, const Options& opt)
+              const void* const* ptrs, int nptrs, const Options& opt, int max_smem)
 {
     const bool can_tma = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, nptrs);
     int memcode = opt.memcode;
@@ -301,20 +304,36 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
     if (memcode != 0 && memcode != 1) return LINREC_ERR_NOT_IMPLEMENTED;
     if (memcode == 1 && !can_tma) return LINREC_ERR_UNALIGNED;
     pl.tma = memcode == 1;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
     if (pl.tma) {
-        // defaults of the selector; every field can be overridden
+        // Defaults of the selector (measured on B200, see the sweep of the standalone harness):
+        // forward: 512 threads x 16 elements, two ring slots; backward: 128 x 16, two ring slots
+        // (its five arrays per tile leave room for three such CTAs per SM).  The tile family needs
+        // the whole row in one tile and therefore takes the smallest tile that holds the row.
         int E = opt.E, NT = opt.NT, S = opt.S, OB = opt.OB;
-        if (E < 0 && NT < 0 && S < 0 && OB < 0) {
-            if (!bwd) { E = 16; NT = 256; S = 2; OB = 1; }
-            else      { E = 16; NT = 128; S = 3; OB = 1; }
+        const bool pinned = !(E < 0 && NT < 0 && S < 0 && OB < 0);
+        if (!pinned && kind != LINREC_KIND_TILE) {
+            if (!bwd) { E = 16; NT = 512; S = 2; OB = 1; }
+            else      { E = 16; NT = 128; S = 2; OB = 1; }
         }
+        const TmaVariant* best = nullptr;
         for (const TmaVariant& v : tma_variants()) {
-            if ((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S) && (OB < 0 || v.OB == OB)) {
-                pl.tv = &v;
+            if (!((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S) && (OB < 0 || v.OB == OB))) continue;
+            if (v.smem[di][bwd] > (size_t)max_smem) continue;
+            if (!pinned && kind == LINREC_KIND_TILE) {
+                // smallest tile that holds the row; among equals the deeper ring
+                if (v.E * v.NT < seqlen) continue;
+                if (!best || v.E * v.NT < best->E * best->NT || (v.E * v.NT == best->E * best->NT && v.S > best->S)) best = &v;
+            } else {
+                best = &v;
                 break;
             }
         }
-        if (!pl.tv) return LINREC_ERR_NOT_IMPLEMENTED;
+        if (!best) {
+            if (!pinned && kind == LINREC_KIND_TILE) return LINREC_ERR_TOO_LONG;
+            return LINREC_ERR_NOT_IMPLEMENTED;
+        }
+        pl.tv = best;
         pl.E = pl.tv->E; pl.NT = pl.tv->NT;
     } else {
         if (opt.S > 1 || opt.OB > 0) return LINREC_ERR_NOT_IMPLEMENTED;
@@ -401,7 +420,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     }
 
     Plan pl;
-    rc = make_plan(pl, kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt);
+    rc = make_plan(pl, kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, dev.max_smem_optin);
     if (rc != LINREC_OK) return rc;
 
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < workspace_need(pl))
@@ -417,7 +436,6 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     const void* fn = pl.tma ? reinterpret_cast<const void*>(pl.tv->fn[di][bwd][asc])
                             : reinterpret_cast<const void*>(pl.gv->fn[di][bwd][asc]);
     const size_t smem = pl.tma ? pl.tv->smem[di][bwd] : 0;
-    if (smem > (size_t)dev.max_smem_optin) return LINREC_ERR_NOT_IMPLEMENTED;
     int occ = 0;
     rc = occupancy(fn, pl.NT, smem, occ);
     if (rc != LINREC_OK) return rc;
@@ -521,7 +539,10 @@ int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, con
         if (o2.memcode < 0) o2.memcode = 1;
         static const double dummy_align[2] = {0, 0};
         const void* ptrs[1] = {reinterpret_cast<const void*>((reinterpret_cast<uintptr_t>(dummy_align) + 15) & ~(uintptr_t)15)};
-        rc = make_plan(pl, LINREC_KIND_PIPE, bwd, dtype, 1024, 1 << 20, 1 << 20, ptrs, 0, o2);
+        DeviceInfo dev;
+        rc = device_info(dev);
+        if (rc != LINREC_OK) return rc;
+        rc = make_plan(pl, LINREC_KIND_PIPE, bwd, dtype, 1024, 1 << 20, 1 << 20, ptrs, 0, o2, dev.max_smem_optin);
         if (rc != LINREC_OK) return rc;
         if (pl.tma) {
             fn = reinterpret_cast<const void*>(pl.tv->fn[di][bwd][1]);

@@ -31,12 +31,15 @@ constexpr int kHeaderBytes = 256;            // [0] ticket counter, [1] status w
 constexpr uint32_t kStatusLookbackTimeout = 1u;
 constexpr uint32_t kStatusCopyTimeout = 2u;
 
-// One look-back descriptor per chained tile (32 bytes = one DRAM sector).
-struct __align__(32) TileDesc {
-    float2 agg;        // (Y, P) of the tile alone               valid once status >= 1
-    float2 inc;        // (Y, P) of the row up to and including   valid once status == 2
-    uint32_t status;   // 0 nothing, 1 aggregate, 2 inclusive
-    uint32_t pad[3];
+// One look-back descriptor per chained tile: 16 bytes that are always read and written with ONE
+// 128-bit access, so that a reader sees the status together with the value it belongs to.
+//   status 0  nothing yet
+//   status 1  (y, p) is the aggregate of the tile alone
+//   status 2  (y, p) is the inclusive value of the row up to and including the tile
+struct __align__(16) TileDesc {
+    float y, p;
+    uint32_t status;
+    uint32_t pad;
 };
 
 // ---- the associative operator -------------------------------------------------------------------
@@ -265,17 +268,26 @@ __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geomet
         float yraw[E];
         load_run<ST, E>(b_y, g.t, yraw);
         const int lo = a - 1, hi = a + E;
+        // The neighbour just outside the run is the adjacent thread's edge element: it comes over a
+        // warp shuffle (lane stride of a blocked run would make a direct shared read a 4-way bank
+        // conflict); only the lane at the warp's edge reads shared memory.
+        const bool lo_ok = g.lo_in_tile;
+        const bool hi_ok = g.hi_in_tile && hi < valid;
         if (ASC) {   // predecessor = slot below, successor = slot above
-            const float c_pred = g.lo_in_tile ? read_slot<ST>(b_c, lo) : pred_c_outside;
-            const float y_succ = (g.hi_in_tile && hi < valid) ? read_slot<ST>(b_y, hi) : succ_y_outside;
+            const float c_from_below = __shfl_up_sync(0xffffffffu, craw[E - 1], 1);
+            const float y_from_above = __shfl_down_sync(0xffffffffu, yraw[0], 1);
+            const float c_pred = !lo_ok ? pred_c_outside : (g.lane > 0 ? c_from_below : read_slot<ST>(b_c, lo));
+            const float y_succ = !hi_ok ? succ_y_outside : (g.lane < 31 ? y_from_above : read_slot<ST>(b_y, hi));
 #pragma unroll
             for (int j = 0; j < E; ++j) {
                 op.c[j] = (j == 0) ? c_pred : craw[j - 1];
                 op.ysh[j] = (j == E - 1) ? y_succ : yraw[j + 1];
             }
         } else {     // predecessor = slot above, successor = slot below
-            const float c_pred = (g.hi_in_tile && hi < valid) ? read_slot<ST>(b_c, hi) : pred_c_outside;
-            const float y_succ = g.lo_in_tile ? read_slot<ST>(b_y, lo) : succ_y_outside;
+            const float c_from_above = __shfl_down_sync(0xffffffffu, craw[0], 1);
+            const float y_from_below = __shfl_up_sync(0xffffffffu, yraw[E - 1], 1);
+            const float c_pred = !hi_ok ? pred_c_outside : (g.lane < 31 ? c_from_above : read_slot<ST>(b_c, hi));
+            const float y_succ = !lo_ok ? succ_y_outside : (g.lane > 0 ? y_from_below : read_slot<ST>(b_y, lo));
 #pragma unroll
             for (int j = 0; j < E; ++j) {
                 op.c[j] = (j == E - 1) ? c_pred : craw[j + 1];
@@ -336,10 +348,18 @@ __device__ __forceinline__ ThreadScan scan_thread_and_warp(const Operands<E, BWD
 }
 
 // Phase 2a (after a block barrier): what the earlier warps contribute to this thread's row.
+// All warp aggregates are read up front (independent broadcast loads) and folded under a
+// predicate, so the dependent chain is NW fused multiply-adds and not NW shared-memory round trips.
+template <int NW>
 __device__ __forceinline__ Pair cross_warp_prefix(const Geometry& g, const Pair* wagg)
 {
+    Pair a[NW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) a[w] = wagg[w];
     Pair wp = pair_identity();
-    for (int w = g.start_warp; w < g.ws; ++w) wp = combine(wp, wagg[w]);
+#pragma unroll
+    for (int w = 0; w < NW - 1; ++w)
+        if (w >= g.start_warp && w < g.ws) wp = combine(wp, a[w]);
     return wp;
 }
 
@@ -357,6 +377,27 @@ __device__ __forceinline__ Pair warp_reduce_far_to_near(Pair v, int lane)
     return v;
 }
 
+// Descriptor access: one 128-bit relaxed load / store at GPU scope.
+__device__ __forceinline__ uint4 desc_load(const TileDesc* d)
+{
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(d)
+                 : "memory");
+    return v;
+}
+
+// Publishes a tile's aggregate (status 1) or inclusive value (status 2); one lane calls this.
+__device__ __forceinline__ void publish(TileDesc* d, Pair v, uint32_t status)
+{
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(d), "r"(__float_as_uint(v.y)),
+                 "r"(__float_as_uint(v.p)), "r"(status), "r"(0u)
+                 : "memory");
+}
+
+__device__ __forceinline__ Pair desc_pair(const uint4& v) { return Pair{__uint_as_float(v.x), __uint_as_float(v.y)}; }
+
 // Phase 2b, chain mode, run by ONE warp: decoupled look-back over the predecessor tiles of the
 // same row.  Tile (row r, scan piece q) has ticket q*numseq + r, so its predecessor is `numseq`
 // tickets back.  Returns (on every lane) the exclusive prefix of this tile.  Each poll is bounded
@@ -372,22 +413,22 @@ __device__ __forceinline__ Pair lookback(const ScanParams& p, long long ticket, 
         uint32_t st = 2u;
         if (pq >= 0) {
             const TileDesc* d = p.desc + (ticket - (long long)(j0 + lane) * p.numseq);
-            st = ptx::ld_acquire_u32(&d->status);
-            if (st == 0u) {
+            uint4 w = desc_load(d);
+            if (w.z == 0u) {
                 const long long t0 = clock64();
                 unsigned ns = 32;
-                while ((st = ptx::ld_acquire_u32(&d->status)) == 0u) {
+                while ((w = desc_load(d)).z == 0u) {
                     if (clock64() - t0 > p.wait_budget) break;
                     __nanosleep(ns);
                     if (ns < 1024) ns <<= 1;
                 }
             }
+            st = w.z;
             if (st == 0u) {
                 atomicOr(p.header + 1, kStatusLookbackTimeout);
                 st = 2u;   // give up: pretend an inclusive identity so that the walk ends
             } else {
-                const float2 f = ptx::ld_relaxed_f32x2(st == 2u ? &d->inc : &d->agg);
-                v = Pair{f.x, f.y};
+                v = desc_pair(w);
             }
         }
         const uint32_t ball = __ballot_sync(0xffffffffu, st == 2u);
@@ -402,13 +443,6 @@ __device__ __forceinline__ Pair lookback(const ScanParams& p, long long ticket, 
         j0 += 32;
     }
     return acc;
-}
-
-// Publishes a tile's aggregate or inclusive value (one lane calls this).
-__device__ __forceinline__ void publish(TileDesc* d, Pair v, bool inclusive)
-{
-    ptx::st_relaxed_f32x2(inclusive ? &d->inc : &d->agg, make_float2(v.y, v.p));
-    ptx::st_release_u32(&d->status, inclusive ? 2u : 1u);
 }
 
 // Phase 3: rerun the recurrence through the thread's slots from the true carry-in, which makes

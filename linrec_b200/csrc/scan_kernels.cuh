@@ -44,46 +44,81 @@ __device__ __forceinline__ TileCoord decode_ticket(const ScanParams& p, uint32_t
     return tc;
 }
 
+// Shared-memory words of the chain logic.
+struct ChainShared {
+    Pair tprefix;   // exclusive prefix of the current tile
+    int early;      // 1: tprefix was known before the operands were even scanned
+};
+
 // Everything that happens between "operands are in registers" and "results are in registers",
-// shared by both tile kernels.  `sync_a` has to be a block barrier after which the operand
-// buffers and wagg may be reused; it is passed in because the pipelined kernel refills its ring
-// at exactly that point.
+// shared by both tile kernels.  `after_read` has to contain a block barrier after which the
+// operand buffers and wagg may be reused; it is passed in because the pipelined kernel refills
+// its ring at exactly that point.
+//
+// Chain mode.  The scan-last warp links the tile to its row.  Fast path: the predecessor's
+// descriptor was fetched ahead of time (`probe`, loaded one iteration earlier while the previous
+// tile was still being worked on) and already holds an inclusive value; then the exclusive prefix
+// is in shared memory before the barrier and nobody waits for the look-back.  Slow path: publish
+// the aggregate, walk back over the predecessors, one more barrier.  Either way the warp then
+// fetches the descriptor that the NEXT tile (`next_tk`) will want.
 template <int E, int NT, bool BWD, bool ASC, typename AfterRead>
 __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g,
                                           const Operands<E, BWD>& op, const TileCoord& tc,
-                                          uint32_t tk, Pair* wagg, Pair* tprefix,
-                                          float (&o0)[E], float (&o1)[BWD ? E : 1],
+                                          uint32_t tk, uint32_t next_tk, uint4& probe, Pair* wagg,
+                                          ChainShared* cs, float (&o0)[E], float (&o1)[BWD ? E : 1],
                                           AfterRead&& after_read)
 {
     constexpr int NW = NT / 32;
-    const ThreadScan ts = scan_thread_and_warp<E, NT, BWD, ASC>(op, g, wagg);
-    if (!after_read()) return;   // contains the block barrier; false = the CTA is bailing out
-    const Pair wp = cross_warp_prefix(g, wagg);
-    Pair pre = pair_identity();
-    if (p.chain) {
-        if (g.ws == NW - 1) {   // the scan-last warp links the tile to its predecessors
-            const Pair bagg = combine(wp, wagg[NW - 1]);
-            Pair tp = pair_identity();
-            TileDesc* d = p.desc + tk;
-            const bool last_piece = (tc.q == p.chunks_per_row - 1);
-            if (tc.q == 0) {
-                if (g.lane == 0 && !last_piece) publish(d, bagg, true);
-            } else {
-                if (g.lane == 0 && !last_piece) publish(d, bagg, false);
-                tp = lookback(p, (long long)tk, tc.q, g.lane);
-                if (g.lane == 0 && !last_piece) publish(d, combine(tp, bagg), true);
-            }
-            if (g.lane == 0) {
-                *tprefix = tp;
-                if (last_piece && p.carry_out) {
-                    const Pair tot = combine(tp, bagg);
-                    p.carry_out[2 * tc.row] = tot.p;
-                    p.carry_out[2 * tc.row + 1] = tot.y;
-                }
+    const bool linker = p.chain && (g.ws == NW - 1);
+    if (linker && g.lane == 0) {
+        int early = 0;
+        Pair tp = pair_identity();
+        if (tc.q == 0) {
+            early = 1;
+        } else {
+            if (probe.z != 2u) probe = desc_load(p.desc + ((long long)tk - p.numseq));
+            if (probe.z == 2u) {
+                tp = desc_pair(probe);
+                early = 1;
             }
         }
-        __syncthreads();
-        pre = *tprefix;
+        cs->tprefix = tp;
+        cs->early = early;
+    }
+    const ThreadScan ts = scan_thread_and_warp<E, NT, BWD, ASC>(op, g, wagg);
+    if (!after_read()) return;   // contains the block barrier; false = the CTA is bailing out
+    const Pair wp = cross_warp_prefix<NW>(g, wagg);
+    Pair pre = pair_identity();
+    if (p.chain) {
+        const bool early = cs->early != 0;
+        if (linker) {
+            const Pair bagg = combine(wp, wagg[NW - 1]);
+            TileDesc* d = p.desc + tk;
+            const bool last_piece = (tc.q == p.chunks_per_row - 1);
+            Pair tp;
+            if (early) {
+                tp = cs->tprefix;
+                if (g.lane == 0 && !last_piece) publish(d, combine(tp, bagg), 2u);
+            } else {
+                if (g.lane == 0 && !last_piece) publish(d, bagg, 1u);
+                tp = lookback(p, (long long)tk, tc.q, g.lane);
+                if (g.lane == 0) {
+                    if (!last_piece) publish(d, combine(tp, bagg), 2u);
+                    cs->tprefix = tp;
+                }
+            }
+            if (g.lane == 0 && last_piece && p.carry_out) {
+                const Pair tot = combine(tp, bagg);
+                p.carry_out[2 * tc.row] = tot.p;
+                p.carry_out[2 * tc.row + 1] = tot.y;
+            }
+            // fetch ahead what the next tile of this CTA will ask for
+            probe = make_uint4(0u, 0u, 0u, 0u);
+            if (next_tk < (uint32_t)p.ntiles && next_tk >= (uint32_t)p.numseq)
+                probe = desc_load(p.desc + ((long long)next_tk - p.numseq));
+        }
+        if (!early) __syncthreads();
+        pre = cs->tprefix;
     }
     if (g.need_wp) pre = combine(pre, wp);
     pre = combine(pre, ts.excl);
@@ -112,7 +147,7 @@ struct TmaLayout {
 };
 
 template <typename ST, int E, int NT, int S, int OB, bool BWD, bool ASC>
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, (E <= 8 && NT >= 512) ? 2 : 1)
 linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_constant__ CUtensorMap tm_c,
                   const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_out0,
                   const __grid_constant__ CUtensorMap tm_out1, const ScanParams p)
@@ -133,7 +168,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     __shared__ uint32_t tile_of_stage[S];
     __shared__ uint32_t halo[S][2];      // backward, chain mode: raw 4-byte words around the tile
     __shared__ Pair wagg[NW];
-    __shared__ Pair tprefix;
+    __shared__ ChainShared chain_sh;
     __shared__ int abort_flag;
 
     const Geometry g = make_geometry<E, NT, ASC>(p);
@@ -198,11 +233,14 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     }
     __syncthreads();
 
+    uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // look-ahead copy of the predecessor's descriptor
     uint32_t it = 0;
     for (;; ++it) {
         const int s = (int)(it % S);
         const uint32_t tk = tile_of_stage[s];
         if (tk >= ntiles) break;
+        // with a ring of one slot the next ticket is not known yet at this point
+        const uint32_t next_tk = S > 1 ? tile_of_stage[(it + 1) % S] : 0xffffffffu;
         const TileCoord tc = decode_ticket<T, ASC>(p, tk);
 
         if (!ptx::mbar_wait_bounded(&full[s], (it / S) & 1u, p.wait_budget)) {
@@ -233,7 +271,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
                                                  tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         bool alive = true;
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, wagg, &tprefix, o0, o1, [&]() -> bool {
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             // the output buffer about to be reused must have been drained by its bulk store
             if (tid == 0) ptx::tma_wait_group_read<OB - 1>();
             __syncthreads();
@@ -289,7 +327,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     __shared__ __align__(1024) ST buf_y[BWD ? T : 8];
     __shared__ float halo[2];
     __shared__ Pair wagg[NW];
-    __shared__ Pair tprefix;
+    __shared__ ChainShared chain_sh;
     __shared__ uint32_t ticket_s;
 
     const Geometry g = make_geometry<E, NT, ASC>(p);
@@ -341,7 +379,8 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
                                                   (BWD && p.chain) ? halo[0] : 0.0f,
                                                   (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, wagg, &tprefix, o0, o1, [&]() -> bool {
+        uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // no look-ahead here: the linking warp probes when it needs to
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             __syncthreads();
             return true;
         });

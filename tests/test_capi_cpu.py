@@ -45,7 +45,7 @@ def test_workspace_size_rules():
     ws = _capi.lib.linrec_b200_workspace_size
     assert ws(0, 0, 0) == 256 and ws(10, 100, 0) == 256        # short rows: header only
     big = ws(8, 1 << 20, 0)
-    assert big % 256 == 0 and big >= 256 + 8 * ((1 << 20) // 2048) * 32
+    assert big % 256 == 0 and big >= 256 + 8 * ((1 << 20) // 2048) * 16
 
 
 def test_bad_arguments_are_refused_before_any_launch():

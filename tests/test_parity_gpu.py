@@ -57,6 +57,11 @@ def test_golden(golden, name, rev, family):
     dev = torch.device("cuda:0")
     x, c, dy = (torch.from_numpy(golden[f"{name}/{k}"]).to(dev) for k in ("x", "c", "dy"))
     tag = f"{name}/rev{int(rev)}"
+    if family == "tile" and x.shape[-1] > 2048 and x.shape[-1] % 32 != 0:
+        # the tile family keeps a whole row in one tile; 2048 is the any-alignment kernels' tile
+        with pytest.raises(RuntimeError, match="does not fit one tile"):
+            lb._C.linrec_tile_fwd(inputs=x, coeffs=c, reverse=rev)
+        return
     y = getattr(lb._C, f"linrec_{family}_fwd")(inputs=x, coeffs=c, reverse=rev)
     np.testing.assert_allclose(y.cpu().numpy(), golden[f"{tag}/y"], rtol=RTOL, atol=ATOL)
     yg = torch.from_numpy(golden[f"{tag}/y"]).to(dev)
@@ -126,6 +131,12 @@ def test_all_variants(shape, rev):
     x, c, dy = _data(shape, clo=0.5, chi=1.0)
     assert len(configs) >= 4
     for cfg in configs:
+        E, NT, S, OB, memcode = cfg
+        if memcode == 1 and E * NT * 4 * (3 * S + 2 * OB) + 1024 > 227 * 1024:
+            # the backward pass of this variant needs more shared memory than an SM has
+            with pytest.raises(NotImplementedError):
+                _check_fwd_bwd(x, c, dy, rev, **dict(zip(names, cfg)))
+            continue
         _check_fwd_bwd(x, c, dy, rev, **dict(zip(names, cfg)))
 
 
