@@ -41,6 +41,7 @@ extern "C" {
 #define LINREC_ERR_TIMEOUT         (-5)  /* a bounded device-side wait gave up (see _status)    */
 #define LINREC_ERR_TOO_LONG        (-6)  /* tile-only call and the row does not fit one tile    */
 #define LINREC_ERR_UNALIGNED       (-7)  /* bulk-copy path forced on pointers/strides it cannot take */
+#define LINREC_ERR_SCRATCH_LIMIT   (-8)  /* problem needs more scratch than the built-in buffer has  */
 
 /* ---- element storage types (arithmetic is always fp32) -------------------------------------- */
 #define LINREC_DTYPE_F32   0
@@ -126,6 +127,35 @@ LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, floa
 LINREC_API int linrec_b200_fixup(void* y, const void* c, const float* carries,
                                  int rank, int world, int64_t numseq, int64_t seqlen,
                                  int64_t row_stride, int reverse, int dtype, void* stream);
+
+/* Forward scan for callers that cannot give the library any scratch memory.
+ *
+ * linrec_b200_fwd needs a caller-provided workspace, which normally means the caller allocates
+ * device memory.  Some hosts cannot: a program that binds only this C function from another
+ * runtime and owns no device allocator to get a workspace from; a service whose device memory is
+ * handed out in full to another pool at start-up; a latency-critical loop in which cudaMalloc's
+ * device-wide synchronisation is not acceptable.  For them this entry point does the same forward
+ * scan (LINREC_KIND_PIPE, selector defaults, same arguments otherwise) but keeps its ticket counter,
+ * status word and look-back descriptors in a buffer that is compiled into the library:
+ * LINREC_STATIC_SCRATCH_BYTES (1 MiB) of device memory per GPU that loads the library, held until
+ * the process exits.  It never calls cudaMalloc, cudaFree or any allocating routine.
+ *
+ * Limit: the scratch a problem needs must fit the built-in buffer.  Rows that fit one tile need
+ * 256 bytes whatever their number; rows longer than a tile need 16 more bytes per tile.  A tile is
+ * 8192 elements when the rows are 16-byte aligned and a multiple of 128 bytes long, else 2048.  So
+ * at most 65,520 tiles of long rows (about 5.3e8 fp32 elements in the aligned case) can be scanned
+ * by one call; larger problems return LINREC_ERR_SCRATCH_LIMIT and launch nothing.
+ *
+ * The first call on each device looks up the buffer's device address (once per device, with that
+ * device current); make that first call outside any stream capture.  All calls on a device share
+ * the one buffer: each call re-initialises the words it needs at its start, the buffer otherwise
+ * keeps what the previous call left, and two calls that overlap on the GPU (different streams,
+ * different host threads) race on it -- serialise them, or use linrec_b200_fwd with separate
+ * workspaces.  This function has no counterpart in the reference. */
+#define LINREC_STATIC_SCRATCH_BYTES (1u << 20)
+LINREC_API int linrec_b200_fwd_static(const void* x, const void* c, void* y,
+                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
+                                      int reverse, int dtype, void* stream);
 
 /* Number of kernels this library has launched in this process (all threads). */
 LINREC_API uint64_t linrec_b200_launch_count(void);

@@ -613,6 +613,63 @@ int linrec_b200_fixup(void* y, const void* c, const float* carries, int rank, in
     return LINREC_ERR_NOT_IMPLEMENTED;
 }
 
+// ---- forward scan on a built-in scratch buffer ----------------------------------------------------
+// The buffer lives in the library's device image, so no call ever has to allocate.  In host code
+// the name below is only a handle for the runtime: the device address has to be asked for with
+// cudaGetSymbolAddress, once per device and with that device current, and it is that address --
+// never the host-side symbol -- that goes to the kernels.
+static __device__ __align__(256) unsigned char g_static_scratch[LINREC_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};   // device address of g_static_scratch, per device ordinal
+
+int static_scratch_address(void** out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return LINREC_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return LINREC_ERR_CUDA;
+        }
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return LINREC_OK;
+}
+}  // namespace
+
+int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen,
+                           int64_t row_stride, int reverse, int dtype, void* stream)
+{
+    const void* ptrs[3] = {x, c, y};
+    int rc = check_common(ptrs, 3, numseq, seqlen, row_stride, dtype);
+    if (rc != LINREC_OK) return rc;
+    if (numseq == 0 || seqlen == 0) return LINREC_OK;
+    // how much scratch this very problem needs, with the same plan the launch below will make
+    DeviceInfo dev;
+    rc = device_info(dev);
+    if (rc != LINREC_OK) return rc;
+    Plan pl;
+    const void* all[5] = {x, c, y, x, y};
+    rc = make_plan(pl, LINREC_KIND_PIPE, false, dtype, numseq, seqlen, row_stride, all, 5, Options{}, dev.max_smem_optin);
+    if (rc != LINREC_OK) return rc;
+    if (workspace_need(pl) > (size_t)LINREC_STATIC_SCRATCH_BYTES) return LINREC_ERR_SCRATCH_LIMIT;
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc != LINREC_OK) return rc;
+    // launch_scan rewrites the header words and zeroes the descriptors this call uses, so whatever
+    // an earlier call left in the buffer does not matter
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, numseq, seqlen, row_stride,
+                       reverse, dtype, nullptr, scratch, (size_t)LINREC_STATIC_SCRATCH_BYTES, stream);
+}
+
 uint64_t linrec_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* linrec_b200_strerror(int code)
@@ -626,6 +683,7 @@ const char* linrec_b200_strerror(int code)
         case LINREC_ERR_TIMEOUT: return "a bounded device-side wait gave up";
         case LINREC_ERR_TOO_LONG: return "row does not fit one tile";
         case LINREC_ERR_UNALIGNED: return "bulk-copy path needs 16-byte aligned rows whose length is a multiple of 128 bytes";
+        case LINREC_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the 1 MiB built into the library (use linrec_b200_fwd with a workspace)";
         default: return "unknown status";
     }
 }
