@@ -110,23 +110,37 @@ LINREC_API int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts
 LINREC_API int linrec_b200_config_names(const char** names, int cap);
 LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
 
-/* Sequence sharding (one row split over several GPUs).  No counterpart in the reference, which
- * is single-device.
- *   linrec_b200_fwd_carry  : local forward scan of this shard with zero carry-in; also writes
- *                            per row the pair (P = product of c over the shard, Y = last local y
- *                            in scan order) to carry_out[2*r], carry_out[2*r+1] (fp32).
- *   linrec_b200_fixup      : given all shards' pairs gathered in rank order
- *                            (carries[(rank*numseq + r)*2 + {0,1}]), folds the pairs of the
- *                            shards that precede `rank` in scan order and adds
- *                            Y_in * prod(c) to this shard's y in place.  The walk along a row
- *                            stops as soon as the running product is exactly zero. */
-LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* carry_out,
+/* Sequence sharding: one row split over `nshards` GPUs, shard s owning the columns
+ * [s*seqlen, (s+1)*seqlen) of every row (`seqlen` is the SHARD's length here).  No counterpart in
+ * the reference, which is single-device.  Per rank:
+ *   1. *_carry   local scan of the shard with zero carry-in; also writes one fp32 record per row:
+ *                forward  records[2r+{0,1}]   = (P, Y): product of c over the shard, last local y;
+ *                backward records[4r+{0..3}]  = (P, Y, c at the shard's scan-last element,
+ *                                                y at the shard's scan-first element).
+ *   2. the caller gathers the records of all shards in shard order into
+ *      gathered[(s*numseq + r)*rec + k]   (one all-gather; rec = 2 forward, 4 backward);
+ *   3. *_fixup   folds the records of the shards that come earlier in scan order and adds
+ *                carry * running product of the coefficients to this shard's results in place.  The
+ *                walk along a row stops once the carried value has underflowed to exactly zero.
+ * `reverse` is the flag of the forward pass in all four. */
+LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
-                                     int reverse, int dtype, const linrec_opts* opts,
+                                     int reverse, int dtype, int shard, int nshards,
+                                     const linrec_opts* opts,
                                      void* workspace, size_t workspace_bytes, void* stream);
-LINREC_API int linrec_b200_fixup(void* y, const void* c, const float* carries,
-                                 int rank, int world, int64_t numseq, int64_t seqlen,
-                                 int64_t row_stride, int reverse, int dtype, void* stream);
+LINREC_API int linrec_b200_fwd_fixup(void* y, const void* c, const float* gathered,
+                                     int64_t numseq, int64_t seqlen, int64_t row_stride,
+                                     int reverse, int dtype, int shard, int nshards, void* stream);
+LINREC_API int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx, void* dc,
+                                     float* records,
+                                     int64_t numseq, int64_t seqlen, int64_t row_stride,
+                                     int reverse, int dtype, int shard, int nshards,
+                                     const linrec_opts* opts,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+LINREC_API int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y,
+                                     const float* gathered,
+                                     int64_t numseq, int64_t seqlen, int64_t row_stride,
+                                     int reverse, int dtype, int shard, int nshards, void* stream);
 
 /* Forward scan for callers that cannot give the library any scratch memory.
  *

@@ -61,10 +61,14 @@ def _load() -> ctypes.CDLL:
     lib.linrec_b200_config_names.restype = i32
     lib.linrec_b200_config_list.argtypes = [ctypes.POINTER(i32), i32]
     lib.linrec_b200_config_list.restype = i32
-    lib.linrec_b200_fwd_carry.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32, i32, po, vp, sz, vp]
+    lib.linrec_b200_fwd_carry.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, po, vp, sz, vp]
     lib.linrec_b200_fwd_carry.restype = i32
-    lib.linrec_b200_fixup.argtypes = [vp, vp, vp, i32, i32, i64, i64, i64, i32, i32, vp]
-    lib.linrec_b200_fixup.restype = i32
+    lib.linrec_b200_fwd_fixup.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
+    lib.linrec_b200_fwd_fixup.restype = i32
+    lib.linrec_b200_bwd_carry.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, po, vp, sz, vp]
+    lib.linrec_b200_bwd_carry.restype = i32
+    lib.linrec_b200_bwd_fixup.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
+    lib.linrec_b200_bwd_fixup.restype = i32
     lib.linrec_b200_launch_count.argtypes = []
     lib.linrec_b200_launch_count.restype = ctypes.c_uint64
     lib.linrec_b200_strerror.argtypes = [i32]

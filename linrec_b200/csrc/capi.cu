@@ -17,6 +17,7 @@
 
 #include "../../include/linrec_b200.h"
 #include "scan_kernels.cuh"
+#include "shard_kernels.cuh"
 
 namespace {
 
@@ -376,7 +377,7 @@ int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seq
 
 // The one launcher behind forward, backward and the carry-emitting forward.
 int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
-                float* carry_out, int open_start, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                float* carry_out, int carry_stride, int open_start, int64_t numseq, int64_t seqlen, int64_t row_stride,
                 int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
                 void* stream_)
 {
@@ -398,6 +399,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.in0 = in0; p.c = c; p.yin = yin; p.out0 = out0; p.out1 = out1;
     p.numseq = numseq; p.seqlen = seqlen; p.row_stride = row_stride;
     p.carry_out = carry_out;
+    p.carry_stride = carry_stride;
     p.open_start = open_start;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
@@ -472,6 +474,53 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
 
 }  // namespace
 
+// ---- sequence sharding -------------------------------------------------------------------------------
+namespace {
+// Does shard `shard` hold the element the scan starts from?
+inline bool holds_scan_start(bool asc, int shard, int nshards) { return asc ? shard == 0 : shard == nshards - 1; }
+
+template <typename ST>
+int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream_t stream, int sm_count)
+{
+    constexpr int NT = 256;
+    long long grid = fp.numseq < (long long)sm_count * 8 ? fp.numseq : (long long)sm_count * 8;
+    if (!bwd) {
+        if (asc) linrec::linrec_fixup_kernel<ST, NT, false, true><<<(unsigned)grid, NT, 0, stream>>>(fp);
+        else     linrec::linrec_fixup_kernel<ST, NT, false, false><<<(unsigned)grid, NT, 0, stream>>>(fp);
+    } else {
+        if (asc) linrec::linrec_fixup_kernel<ST, NT, true, true><<<(unsigned)grid, NT, 0, stream>>>(fp);
+        else     linrec::linrec_fixup_kernel<ST, NT, true, false><<<(unsigned)grid, NT, 0, stream>>>(fp);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+}
+
+int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
+                 int64_t numseq, int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
+                 void* stream_)
+{
+    const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
+    if (!carries && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    int rc = check_common(ptrs, 2, numseq, seqlen, row_stride, dtype);
+    if (rc != LINREC_OK) return rc;
+    if (bwd && (!out1 || !yin) && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
+    if (numseq == 0 || seqlen == 0) return LINREC_OK;
+    const bool asc = bwd ? (reverse != 0) : (reverse == 0);
+    if (holds_scan_start(asc, shard, nshards) && !bwd) return LINREC_OK;   // nothing enters this shard
+    DeviceInfo dev;
+    rc = device_info(dev);
+    if (rc != LINREC_OK) return rc;
+    linrec::FixupParams fp{};
+    fp.out0 = out0; fp.out1 = out1; fp.c = c; fp.yin = yin; fp.carries = carries;
+    fp.numseq = numseq; fp.seqlen = seqlen; fp.row_stride = row_stride;
+    fp.shard = shard; fp.nshards = nshards; fp.rec = bwd ? 4 : 2;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    return dtype == LINREC_DTYPE_F32 ? launch_fixup_t<float>(bwd, asc, fp, stream, dev.sm_count)
+                                     : launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count);
+}
+}  // namespace
+
 // =================================================================================================
 //  C ABI
 // =================================================================================================
@@ -495,7 +544,7 @@ int linrec_b200_fwd(int kind, const void* x, const void* c, void* y, int64_t num
                     int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
                     size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, numseq, seqlen, row_stride, reverse,
+    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, numseq, seqlen, row_stride, reverse,
                        dtype, opts, workspace, workspace_bytes, stream);
 }
 
@@ -503,7 +552,7 @@ int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y, void
                     int64_t seqlen, int64_t row_stride, int reverse, int dtype, const linrec_opts* opts,
                     void* workspace, size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype, opts,
+    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, 0, numseq, seqlen, row_stride, reverse, dtype, opts,
                        workspace, workspace_bytes, stream);
 }
 
@@ -596,21 +645,54 @@ int linrec_b200_config_list(int* values, int cap_rows)
     return row;
 }
 
-int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* carry_out, int64_t numseq, int64_t seqlen,
-                          int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
-                          size_t workspace_bytes, void* stream)
+int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records, int64_t numseq, int64_t seqlen,
+                          int64_t row_stride, int reverse, int dtype, int shard, int nshards, const linrec_opts* opts,
+                          void* workspace, size_t workspace_bytes, void* stream)
 {
-    if (!carry_out && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, carry_out, 1, numseq, seqlen, row_stride,
+    if (!records && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
+    const int open = holds_scan_start(reverse == 0, shard, nshards) ? 0 : 1;
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, records, 2, open, numseq, seqlen, row_stride,
                        reverse, dtype, opts, workspace, workspace_bytes, stream);
 }
 
-int linrec_b200_fixup(void* y, const void* c, const float* carries, int rank, int world, int64_t numseq,
-                      int64_t seqlen, int64_t row_stride, int reverse, int dtype, void* stream)
+int linrec_b200_fwd_fixup(void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
+                          int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream)
 {
-    (void)y; (void)c; (void)carries; (void)rank; (void)world; (void)numseq; (void)seqlen; (void)row_stride;
-    (void)reverse; (void)dtype; (void)stream;
-    return LINREC_ERR_NOT_IMPLEMENTED;
+    return launch_fixup(false, y, nullptr, c, nullptr, records, numseq, seqlen, row_stride, reverse, dtype, shard,
+                        nshards, stream);
+}
+
+int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx, void* dc, float* records,
+                          int64_t numseq, int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard,
+                          int nshards, const linrec_opts* opts, void* workspace, size_t workspace_bytes, void* stream_)
+{
+    if (!records && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
+    const bool asc = reverse != 0;   // the gradient scan runs against the forward direction
+    const int open = holds_scan_start(asc, shard, nshards) ? 0 : 1;
+    int rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, records, 4, open, numseq, seqlen, row_stride, reverse,
+                         dtype, opts, workspace, workspace_bytes, stream_);
+    if (rc != LINREC_OK || numseq == 0 || seqlen == 0) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const unsigned blocks = (unsigned)ceil_div(numseq, 128);
+    if (dtype == LINREC_DTYPE_F32) {
+        if (asc) linrec::linrec_edges_kernel<float, true><<<blocks, 128, 0, stream>>>((const float*)c, (const float*)y, records, numseq, seqlen, row_stride);
+        else     linrec::linrec_edges_kernel<float, false><<<blocks, 128, 0, stream>>>((const float*)c, (const float*)y, records, numseq, seqlen, row_stride);
+    } else {
+        using B = __nv_bfloat16;
+        if (asc) linrec::linrec_edges_kernel<B, true><<<blocks, 128, 0, stream>>>((const B*)c, (const B*)y, records, numseq, seqlen, row_stride);
+        else     linrec::linrec_edges_kernel<B, false><<<blocks, 128, 0, stream>>>((const B*)c, (const B*)y, records, numseq, seqlen, row_stride);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+}
+
+int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y, const float* records, int64_t numseq,
+                          int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
+                          void* stream)
+{
+    return launch_fixup(true, dx, dc, c, y, records, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
 
 // ---- forward scan on a built-in scratch buffer ----------------------------------------------------
@@ -666,7 +748,7 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
     if (rc != LINREC_OK) return rc;
     // launch_scan rewrites the header words and zeroes the descriptors this call uses, so whatever
     // an earlier call left in the buffer does not matter
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, numseq, seqlen, row_stride,
                        reverse, dtype, nullptr, scratch, (size_t)LINREC_STATIC_SCRATCH_BYTES, stream);
 }
 

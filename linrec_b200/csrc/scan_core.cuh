@@ -72,7 +72,9 @@ struct ScanParams {
     TileDesc* desc;      // chain mode: one descriptor per tile, zeroed before the launch
     long long wait_budget;  // clock ticks any device-side wait may last
     float* carry_out;    // optional: per row (P, Y) of the whole row, for sequence sharding
-    int open_start;      // 1: the rows continue an earlier shard, so their first coefficient counts
+    int carry_stride;    // floats between the records of consecutive rows in carry_out
+    int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
+                         //    coefficient that lies before the shard is taken as 1 (folded in later)
 };
 
 // ---- storage-type helpers -----------------------------------------------------------------------

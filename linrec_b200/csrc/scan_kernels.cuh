@@ -109,8 +109,8 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
             }
             if (g.lane == 0 && last_piece && p.carry_out) {
                 const Pair tot = combine(tp, bagg);
-                p.carry_out[2 * tc.row] = tot.p;
-                p.carry_out[2 * tc.row + 1] = tot.y;
+                p.carry_out[p.carry_stride * tc.row] = tot.p;
+                p.carry_out[p.carry_stride * tc.row + 1] = tot.y;
             }
             // fetch ahead what the next tile of this CTA will ask for
             probe = make_uint4(0u, 0u, 0u, 0u);
@@ -126,8 +126,8 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
         const long long row = tc.row + g.row_in_tile;
         if (row < p.numseq) {
             const Pair tot = combine(pre, ts.agg);
-            p.carry_out[2 * row] = tot.p;
-            p.carry_out[2 * row + 1] = tot.y;
+            p.carry_out[p.carry_stride * row] = tot.p;
+            p.carry_out[p.carry_stride * row + 1] = tot.y;
         }
     }
     apply_carry<E, BWD, ASC>(op, pre.y, o0, o1);
@@ -210,8 +210,9 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             const bool c_ok = ASC ? (lo >= 0) : (hi < p.seqlen);
             const bool y_ok = ASC ? (hi < p.seqlen) : (lo >= 0);
             // 4-byte copies from the 4-byte-aligned word that contains the element
+            // (a coefficient that lies before an open shard start is 1; both halves for 2-byte storage)
             if (c_ok) ptx::cp_async_4(&halo[s][0], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(csrc) & ~(uintptr_t)3));
-            else halo[s][0] = 0u;
+            else halo[s][0] = !p.open_start ? 0u : (sizeof(ST) == 4 ? 0x3f800000u : 0x3f803f80u);
             if (y_ok) ptx::cp_async_4(&halo[s][1], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ysrc) & ~(uintptr_t)3));
             else halo[s][1] = 0u;
             ptx::cp_async_mbar_arrive_noinc(&full[s]);
@@ -248,7 +249,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             abort_flag = 1;
         }
 
-        float pred_c = 0.0f, succ_y = 0.0f;
+        float pred_c = p.open_start ? 1.0f : 0.0f, succ_y = 0.0f;
         if (with_halo) {
             // the halo word holds the element in its low or high half for 2-byte storage
             const uint32_t wc = halo[s][0], wy = halo[s][1];
@@ -356,7 +357,11 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
             const long long off = row * p.row_stride + col;
             write_slot<ST>(buf_in0, i, ok ? Storage<ST>::to_float(gin0[off]) : 0.0f);
-            write_slot<ST>(buf_c, i, ok ? Storage<ST>::to_float(gc[off]) : 1.0f);
+            float cv = ok ? Storage<ST>::to_float(gc[off]) : 1.0f;
+            // the coefficient of a row's very first element has no effect (closed rows only); with
+            // padded rows that element need not be a thread's first slot, so it is cleared here
+            if (!BWD && !p.open_start && col == (ASC ? 0 : p.seqlen - 1)) cv = 0.0f;
+            write_slot<ST>(buf_c, i, cv);
             if (BWD) write_slot<ST>(buf_y, i, ok ? Storage<ST>::to_float(gy[off]) : 0.0f);
         }
         if (BWD && p.chain && tid < 2) {
@@ -364,7 +369,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             const long long rb = tc.row * p.row_stride;
             if (tid == 0) {   // coefficient at the scan predecessor of the piece
                 const long long ci = ASC ? lo : hi;
-                halo[0] = (ci >= 0 && ci < p.seqlen) ? Storage<ST>::to_float(gc[rb + ci]) : 0.0f;
+                halo[0] = (ci >= 0 && ci < p.seqlen) ? Storage<ST>::to_float(gc[rb + ci]) : (p.open_start ? 1.0f : 0.0f);
             } else {          // output at the scan successor of the piece
                 const long long yi = ASC ? hi : lo;
                 halo[1] = (yi >= 0 && yi < p.seqlen) ? Storage<ST>::to_float(gy[rb + yi]) : 0.0f;
@@ -376,7 +381,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, false>(op, g, buf_in0, buf_c, buf_y,
-                                                  (BWD && p.chain) ? halo[0] : 0.0f,
+                                                  (BWD && p.chain) ? halo[0] : (p.open_start ? 1.0f : 0.0f),
                                                   (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // no look-ahead here: the linking warp probes when it needs to

@@ -1,0 +1,151 @@
+"""Multi-GPU modes of the scan (one process per GPU, `torch.distributed`).
+
+The reference is single-device; both modes are additions, checked against the single-device result
+on the unsharded tensor.
+
+channel sharding   rows are independent: every rank scans its own rows with `linrec_b200.linrec`,
+                   no communication at all (`linrec_channel_sharded` is literally that call).
+sequence sharding  every rank holds the columns [rank*L, (rank+1)*L) of ALL rows.  Each rank scans
+                   its shard locally and emits one small record per row, the records are
+                   all-gathered once (NCCL over NVLink; 8 or 16 bytes per row and rank), and a fused
+                   fix-up kernel folds the records of the earlier shards and adds
+                   `carry * running product of c` to the local result, stopping along each row as
+                   soon as that correction has underflowed to exactly zero.
+
+`linrec_seq_sharded(x_shard, c_shard, reverse=False, group=None)` is differentiable; its backward
+does the same three steps with the gradient scan.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _capi
+from .ops import _DTYPES, _check_same, _row_layout, _workspace, linrec_pipe
+
+__all__ = ["linrec_channel_sharded", "linrec_seq_sharded", "seq_sharded_fwd", "seq_sharded_bwd"]
+
+
+def linrec_channel_sharded(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False) -> torch.Tensor:
+    """Rows sharded over ranks: the local scan is the whole job."""
+    return linrec_pipe(inputs, coeffs, reverse)
+
+
+class CudaShardKernels:
+    """The four C-ABI calls of sequence sharding on torch CUDA tensors."""
+
+    @staticmethod
+    def _prep(*ts):
+        _check_same(*ts)
+        ts = [t if _row_layout(t) is not None else t.contiguous() for t in ts]
+        lay = _row_layout(ts[0])
+        if any(_row_layout(t) != lay for t in ts):
+            ts = [t.contiguous() for t in ts]
+            lay = _row_layout(ts[0])
+        return ts, lay
+
+    @staticmethod
+    def _launch_env(ref, numseq, seqlen):
+        stream = torch.cuda.current_stream(ref.device).cuda_stream
+        dtype = _DTYPES[ref.dtype]
+        need = _capi.lib.linrec_b200_workspace_size(numseq, seqlen, dtype)
+        ws = _workspace(ref.device, stream, need)
+        return stream, dtype, ws
+
+    def fwd_carry(self, x, c, reverse, shard, nshards):
+        (x, c), (numseq, seqlen, stride) = self._prep(x, c)
+        y = torch.empty_like(x)
+        rec = torch.empty((numseq, 2), dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            stream, dtype, ws = self._launch_env(x, numseq, seqlen)
+            rc = _capi.lib.linrec_b200_fwd_carry(x.data_ptr(), c.data_ptr(), y.data_ptr(), rec.data_ptr(), numseq,
+                                                 seqlen, stride, int(bool(reverse)), dtype, shard, nshards, None,
+                                                 ws.data_ptr(), ws.numel(), stream)
+        _capi.raise_for(rc, "linrec_b200_fwd_carry")
+        return y, rec
+
+    def fwd_fixup(self, y, c, gathered, reverse, shard, nshards):
+        numseq, seqlen, stride = _row_layout(y)
+        with torch.cuda.device(y.device):
+            stream = torch.cuda.current_stream(y.device).cuda_stream
+            rc = _capi.lib.linrec_b200_fwd_fixup(y.data_ptr(), c.data_ptr(), gathered.data_ptr(), numseq, seqlen, stride,
+                                                 int(bool(reverse)), _DTYPES[y.dtype], shard, nshards, stream)
+        _capi.raise_for(rc, "linrec_b200_fwd_fixup")
+
+    def bwd_carry(self, dy, c, y, reverse, shard, nshards):
+        (dy, c, y), (numseq, seqlen, stride) = self._prep(dy, c, y)
+        dx, dc = torch.empty_like(dy), torch.empty_like(dy)
+        rec = torch.empty((numseq, 4), dtype=torch.float32, device=dy.device)
+        with torch.cuda.device(dy.device):
+            stream, dtype, ws = self._launch_env(dy, numseq, seqlen)
+            rc = _capi.lib.linrec_b200_bwd_carry(dy.data_ptr(), c.data_ptr(), y.data_ptr(), dx.data_ptr(), dc.data_ptr(),
+                                                 rec.data_ptr(), numseq, seqlen, stride, int(bool(reverse)), dtype,
+                                                 shard, nshards, None, ws.data_ptr(), ws.numel(), stream)
+        _capi.raise_for(rc, "linrec_b200_bwd_carry")
+        return dx, dc, rec, c, y
+
+    def bwd_fixup(self, dx, dc, c, y, gathered, reverse, shard, nshards):
+        numseq, seqlen, stride = _row_layout(dx)
+        with torch.cuda.device(dx.device):
+            stream = torch.cuda.current_stream(dx.device).cuda_stream
+            rc = _capi.lib.linrec_b200_bwd_fixup(dx.data_ptr(), dc.data_ptr(), c.data_ptr(), y.data_ptr(),
+                                                 gathered.data_ptr(), numseq, seqlen, stride, int(bool(reverse)),
+                                                 _DTYPES[dx.dtype], shard, nshards, stream)
+        _capi.raise_for(rc, "linrec_b200_bwd_fixup")
+
+
+_CUDA_KERNELS = CudaShardKernels()
+
+
+def _gather(records: torch.Tensor, group) -> torch.Tensor:
+    """All-gather of the per-row records in rank order: result[(rank, row, k)]."""
+    world = dist.get_world_size(group)
+    rows = records.shape[0]
+    out = torch.empty((world * rows,) + tuple(records.shape[1:]), dtype=records.dtype, device=records.device)
+    dist.all_gather_into_tensor(out, records.contiguous(), group=group)   # concatenation along dim 0
+    return out.view((world, rows) + tuple(records.shape[1:]))
+
+
+def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None):
+    """Forward scan of a row that is split over the ranks of `group` (this rank holds shard `rank`)."""
+    k = kernels or _CUDA_KERNELS
+    shard, nshards = dist.get_rank(group), dist.get_world_size(group)
+    y, rec = k.fwd_carry(x, c, reverse, shard, nshards)
+    if nshards > 1:
+        gathered = _gather(rec, group)
+        k.fwd_fixup(y, c if c.stride() == y.stride() else c.contiguous(), gathered, reverse, shard, nshards)
+    return y
+
+
+def seq_sharded_bwd(dy: torch.Tensor, c: torch.Tensor, y: torch.Tensor, reverse: bool = False, group=None,
+                    kernels=None):
+    """Backward of `seq_sharded_fwd`: (dx, dc) of this rank's shard; `y` is the forward output shard."""
+    k = kernels or _CUDA_KERNELS
+    shard, nshards = dist.get_rank(group), dist.get_world_size(group)
+    dx, dc, rec, c2, y2 = k.bwd_carry(dy, c, y, reverse, shard, nshards)
+    if nshards > 1:
+        gathered = _gather(rec, group)
+        k.bwd_fixup(dx, dc, c2, y2, gathered, reverse, shard, nshards)
+    return dx, dc
+
+
+class _SeqShardedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, c, reverse, group):
+        y = seq_sharded_fwd(x, c, reverse, group)
+        ctx.save_for_backward(c, y)
+        ctx.reverse, ctx.group = reverse, group
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        c, y = ctx.saved_tensors
+        if dy.stride() != c.stride():
+            dy = torch.empty_like(c).copy_(dy)
+        dx, dc = seq_sharded_bwd(dy, c, y, ctx.reverse, ctx.group)
+        return dx, dc, None, None
+
+
+def linrec_seq_sharded(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False, group=None) -> torch.Tensor:
+    """Differentiable scan over a sequence that is sharded across the ranks of `group`."""
+    return _SeqShardedFn.apply(inputs, coeffs, reverse, group)

@@ -1,0 +1,145 @@
+"""Sequence sharding, host side: two gloo ranks on CPU run `seq_sharded_fwd/bwd` with the device
+kernels replaced by a numpy stand-in that follows the same record contract as the C ABI
+(forward record (P, Y); backward record (P, Y, c at the shard's scan-last element, y at its
+scan-first element); fix-up = fold of the earlier shards' records + carry * running product).
+The records travel as fp32 (their contract), hence the 5e-6 tolerance.  What is under test is everything around the kernels: shard/rank bookkeeping, the all-gather layout,
+direction handling -- against the CPU oracle on the unsharded tensor."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class NumpyShardKernels:
+    """float64 stand-in for the four device entry points (same argument and record conventions)."""
+
+    @staticmethod
+    def _scan(x, c, asc, first_coeff_counts):
+        L = x.shape[-1]
+        y = np.zeros_like(x)
+        v = np.zeros(x.shape[:-1])
+        P = np.ones(x.shape[:-1])
+        order = range(L) if asc else range(L - 1, -1, -1)
+        for n, i in enumerate(order):
+            ci = c[..., i] if (n > 0 or first_coeff_counts) else np.zeros_like(c[..., i])
+            v = v * ci + x[..., i]
+            P = P * ci
+            y[..., i] = v
+        return y, P, v
+
+    def fwd_carry(self, x, c, reverse, shard, nshards):
+        asc = not reverse
+        holds_start = shard == (0 if asc else nshards - 1)
+        y, P, Y = self._scan(x.numpy().astype(np.float64), c.numpy().astype(np.float64), asc, not holds_start)
+        return torch.from_numpy(y), torch.from_numpy(np.stack([P, Y], -1).astype(np.float32))
+
+    def fwd_fixup(self, y, c, gathered, reverse, shard, nshards):
+        asc = not reverse
+        order = list(range(nshards)) if asc else list(range(nshards - 1, -1, -1))
+        g = gathered.numpy().astype(np.float64)
+        v = np.zeros(y.shape[0])
+        for s in order[:order.index(shard)]:
+            v = v * g[s, :, 0] + g[s, :, 1]
+        yn, cn = y.numpy(), c.numpy().astype(np.float64)
+        L = yn.shape[-1]
+        for i in (range(L) if asc else range(L - 1, -1, -1)):
+            v = v * cn[:, i]
+            yn[:, i] += v
+
+    def bwd_carry(self, dy, c, y, reverse, shard, nshards):
+        asc = bool(reverse)
+        holds_start = shard == (0 if asc else nshards - 1)
+        cn, yn, dyn = (t.numpy().astype(np.float64) for t in (c, y, dy))
+        L = cn.shape[-1]
+        cs, ys = np.ones_like(cn), np.zeros_like(yn)
+        if asc:
+            cs[:, 1:] = cn[:, :-1]
+            ys[:, :-1] = yn[:, 1:]
+        else:
+            cs[:, :-1] = cn[:, 1:]
+            ys[:, 1:] = yn[:, :-1]
+        dx, P, Y = self._scan(dyn, cs, asc, not holds_start)
+        dc = dx * ys
+        first, last = (0, L - 1) if asc else (L - 1, 0)
+        rec = np.stack([P, Y, cn[:, last], yn[:, first]], -1).astype(np.float32)
+        return torch.from_numpy(dx), torch.from_numpy(dc), torch.from_numpy(rec), c, y
+
+    def bwd_fixup(self, dx, dc, c, y, gathered, reverse, shard, nshards):
+        asc = bool(reverse)
+        order = list(range(nshards)) if asc else list(range(nshards - 1, -1, -1))
+        pos = order.index(shard)
+        g = gathered.numpy().astype(np.float64)
+        v = np.zeros(dx.shape[0])
+        prev = None
+        for s in order[:pos]:
+            if prev is not None:
+                v = v * g[prev, :, 2]
+            v = v * g[s, :, 0] + g[s, :, 1]
+            prev = s
+        if prev is not None:
+            v = v * g[prev, :, 2]
+        dxn, dcn, cn, yn = dx.numpy(), dc.numpy(), c.numpy().astype(np.float64), y.numpy().astype(np.float64)
+        L = dxn.shape[-1]
+        idx = list(range(L)) if asc else list(range(L - 1, -1, -1))
+        for n, i in enumerate(idx):
+            if n > 0:
+                v = v * cn[:, idx[n - 1]]
+            dxn[:, i] += v
+            if n + 1 < L:
+                dcn[:, i] += v * yn[:, idx[n + 1]]
+        if pos + 1 < nshards:
+            dcn[:, idx[-1]] = dxn[:, idx[-1]] * g[order[pos + 1], :, 3]
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from linrec_b200 import sharded
+        rows, L = 5, 96
+        Ls = L // world
+        g = torch.Generator().manual_seed(99)
+        x = torch.randn(rows, L, generator=g, dtype=torch.float64)
+        c = 0.6 + 0.4 * torch.rand(rows, L, generator=g, dtype=torch.float64)
+        dy = torch.randn(rows, L, generator=g, dtype=torch.float64)
+        k = NumpyShardKernels()
+        sl = slice(rank * Ls, (rank + 1) * Ls)
+        for rev in (False, True):
+            y_full = oracle.fwd_f64(x.numpy().astype(np.float32), c.numpy().astype(np.float32), reverse=rev)
+            x32, c32, dy32 = x.float().double(), c.float().double(), dy.float().double()
+            y = sharded.seq_sharded_fwd(x32[:, sl].contiguous(), c32[:, sl].contiguous(), rev, None, k)
+            np.testing.assert_allclose(y.numpy(), y_full[:, sl], rtol=5e-6, atol=5e-6)
+            dx_full, dc_full = oracle.bwd_f64(dy.numpy().astype(np.float32), c.numpy().astype(np.float32), y_full, reverse=rev)
+            ysh = torch.from_numpy(np.ascontiguousarray(y_full[:, sl]))
+            dx, dc = sharded.seq_sharded_bwd(dy32[:, sl].contiguous(), c32[:, sl].contiguous(), ysh, rev, None, k)
+            np.testing.assert_allclose(dx.numpy(), dx_full[:, sl], rtol=5e-6, atol=5e-6)
+            np.testing.assert_allclose(dc.numpy(), dc_full[:, sl], rtol=5e-6, atol=5e-6)
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_sharding_host_logic_gloo(tmp_path, world):
+    port = 29500 + (os.getpid() % 2000) + world
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_channel_sharding_is_the_plain_operator():
+    from linrec_b200 import sharded
+    import linrec_b200
+    assert sharded.linrec_channel_sharded.__doc__
+    # rows are independent: the sharded entry point must be the same operator, nothing added
+    import inspect
+    assert "linrec_pipe(inputs, coeffs, reverse)" in inspect.getsource(sharded.linrec_channel_sharded)
+    assert linrec_b200.linrec is linrec_b200.linrec_pipe

@@ -1,0 +1,115 @@
+"""Sequence sharding on the GPU.
+
+1. One GPU, all shards: the four C-ABI entry points are called for every shard in turn on slices of
+   one tensor and the records are stacked by hand (what the all-gather would deliver).  No kernel
+   waits for another launch, so this is safe on a single device.  Checked against the CPU oracle on
+   the unsharded tensor at the fp32 tolerance of the suite.
+2. Two or more GPUs (skipped otherwise): real ranks over NCCL through `linrec_seq_sharded` with
+   autograd, checked against the single-device operator.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-4, 1e-5
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _data(shape, clo, seed=5):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g), clo + (1 - clo) * torch.rand(shape, generator=g),
+            torch.randn(shape, generator=g))
+
+
+@pytest.mark.parametrize("rows,L,G,clo", [(6, 4 * 96, 4, 0.5), (3, 2 * 8192 * 3, 2, 0.9), (5, 3 * 2080, 3, 0.99),
+                                          (130, 8 * 512, 8, 0.0), (2, 4 * 40001, 4, 0.999)],
+                         ids=["short", "chained", "ragged", "many_rows", "slow_decay"])
+@pytest.mark.parametrize("rev", [False, True])
+def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
+    from linrec_b200.sharded import CudaShardKernels
+    k = CudaShardKernels()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((rows, L), clo)
+    Ls = L // G
+    xs = [x[:, s * Ls:(s + 1) * Ls].contiguous().to(dev) for s in range(G)]
+    cs = [c[:, s * Ls:(s + 1) * Ls].contiguous().to(dev) for s in range(G)]
+    # forward
+    ys, recs = zip(*[k.fwd_carry(xs[s], cs[s], rev, s, G) for s in range(G)])
+    gathered = torch.stack(recs).contiguous()
+    for s in range(G):
+        k.fwd_fixup(ys[s], cs[s], gathered, rev, s, G)
+    y = torch.cat([t.cpu() for t in ys], dim=1).numpy()
+    y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+    y64 = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
+    if clo < 0.99:
+        np.testing.assert_allclose(y, y_ref, rtol=RTOL, atol=ATOL)
+    else:
+        # slowly decaying coefficients: two valid fp32 orders differ by more than the nominal
+        # tolerance near zero crossings, so the fp64 evaluation is the judge
+        np.testing.assert_allclose(y, y64, rtol=RTOL, atol=6 * ATOL)
+    # backward, from the oracle's forward outputs
+    yg = [torch.from_numpy(np.ascontiguousarray(y_ref[:, s * Ls:(s + 1) * Ls])).to(dev) for s in range(G)]
+    dys = [dy[:, s * Ls:(s + 1) * Ls].contiguous().to(dev) for s in range(G)]
+    outs = [k.bwd_carry(dys[s], cs[s], yg[s], rev, s, G) for s in range(G)]
+    gathered = torch.stack([o[2] for o in outs]).contiguous()
+    for s in range(G):
+        k.bwd_fixup(outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
+    dx = torch.cat([o[0].cpu() for o in outs], dim=1).numpy()
+    dc = torch.cat([o[1].cpu() for o in outs], dim=1).numpy()
+    if clo < 0.99:
+        dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+        np.testing.assert_allclose(dx, dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dc, dc_ref, rtol=RTOL, atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+    else:
+        dx64, dc64 = oracle.bwd_f64(dy.numpy(), c.numpy(), y_ref.astype(np.float64), reverse=rev)
+        np.testing.assert_allclose(dx, dx64, rtol=RTOL, atol=6 * ATOL)
+        np.testing.assert_allclose(dc, dc64, rtol=RTOL, atol=6 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+    import linrec_b200
+    linrec_b200.check_status()
+
+
+def _nccl_worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import linrec_b200
+        from linrec_b200.sharded import linrec_seq_sharded
+        rows, L = 12, world * 3 * 4096
+        Ls = L // world
+        x, c, dy = _data((rows, L), 0.9, seed=77)
+        sl = slice(rank * Ls, (rank + 1) * Ls)
+        for rev in (False, True):
+            xf, cf = x.to(dev).requires_grad_(True), c.to(dev).requires_grad_(True)
+            y_full = linrec_b200.linrec(xf, cf, reverse=rev)
+            gx_full, gc_full = torch.autograd.grad(y_full, (xf, cf), dy.to(dev))
+            xs = x[:, sl].contiguous().to(dev).requires_grad_(True)
+            cs = c[:, sl].contiguous().to(dev).requires_grad_(True)
+            ys = linrec_seq_sharded(xs, cs, reverse=rev)
+            gx, gc = torch.autograd.grad(ys, (xs, cs), dy[:, sl].contiguous().to(dev))
+            torch.testing.assert_close(ys, y_full[:, sl], rtol=RTOL, atol=ATOL)
+            torch.testing.assert_close(gx, gx_full[:, sl], rtol=RTOL, atol=ATOL)
+            torch.testing.assert_close(gc, gc_full[:, sl], rtol=RTOL, atol=4 * ATOL)
+        linrec_b200.check_status()
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_real_ranks_over_nccl(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    port = 29600 + os.getpid() % 1000
+    mp.spawn(_nccl_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
