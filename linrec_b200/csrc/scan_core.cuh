@@ -248,21 +248,24 @@ struct Operands {
 //             belongs to the same row, otherwise the caller supplies it: `pred_c_outside` /
 //             `succ_y_outside` are the halo words at a tile edge inside a row and the edge values
 //             (0 unless the row continues on another shard) at a row end.
-// `valid` is the number of slots of this tile that lie inside the row (chain mode; < T only for
-// the piece at the row's memory end; T in multi-row mode).  A neighbour slot at or beyond it is
-// outside the row, so the caller's outside value is used for it as well.  With PATCH set, the coefficients of slots beyond it are
-// forced to 1: bulk copies fill them with 0, which would wipe the row's running product.
+// `valid` is the number of slots of the thread's row piece that lie inside the row: the row length
+// in multi-row mode (smaller than the slots a row occupies when rows are padded), and in chain mode
+// the part of the tile before the row's end.  A neighbour slot at or beyond it is outside the row,
+// so the caller's outside value is used for it as well.  With PATCH set, the coefficients of slots beyond it are
+// forced to 1 AFTER the backward shift: padding must be an identity element (x = 0, c = 1) or the
+// carry record of the row would pick up a stray factor (bulk copies fill with 0, and the shifted
+// coefficient of the first padding slot is the row's last real coefficient).
 template <typename ST, int E, int NT, bool BWD, bool ASC, bool PATCH>
 __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geometry& g,
                                               const ST* b_in0, const ST* b_c, const ST* b_y,
                                               float pred_c_outside, float succ_y_outside, int valid,
                                               bool zero_first)
 {
-    constexpr int T = E * NT;
     load_run<ST, E>(b_in0, g.t, op.x);
     float craw[E];
     load_run<ST, E>(b_c, g.t, craw);
-    const int a = g.t * E;
+    const int a = g.t * E;          // first slot of the run inside the tile
+    const int ra = g.m * E;         // ... and inside its row piece
     if (!BWD) {
 #pragma unroll
         for (int j = 0; j < E; ++j) op.c[j] = craw[j];
@@ -274,7 +277,7 @@ __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geomet
         // warp shuffle (lane stride of a blocked run would make a direct shared read a 4-way bank
         // conflict); only the lane at the warp's edge reads shared memory.
         const bool lo_ok = g.lo_in_tile;
-        const bool hi_ok = g.hi_in_tile && hi < valid;
+        const bool hi_ok = g.hi_in_tile && ra + E < valid;
         if (ASC) {   // predecessor = slot below, successor = slot above
             const float c_from_below = __shfl_up_sync(0xffffffffu, craw[E - 1], 1);
             const float y_from_above = __shfl_down_sync(0xffffffffu, yraw[0], 1);
@@ -298,10 +301,10 @@ __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geomet
         }
     }
     // Slots past the end of the row are identity elements (x = 0 already, c = 1).
-    if (PATCH && valid < T) {
+    if (PATCH && valid < g.tpr * E) {
 #pragma unroll
         for (int j = 0; j < E; ++j)
-            if (a + j >= valid) op.c[j] = 1.0f;
+            if (ra + j >= valid) op.c[j] = 1.0f;
     }
     // Nothing precedes the first element of a row: its coefficient is defined away, as in the
     // reference kernels that start with y[s] = x[s] (linrec/impl/cuda/linrec_ref.cuh:63).

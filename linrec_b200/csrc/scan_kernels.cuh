@@ -21,7 +21,7 @@ struct TileCoord {
     long long row;     // first row of the tile
     int q;             // chain: piece index in scan order
     int piece;         // chain: piece index in memory order
-    int valid;         // chain: slots of the tile that lie inside the row
+    int valid;         // slots of a row piece that lie inside the row (chain: of the tile; else the row length)
 };
 
 template <int T, bool ASC>
@@ -39,7 +39,7 @@ __device__ __forceinline__ TileCoord decode_ticket(const ScanParams& p, uint32_t
         tc.q = 0;
         tc.piece = 0;
         tc.row = (long long)tk * p.rows_per_tile;
-        tc.valid = T;
+        tc.valid = (int)p.seqlen;
     }
     return tc;
 }
@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
         const bool zero_first =
             !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
         Operands<E, BWD> op;
-        load_operands<ST, E, NT, BWD, ASC, false>(op, g, buf_in0, buf_c, buf_y,
+        load_operands<ST, E, NT, BWD, ASC, true>(op, g, buf_in0, buf_c, buf_y,
                                                   (BWD && p.chain) ? halo[0] : (p.open_start ? 1.0f : 0.0f),
                                                   (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
