@@ -255,12 +255,42 @@ def run_ours(args):
     value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
 
     # ---- end to end from pinned host buffers through the public API -----------------------------
+    # linrec_b200.host streams row slabs: copy-in of slab i+1, scan of slab i and copy-out of slab
+    # i-1 overlap on three streams; every byte of x, c, dy crosses PCIe in and every byte of y, dx, dc
+    # crosses it out inside the timed region.
+    from linrec_b200 import host as lr_host
     e2e_steps = max(1, min(args.steps, 3))
     hx, hc, hdy = (torch.empty(SHAPE, pin_memory=True) for _ in range(3))
     hy, hdx, hdc = (torch.empty(SHAPE, pin_memory=True) for _ in range(3))
     hx.copy_(x); hc.copy_(c); hdy.copy_(dy)
+    y_dev_cpu = y.cpu()
+    del y, dx, dc
 
     def e2e_step():
+        lr_host.linrec_fwd_bwd_host(hx, hc, hdy, reverse=False, out=(hy, hdx, hdc), device=dev)
+
+    def e2e_time(fn, n):
+        fn()
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            fn()
+        t1.record()
+        barrier()
+        ms = t0.elapsed_time(t1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    e2e_ms = e2e_time(e2e_step, e2e_steps)
+    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    e2e_ok = bool(torch.equal(hy, y_dev_cpu))   # same numbers as the device-resident step
+
+    # the same through autograd on whole tensors (copy in, scan, copy out, nothing overlapped)
+    def e2e_autograd_step():
         xd = hx.to(dev, non_blocking=True).requires_grad_(True)
         cd = hc.to(dev, non_blocking=True).requires_grad_(True)
         dyd = hdy.to(dev, non_blocking=True)
@@ -270,21 +300,49 @@ def run_ours(args):
         hdx.copy_(gx, non_blocking=True)
         hdc.copy_(gc, non_blocking=True)
 
-    e2e_step()
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    t1.record()
-    barrier()
-    e2e_ms = t0.elapsed_time(t1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
-    e2e_ok = bool(torch.equal(hy, y.cpu()))   # same numbers as the device-resident step
+    e2e_auto_ms = e2e_time(e2e_autograd_step, e2e_steps)
+    e2e_auto_value = world * step_bytes * e2e_steps / (e2e_auto_ms * 1e-3) / 1e9
+
+    # ---- sequence sharding: a fixed global problem (1024 rows x 2^20, c ~ U(0.99,1)) split along the
+    # sequence over the ranks: local scan -> one all-gather of per-row records -> fused fix-up
+    seq = None
+    if not args.no_seq_sharded:
+        from linrec_b200 import sharded
+        rows_s, L_s = 1024, (1 << 20) // world
+        gs = torch.Generator(device=dev).manual_seed(SEED + 100 + rank)
+        del hx, hc, hdy, hy, hdx, hdc
+        xs = torch.randn((rows_s, L_s), device=dev, generator=gs)
+        cs = 0.99 + 0.01 * torch.rand((rows_s, L_s), device=dev, generator=gs)
+        dys = torch.randn((rows_s, L_s), device=dev, generator=gs)
+
+        def seq_step():
+            if world == 1:
+                ys = C.linrec_pipe_fwd(inputs=xs, coeffs=cs, reverse=False)
+                return C.linrec_pipe_bwd(d_outputs=dys, coeffs=cs, outputs=ys, reverse=False)
+            ys = sharded.seq_sharded_fwd(xs, cs, False)
+            return sharded.seq_sharded_bwd(dys, cs, ys, False)
+
+        for _ in range(3):
+            seq_step()
+        barrier()
+        k_seq = max(1, min(args.steps, 10))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(k_seq):
+            seq_step()
+        s1.record()
+        barrier()
+        seq_ms = s0.elapsed_time(s1)
+        if world > 1:
+            t = torch.tensor([seq_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            seq_ms = float(t.item())
+        linrec_b200.check_status()
+        seq_bytes = rows_s * L_s * world * 32
+        seq = {"value": seq_bytes * k_seq / (seq_ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong",
+               "workload": "fwd+bwd, (1024, 2^20) fp32 global, c~U(0.99,1), columns split over the ranks",
+               "ms_per_step": seq_ms / k_seq, "steps": k_seq,
+               "collective": "one all-gather of 8 B (fwd) / 16 B (bwd) per row and rank" if world > 1 else "none"}
 
     if rank != 0:
         if world > 1:
@@ -325,8 +383,12 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 3 * n_elem * 4,
                 "d2h_bytes_per_step": 3 * n_elem * 4, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
-                "matches_device_run": e2e_ok},
+                "api": "linrec_b200.host.linrec_fwd_bwd_host (row slabs, copies and scans overlapped)",
+                "matches_device_run": e2e_ok,
+                "autograd_whole_tensor": {"value": e2e_auto_value, "ms_per_step": e2e_auto_ms / e2e_steps,
+                                          "api": "linrec_b200.linrec + torch.autograd.grad"}},
         "gpu_launches": int(launches),
+        "seq_sharded": seq,
         "roofline": roof,
         "cpu_baseline": cpu,
     }
@@ -338,9 +400,10 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-seq-sharded", action="store_true", help="skip the sequence-sharded extra measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -156,9 +156,10 @@ LINREC_API int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const vo
  *
  * Limit: the scratch a problem needs must fit the built-in buffer.  Rows that fit one tile need
  * 256 bytes whatever their number; rows longer than a tile need 16 more bytes per tile.  A tile is
- * 8192 elements when the rows are 16-byte aligned and a multiple of 128 bytes long, else 2048.  So
- * at most 65,520 tiles of long rows (about 5.3e8 fp32 elements in the aligned case) can be scanned
- * by one call; larger problems return LINREC_ERR_SCRATCH_LIMIT and launch nothing.
+ * 8192 elements for fp32 rows that are 16-byte aligned and a multiple of 128 bytes long, and 2048
+ * to 8192 otherwise (alignment, storage type and row count decide).  So at most 65,520 tiles of
+ * long rows (about 5.3e8 fp32 elements in the aligned case) can be scanned by one call; larger
+ * problems return LINREC_ERR_SCRATCH_LIMIT and launch nothing.
  *
  * The first call on each device looks up the buffer's device address (once per device, with that
  * device current); make that first call outside any stream capture.  All calls on a device share

@@ -129,6 +129,9 @@ const std::vector<TmaVariant>& tma_variants()
         make_tma_variant<8, 512, 2, 1>(),
         make_tma_variant<16, 512, 2, 1>(),
         make_tma_variant<16, 512, 1, 1>(),
+        make_tma_variant<32, 128, 2, 1>(),
+        make_tma_variant<32, 128, 3, 1>(),
+        make_tma_variant<32, 256, 2, 1>(),
     };
     return v;
 }
@@ -297,7 +300,7 @@ void shape_plan(Plan& pl, int dtype, int64_t numseq, int64_t seqlen)
 // The regime selector.  `kind` TILE refuses rows that do not fit one tile, as the reference's
 // tile operator does (linrec/impl/cuda/linrec_tile.cu:60).
 int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride,
-              const void* const* ptrs, int nptrs, const Options& opt, int max_smem)
+              const void* const* ptrs, int nptrs, const Options& opt, int max_smem, int sm_count)
 {
     const bool can_tma = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, nptrs);
     int memcode = opt.memcode;
@@ -314,8 +317,23 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
         int E = opt.E, NT = opt.NT, S = opt.S, OB = opt.OB;
         const bool pinned = !(E < 0 && NT < 0 && S < 0 && OB < 0);
         if (!pinned && kind != LINREC_KIND_TILE) {
-            if (!bwd) { E = 16; NT = 512; S = 2; OB = 1; }
-            else      { E = 16; NT = 128; S = 2; OB = 1; }
+            const int sz = di == 0 ? 4 : 2;
+            // rows shorter than the small tile never chain; with few long rows the predecessor of a
+            // tile is often still in flight, and fewer, larger CTAs do better
+            const bool short_rows = seqlen <= 2048;
+            const bool few_rows = !short_rows && numseq < 4LL * sm_count;
+            if (sz == 4) {
+                if (!bwd)          { E = 16; NT = 512; S = 2; OB = 1; }
+                else if (few_rows) { E = 16; NT = 512; S = 1; OB = 1; }
+                else               { E = 16; NT = 128; S = 2; OB = 1; }
+            } else {
+                // 2-byte storage moves half the bytes per element, so instruction issue starts to
+                // matter: 32 elements per thread halve the shuffle and barrier cost per element
+                if (short_rows)    { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
+                else if (few_rows) { E = 32; NT = 256; S = 2; OB = 1; }
+                else if (!bwd)     { E = 32; NT = 128; S = 3; OB = 1; }
+                else               { E = 16; NT = 128; S = 3; OB = 1; }
+            }
         }
         const TmaVariant* best = nullptr;
         for (const TmaVariant& v : tma_variants()) {
@@ -422,7 +440,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     }
 
     Plan pl;
-    rc = make_plan(pl, kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, dev.max_smem_optin);
+    rc = make_plan(pl, kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, dev.max_smem_optin, dev.sm_count);
     if (rc != LINREC_OK) return rc;
 
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < workspace_need(pl))
@@ -591,7 +609,7 @@ int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, con
         DeviceInfo dev;
         rc = device_info(dev);
         if (rc != LINREC_OK) return rc;
-        rc = make_plan(pl, LINREC_KIND_PIPE, bwd, dtype, 1024, 1 << 20, 1 << 20, ptrs, 0, o2, dev.max_smem_optin);
+        rc = make_plan(pl, LINREC_KIND_PIPE, bwd, dtype, 1024, 1 << 20, 1 << 20, ptrs, 0, o2, dev.max_smem_optin, dev.sm_count);
         if (rc != LINREC_OK) return rc;
         if (pl.tma) {
             fn = reinterpret_cast<const void*>(pl.tv->fn[di][bwd][1]);
@@ -740,7 +758,7 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
     if (rc != LINREC_OK) return rc;
     Plan pl;
     const void* all[5] = {x, c, y, x, y};
-    rc = make_plan(pl, LINREC_KIND_PIPE, false, dtype, numseq, seqlen, row_stride, all, 5, Options{}, dev.max_smem_optin);
+    rc = make_plan(pl, LINREC_KIND_PIPE, false, dtype, numseq, seqlen, row_stride, all, 5, Options{}, dev.max_smem_optin, dev.sm_count);
     if (rc != LINREC_OK) return rc;
     if (workspace_need(pl) > (size_t)LINREC_STATIC_SCRATCH_BYTES) return LINREC_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;

@@ -95,11 +95,19 @@ def _row_layout(t: torch.Tensor):
     return n, L, row_stride
 
 
-def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict):
+def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
+    """One forward or backward call.  `outs` (optional) are caller-provided result tensors with the
+    layout of the inputs; without them the results are allocated like the inputs."""
     _check_same(*ins)
     ref = ins[0]
     n_out = 2 if bwd else 1
-    outs = [torch.empty_like(ref) for _ in range(n_out)]
+    if outs is None:
+        outs = [torch.empty_like(ref) for _ in range(n_out)]
+    else:
+        outs = list(outs)
+        if len(outs) != n_out:
+            raise RuntimeError("linrec: wrong number of result tensors")
+        _check_same(ref, *outs)
     if ref.numel() == 0:
         return outs
     layout = _row_layout(ref)

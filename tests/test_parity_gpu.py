@@ -118,6 +118,34 @@ def test_three_dim_batch_autograd():
         np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
 
 
+# ---- bf16 storage, fp32 arithmetic -----------------------------------------------------------------
+BF16_RTOL = 2.0 ** -7
+
+
+@pytest.mark.parametrize("shape", [(64, 512), (300, 64), (5, 3 * 8192), (3, 1000), (7, 4097), (16, 65536), (2, 2 * 8192 + 64)],
+                         ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_bf16_storage(shape, rev):
+    """Inputs rounded to bf16; the oracle runs in fp32 on the upcast inputs; our outputs are fp32
+    accumulations rounded once to bf16 (relative error <= 2^-9), tolerance rtol 2^-7 / atol 1e-5."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = (t.bfloat16() for t in _data(shape, clo=0.5, chi=1.0))
+    y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
+    assert y.dtype == torch.bfloat16
+    y_ref = oracle.fwd_f32(x.float().numpy(), c.float().numpy(), reverse=rev)
+    np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=BF16_RTOL, atol=ATOL)
+    yb = torch.from_numpy(y_ref).bfloat16()
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yb.to(dev), reverse=rev)
+    dx_ref, dc_ref = oracle.bwd_f32(dy.float().numpy(), c.float().numpy(), yb.float().numpy(), reverse=rev)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=BF16_RTOL, atol=ATOL)
+    np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref, rtol=BF16_RTOL, atol=2 * ATOL)
+    # the sequential operator and every bulk-copy variant agree on bf16 as well
+    y_seq = lb._C.linrec_ref_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
+    np.testing.assert_allclose(y_seq.float().cpu().numpy(), y_ref, rtol=BF16_RTOL, atol=ATOL)
+    lb.check_status()
+
+
 # ---- every compiled variant ------------------------------------------------------------------------
 def _variants():
     lb = _ops()
@@ -202,6 +230,25 @@ def test_guard_bands_untouched():
                     if stride > L:
                         assert torch.all(body[:, L:] == -777.0)
                     assert not torch.any(body[:, :L] == -777.0)
+
+
+def test_host_streamed_path():
+    """Tensors in host memory, streamed through the device in row slabs (ragged last slab)."""
+    from linrec_b200 import host
+    for shape, slab in [((37, 1024), 8), ((5, 3 * 8192), 2), ((3, 7, 100), 4), ((9, 4096), None)]:
+        x, c, dy = _data(shape, clo=0.5)
+        pinned = [t.pin_memory() for t in (x, c, dy)]
+        for rev in (False, True):
+            y, dx, dc = host.linrec_fwd_bwd_host(*pinned, reverse=rev, slab_rows=slab)
+            yf = host.linrec_fwd_host(pinned[0], pinned[1], reverse=rev, slab_rows=slab)
+            torch.cuda.synchronize()
+            y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+            dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y.numpy(), reverse=rev)
+            np.testing.assert_allclose(y.numpy(), y_ref, rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(yf.numpy(), y_ref, rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(dx.numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(dc.numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
+    _ops().check_status()
 
 
 # ---- the three operator families and their error behaviour ------------------------------------------
