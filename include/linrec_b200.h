@@ -69,9 +69,11 @@ typedef struct linrec_opts {
     const int* values;
 } linrec_opts;
 
-/* Bytes of scratch a call on this shape may need (look-back descriptors, ticket counter and the
- * status word).  Always > 0 and a multiple of 256; the buffer must be 256-byte aligned device
- * memory.  Replaces nothing in the reference (its kernels never leave one CTA per row). */
+/* Bytes of scratch a call on this shape may need (look-back descriptors, ticket counter, epoch and
+ * the status word).  Always > 0 and a multiple of 256; the buffer must be 256-byte aligned device
+ * memory that its owner ZEROES ONCE before the first call (cudaMemset).  After that no call needs
+ * any preparation: each launch leaves the workspace ready for the next one, whatever its shape.
+ * Replaces nothing in the reference (its kernels never leave one CTA per row). */
 LINREC_API size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype);
 
 /* Forward scan.  Replaces linrec_{ref,tile,pipe}_fwd (linrec/impl/cuda/linrec.h:17-19,28-31,44-47).
@@ -89,8 +91,8 @@ LINREC_API int linrec_b200_bwd(int kind, const void* dy, const void* c, const vo
                                int reverse, int dtype, const linrec_opts* opts,
                                void* workspace, size_t workspace_bytes, void* stream);
 
-/* Device-side status word of the last call that used `workspace`: synchronises `stream`, reads
- * the word and returns LINREC_OK or LINREC_ERR_TIMEOUT.  The bounded waits inside the kernels
+/* Device-side status word of the calls that used `workspace` since it was last read: synchronises
+ * `stream`, reads the word, clears it, and returns LINREC_OK or LINREC_ERR_TIMEOUT.  The bounded waits inside the kernels
  * (look-back on a predecessor tile, arrival of a bulk copy) never trap and never spin forever;
  * when one gives up the kernel finishes with wrong numbers and sets this word.
  * No counterpart in the reference (its kernels contain no inter-CTA wait). */

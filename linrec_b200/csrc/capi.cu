@@ -463,14 +463,11 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     long long grid = (long long)dev.sm_count * occ;
     if (grid > pl.ntiles) grid = pl.ntiles;
 
-    // workspace: ticket counter and status word by a one-thread kernel, descriptors by a memset
-    linrec::linrec_init_header_kernel<<<1, 32, 0, stream>>>(p.header, (uint32_t)opt.first_ticket);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (pl.chain) {
-        if (cudaMemsetAsync(p.desc, 0, (size_t)pl.ntiles * sizeof(TileDesc), stream) != cudaSuccess) {
-            cudaGetLastError();
-            return LINREC_ERR_CUDA;
-        }
+    // The workspace cleans up after every launch by itself (see scan_core.cuh); nothing to prepare
+    // here, except for the diagnostics option that moves the first ticket.
+    if (opt.first_ticket != 0) {
+        linrec::linrec_set_first_ticket_kernel<<<1, 32, 0, stream>>>(p.header, (uint32_t)opt.first_ticket);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
     }
 
     if (pl.tma) {
@@ -502,13 +499,20 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
 {
     constexpr int NT = 256;
     long long grid = fp.numseq < (long long)sm_count * 8 ? fp.numseq : (long long)sm_count * 8;
+    // 16-byte accesses need aligned rows whose length is a multiple of the 8 elements a thread takes
+    auto al = [](const void* q) { return q == nullptr || reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+    const bool vec = al(fp.out0) && al(fp.out1) && al(fp.c) && al(fp.yin) && fp.seqlen % 8 == 0 &&
+                     (fp.row_stride * (long long)sizeof(ST)) % 16 == 0;
+    const unsigned g = (unsigned)grid;
+#define LINREC_FIXUP(B, A, V) linrec::linrec_fixup_kernel<ST, NT, B, A, V><<<g, NT, 0, stream>>>(fp)
     if (!bwd) {
-        if (asc) linrec::linrec_fixup_kernel<ST, NT, false, true><<<(unsigned)grid, NT, 0, stream>>>(fp);
-        else     linrec::linrec_fixup_kernel<ST, NT, false, false><<<(unsigned)grid, NT, 0, stream>>>(fp);
+        if (asc) { if (vec) LINREC_FIXUP(false, true, true); else LINREC_FIXUP(false, true, false); }
+        else     { if (vec) LINREC_FIXUP(false, false, true); else LINREC_FIXUP(false, false, false); }
     } else {
-        if (asc) linrec::linrec_fixup_kernel<ST, NT, true, true><<<(unsigned)grid, NT, 0, stream>>>(fp);
-        else     linrec::linrec_fixup_kernel<ST, NT, true, false><<<(unsigned)grid, NT, 0, stream>>>(fp);
+        if (asc) { if (vec) LINREC_FIXUP(true, true, true); else LINREC_FIXUP(true, true, false); }
+        else     { if (vec) LINREC_FIXUP(true, false, true); else LINREC_FIXUP(true, false, false); }
     }
+#undef LINREC_FIXUP
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
 }
@@ -580,7 +584,11 @@ int linrec_b200_status(const void* workspace, void* stream)
     uint32_t words[2] = {0, 0};
     if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return LINREC_ERR_CUDA;
     if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return LINREC_ERR_CUDA;
-    return words[1] == 0 ? LINREC_OK : LINREC_ERR_TIMEOUT;
+    if (words[1] == 0) return LINREC_OK;
+    // the word is sticky until it has been read: clear it now
+    if (cudaMemset(static_cast<char*>(const_cast<void*>(workspace)) + sizeof(uint32_t), 0, sizeof(uint32_t)) != cudaSuccess)
+        return LINREC_ERR_CUDA;
+    return LINREC_ERR_TIMEOUT;
 }
 
 int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, const char** names, int* values, int cap)

@@ -204,6 +204,7 @@ static int run(const Args& a)
     const size_t ws_bytes = linrec_b200_workspace_size(a.numseq, a.seqlen, a.dtype);
     void* ws;
     CK(cudaMalloc(&ws, ws_bytes));
+    CK(cudaMemset(ws, 0, ws_bytes));   // once; launches leave the workspace ready for the next one
     float* flush_buf = nullptr;
     const size_t flush_n = a.flush ? (size_t)64 << 20 : 0;   // 256 MiB of floats, twice the L2
     if (a.flush) CK(cudaMalloc(&flush_buf, flush_n * sizeof(float)));

@@ -27,15 +27,20 @@
 namespace linrec {
 
 // ---- workspace layout ---------------------------------------------------------------------------
-constexpr int kHeaderBytes = 256;            // [0] ticket counter, [1] status word, rest reserved
+// Header words: [0] ticket counter, [1] status word (sticky until read), [2] epoch, [3] CTAs done.
+// The workspace is zeroed ONCE by its owner; after that every launch cleans up after itself: the
+// last CTA to finish resets the ticket and done counters and advances the epoch, and look-back
+// descriptors carry the epoch they were written in, so stale ones read as "nothing yet".
+constexpr int kHeaderBytes = 256;
 constexpr uint32_t kStatusLookbackTimeout = 1u;
 constexpr uint32_t kStatusCopyTimeout = 2u;
 
 // One look-back descriptor per chained tile: 16 bytes that are always read and written with ONE
 // 128-bit access, so that a reader sees the status together with the value it belongs to.
-//   status 0  nothing yet
-//   status 1  (y, p) is the aggregate of the tile alone
-//   status 2  (y, p) is the inclusive value of the row up to and including the tile
+//   status = epoch * 4 + state;  a descriptor of another epoch counts as state 0
+//   state 0  nothing yet
+//   state 1  (y, p) is the aggregate of the tile alone
+//   state 2  (y, p) is the inclusive value of the row up to and including the tile
 struct __align__(16) TileDesc {
     float y, p;
     uint32_t status;
@@ -383,22 +388,42 @@ __device__ __forceinline__ Pair warp_reduce_far_to_near(Pair v, int lane)
 }
 
 // Descriptor access: one 128-bit relaxed load / store at GPU scope.
-__device__ __forceinline__ uint4 desc_load(const TileDesc* d)
+// The returned word has its status reduced to the state (0, 1, 2) as seen from `epoch`.
+__device__ __forceinline__ uint4 desc_load(const TileDesc* d, uint32_t epoch)
 {
     uint4 v;
     asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(d)
                  : "memory");
+    v.z = ((v.z >> 2) == epoch) ? (v.z & 3u) : 0u;
     return v;
 }
 
 // Publishes a tile's aggregate (status 1) or inclusive value (status 2); one lane calls this.
-__device__ __forceinline__ void publish(TileDesc* d, Pair v, uint32_t status)
+__device__ __forceinline__ void publish(TileDesc* d, Pair v, uint32_t state, uint32_t epoch)
 {
     asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(d), "r"(__float_as_uint(v.y)),
-                 "r"(__float_as_uint(v.p)), "r"(status), "r"(0u)
+                 "r"(__float_as_uint(v.p)), "r"((epoch << 2) | state), "r"(0u)
                  : "memory");
+}
+
+// Launch epilogue, called by one thread of every CTA after the CTA's last access to the workspace:
+// the CTA that finishes last makes the workspace ready for the next launch.
+__device__ __forceinline__ void finish_launch(uint32_t* header, uint32_t epoch)
+{
+    __threadfence();
+    const uint32_t done = atomicAdd(header + 3, 1u);
+    if (done == gridDim.x - 1) {
+        header[0] = 0u;
+        header[3] = 0u;
+        header[2] = (epoch + 1u) & 0x3fffffffu;
+    }
+}
+
+__device__ __forceinline__ uint32_t read_epoch(const uint32_t* header)
+{
+    return *reinterpret_cast<const volatile uint32_t*>(header + 2);
 }
 
 __device__ __forceinline__ Pair desc_pair(const uint4& v) { return Pair{__uint_as_float(v.x), __uint_as_float(v.y)}; }
@@ -408,7 +433,7 @@ __device__ __forceinline__ Pair desc_pair(const uint4& v) { return Pair{__uint_a
 // tickets back.  Returns (on every lane) the exclusive prefix of this tile.  Each poll is bounded
 // by p.wait_budget clock ticks; on expiry the status word is flagged and the missing predecessor
 // is treated as an inclusive identity so that the walk terminates.
-__device__ __forceinline__ Pair lookback(const ScanParams& p, long long ticket, int q, int lane)
+__device__ __forceinline__ Pair lookback(const ScanParams& p, uint32_t epoch, long long ticket, int q, int lane)
 {
     Pair acc = pair_identity();
     int j0 = 1;
@@ -418,11 +443,11 @@ __device__ __forceinline__ Pair lookback(const ScanParams& p, long long ticket, 
         uint32_t st = 2u;
         if (pq >= 0) {
             const TileDesc* d = p.desc + (ticket - (long long)(j0 + lane) * p.numseq);
-            uint4 w = desc_load(d);
+            uint4 w = desc_load(d, epoch);
             if (w.z == 0u) {
                 const long long t0 = clock64();
                 unsigned ns = 32;
-                while ((w = desc_load(d)).z == 0u) {
+                while ((w = desc_load(d, epoch)).z == 0u) {
                     if (clock64() - t0 > p.wait_budget) break;
                     __nanosleep(ns);
                     if (ns < 1024) ns <<= 1;

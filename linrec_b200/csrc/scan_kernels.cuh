@@ -64,7 +64,7 @@ struct ChainShared {
 template <int E, int NT, bool BWD, bool ASC, typename AfterRead>
 __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g,
                                           const Operands<E, BWD>& op, const TileCoord& tc,
-                                          uint32_t tk, uint32_t next_tk, uint4& probe, Pair* wagg,
+                                          uint32_t tk, uint32_t next_tk, uint32_t epoch, uint4& probe, Pair* wagg,
                                           ChainShared* cs, float (&o0)[E], float (&o1)[BWD ? E : 1],
                                           AfterRead&& after_read)
 {
@@ -76,7 +76,7 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
         if (tc.q == 0) {
             early = 1;
         } else {
-            if (probe.z != 2u) probe = desc_load(p.desc + ((long long)tk - p.numseq));
+            if (probe.z != 2u) probe = desc_load(p.desc + ((long long)tk - p.numseq), epoch);
             if (probe.z == 2u) {
                 tp = desc_pair(probe);
                 early = 1;
@@ -98,12 +98,12 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
             Pair tp;
             if (early) {
                 tp = cs->tprefix;
-                if (g.lane == 0 && !last_piece) publish(d, combine(tp, bagg), 2u);
+                if (g.lane == 0 && !last_piece) publish(d, combine(tp, bagg), 2u, epoch);
             } else {
-                if (g.lane == 0 && !last_piece) publish(d, bagg, 1u);
-                tp = lookback(p, (long long)tk, tc.q, g.lane);
+                if (g.lane == 0 && !last_piece) publish(d, bagg, 1u, epoch);
+                tp = lookback(p, epoch, (long long)tk, tc.q, g.lane);
                 if (g.lane == 0) {
-                    if (!last_piece) publish(d, combine(tp, bagg), 2u);
+                    if (!last_piece) publish(d, combine(tp, bagg), 2u, epoch);
                     cs->tprefix = tp;
                 }
             }
@@ -115,7 +115,7 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
             // fetch ahead what the next tile of this CTA will ask for
             probe = make_uint4(0u, 0u, 0u, 0u);
             if (next_tk < (uint32_t)p.ntiles && next_tk >= (uint32_t)p.numseq)
-                probe = desc_load(p.desc + ((long long)next_tk - p.numseq));
+                probe = desc_load(p.desc + ((long long)next_tk - p.numseq), epoch);
         }
         if (!early) __syncthreads();
         pre = cs->tprefix;
@@ -174,6 +174,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     const Geometry g = make_geometry<E, NT, ASC>(p);
     const int tid = g.t;
     const uint32_t ntiles = (uint32_t)p.ntiles;
+    const uint32_t epoch = read_epoch(p.header);
     const bool with_halo = BWD && p.chain;
     const uint32_t stage_bytes =
         (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
@@ -272,7 +273,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
                                                  tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         bool alive = true;
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             // the output buffer about to be reused must have been drained by its bulk store
             if (tid == 0) ptx::tma_wait_group_read<OB - 1>();
             __syncthreads();
@@ -313,6 +314,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             }
         }
         ptx::tma_wait_group<0>();
+        finish_launch(p.header, epoch);
     }
 }
 
@@ -334,6 +336,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     const Geometry g = make_geometry<E, NT, ASC>(p);
     const int tid = g.t;
     const uint32_t ntiles = (uint32_t)p.ntiles;
+    const uint32_t epoch = read_epoch(p.header);
     const ST* gin0 = reinterpret_cast<const ST*>(p.in0);
     const ST* gc = reinterpret_cast<const ST*>(p.c);
     const ST* gy = reinterpret_cast<const ST*>(p.yin);
@@ -385,7 +388,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
                                                   (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // no look-ahead here: the linking warp probes when it needs to
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             __syncthreads();
             return true;
         });
@@ -407,6 +410,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             }
         }
     }
+    if (tid == 0) finish_launch(p.header, epoch);
 }
 
 // =================================================================================================
@@ -450,14 +454,12 @@ __global__ void linrec_seq_kernel(const ScanParams p, int reverse)
 }
 
 // =================================================================================================
-//  Workspace header initialisation
+//  Workspace header: diagnostics hook
 // =================================================================================================
-__global__ void linrec_init_header_kernel(uint32_t* header, uint32_t first_ticket)
+// Diagnostics only: lets the tickets of the next launch start past the first tiles.
+__global__ void linrec_set_first_ticket_kernel(uint32_t* header, uint32_t first_ticket)
 {
-    if (threadIdx.x == 0) {
-        header[0] = first_ticket;
-        header[1] = 0u;
-    }
+    if (threadIdx.x == 0) header[0] = first_ticket;
 }
 
 }  // namespace linrec

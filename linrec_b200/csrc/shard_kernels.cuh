@@ -46,17 +46,66 @@ __global__ void linrec_edges_kernel(const ST* c, const ST* y, float* records, lo
     records[4 * r + 3] = Storage<ST>::to_float(y[r * row_stride + first]);
 }
 
-// One CTA per row (grid-stride over rows).  Every thread handles V consecutive elements per step;
-// a step covers NT*V elements in scan order.
-template <typename ST, int NT, bool BWD, bool ASC>
+// Eight consecutive elements of a row as floats, memory order.  VEC: 16-byte loads (the caller has
+// checked alignment), else element loads.  `m0` may address elements outside [0, seqlen) only when
+// VEC is false, where every element is bounds-checked.
+template <typename ST, bool VEC>
+__device__ __forceinline__ void load8(const ST* row, long long m0, long long seqlen, float fill, float (&v)[8])
+{
+    if (VEC) {
+        constexpr int PC = Storage<ST>::kPerChunk;
+#pragma unroll
+        for (int k = 0; k < 8 / PC; ++k) {
+            const uint4 q = *reinterpret_cast<const uint4*>(row + m0 + k * PC);
+            Storage<ST>::unpack(q, &v[k * PC]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long m = m0 + j;
+            v[j] = (m >= 0 && m < seqlen) ? Storage<ST>::to_float(row[m]) : fill;
+        }
+    }
+}
+
+template <typename ST, bool VEC>
+__device__ __forceinline__ void store8(ST* row, long long m0, long long seqlen, const float (&v)[8])
+{
+    if (VEC) {
+        constexpr int PC = Storage<ST>::kPerChunk;
+#pragma unroll
+        for (int k = 0; k < 8 / PC; ++k) *reinterpret_cast<uint4*>(row + m0 + k * PC) = Storage<ST>::pack(&v[k * PC]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long m = m0 + j;
+            if (m >= 0 && m < seqlen) row[m] = Storage<ST>::from_float(v[j]);
+        }
+    }
+}
+
+// What one thread needs for one step of the walk, in MEMORY order (8 consecutive elements).
+template <bool BWD>
+struct FixupStep {
+    float c[8];              // forward: c of the element; backward: c of the scan predecessor
+    float o0[8];             // current y (forward) / dx (backward)
+    float o1[BWD ? 8 : 1];   // backward: current dc
+    float ys[BWD ? 8 : 1];   // backward: y of the scan successor
+    long long m0;            // memory index of element 0
+};
+
+// One CTA per row (grid-stride over rows).  Every thread handles 8 consecutive elements per step,
+// a step covers NT*8 elements in scan order; the operands of the next step are requested before
+// the current step is worked on, so the walk runs at one DRAM round trip per step at most.
+template <typename ST, int NT, bool BWD, bool ASC, bool VEC>
 __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
 {
-    constexpr int V = 4, NW = NT / 32, STEP = NT * V;
-    __shared__ float wprod[NW];
+    constexpr int V = 8, NW = NT / 32, STEP = NT * V;
+    __shared__ float wprod[2][NW];
     __shared__ float v_in_s;
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
-    // my position among the shards in scan order
-    const int my_pos = ASC ? p.shard : p.nshards - 1 - p.shard;
+    const int my_pos = ASC ? p.shard : p.nshards - 1 - p.shard;   // my rank among the shards in scan order
+    const long long L = p.seqlen;
 
     for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
         // ---- carry that enters this shard ---------------------------------------------------------
@@ -80,42 +129,60 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
         ST* o1 = BWD ? reinterpret_cast<ST*>(p.out1) + rb : nullptr;
         const ST* c = reinterpret_cast<const ST*>(p.c) + rb;
         const ST* y = BWD ? reinterpret_cast<const ST*>(p.yin) + rb : nullptr;
-        const bool have_next = my_pos + 1 < p.nshards;
 
-        // ---- walk the shard in scan order until the carried value is exactly zero ------------------
-        for (long long base = 0; base < p.seqlen && v != 0.0f; base += STEP) {
-            // scan position n (0-based within the shard) <-> memory index
-            float cc[V], oo[V], ys[V];
-            bool ok[V];
-            long long idx[V];
+        // operands of the step that starts at scan position `base`
+        auto fetch = [&](long long base, FixupStep<BWD>& st) {
+            const long long n0 = base + (long long)tid * V;          // first scan position of the thread
+            st.m0 = ASC ? n0 : L - n0 - V;                            // lowest memory index of its 8 elements
+            if (n0 >= L) return;                                      // nothing of this thread is in range
+            load8<ST, VEC>(o0, st.m0, L, 0.0f, st.o0);
+            float cr[8];
+            load8<ST, VEC>(c, st.m0, L, 1.0f, cr);
+            if constexpr (!BWD) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-                const long long n = base + (long long)tid * V + j;
-                ok[j] = n < p.seqlen;
-                idx[j] = ASC ? n : p.seqlen - 1 - n;
-                float coef = 1.0f;
-                if (ok[j]) {
-                    if (!BWD) {
-                        coef = Storage<ST>::to_float(c[idx[j]]);
-                    } else if (n > 0) {
-                        // coefficient of the scan predecessor; for n == 0 the neighbour shard's edge
-                        // coefficient is already folded into v
-                        coef = Storage<ST>::to_float(c[ASC ? idx[j] - 1 : idx[j] + 1]);
+                for (int j = 0; j < 8; ++j) st.c[j] = cr[j];
+            } else {
+                float yr[8];
+                load8<ST, VEC>(y, st.m0, L, 0.0f, yr);
+                load8<ST, VEC>(o1, st.m0, L, 0.0f, st.o1);
+                // neighbours just outside the 8 elements (0 / 1 beyond the shard: the edge factors are
+                // folded into the carry and the scan-last dc is finished after the walk)
+                const long long below = st.m0 - 1, above = st.m0 + V;
+                const float c_below = below >= 0 ? Storage<ST>::to_float(c[below]) : 1.0f;
+                const float c_above = above < L ? Storage<ST>::to_float(c[above]) : 1.0f;
+                const float y_below = below >= 0 ? Storage<ST>::to_float(y[below]) : 0.0f;
+                const float y_above = above < L ? Storage<ST>::to_float(y[above]) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (ASC) {
+                        st.c[j] = j == 0 ? c_below : cr[j - 1];
+                        st.ys[j] = j == 7 ? y_above : yr[j + 1];
+                    } else {
+                        st.c[j] = j == 7 ? c_above : cr[j + 1];
+                        st.ys[j] = j == 0 ? y_below : yr[j - 1];
                     }
-                    oo[j] = Storage<ST>::to_float(o0[idx[j]]);
-                    if (BWD) ys[j] = (n + 1 < p.seqlen) ? Storage<ST>::to_float(y[ASC ? idx[j] + 1 : idx[j] - 1]) : 0.0f;
-                } else {
-                    oo[j] = 0.0f;
-                    if (BWD) ys[j] = 0.0f;
                 }
-                cc[j] = coef;
             }
-            // running products inside the thread, then across the block
-            float pr[V];
+        };
+
+        FixupStep<BWD> cur, nxt;
+        if (v != 0.0f) fetch(0, cur);
+        int par = 0;
+        for (long long base = 0; base < L && v != 0.0f; base += STEP, par ^= 1) {
+            if (base + STEP < L) fetch(base + STEP, nxt);
+            const long long n0 = base + (long long)tid * V;
+            // coefficients in scan order; identity outside the shard
+            float cc[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const int j = ASC ? jj : 7 - jj;
+                cc[jj] = (n0 + jj < L) ? cur.c[j] : 1.0f;
+            }
+            float pr[8];
             pr[0] = cc[0];
 #pragma unroll
-            for (int j = 1; j < V; ++j) pr[j] = pr[j - 1] * cc[j];
-            float incl = pr[V - 1];
+            for (int jj = 1; jj < 8; ++jj) pr[jj] = pr[jj - 1] * cc[jj];
+            float incl = pr[7];
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
                 const float t = __shfl_up_sync(0xffffffffu, incl, d);
@@ -123,44 +190,42 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             }
             float excl = __shfl_up_sync(0xffffffffu, incl, 1);
             if (lane == 0) excl = 1.0f;
-            if (lane == 31) wprod[w] = incl;
-            __syncthreads();
+            if (lane == 31) wprod[par][w] = incl;
+            __syncthreads();   // (the other half of wprod belongs to the previous step: no second barrier)
             float before = 1.0f, total = 1.0f;
 #pragma unroll
             for (int k = 0; k < NW; ++k) {
-                const float t = wprod[k];
+                const float t = wprod[par][k];
                 if (k < w) before *= t;
                 total *= t;
             }
-            const float zin = v * before * excl;   // value entering this thread's first element
+            const float zin = v * before * excl;   // value that enters this thread's first element
+            if (n0 < L) {
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-                if (ok[j]) {
-                    const float z = zin * pr[j];
-                    const float nv = oo[j] + z;
-                    o0[idx[j]] = Storage<ST>::from_float(nv);
-                    if (BWD) {
-                        // dc = dx * y_successor; the scan-last element is finished after the walk
-                        const float dcv = Storage<ST>::to_float(o1[idx[j]]);
-                        o1[idx[j]] = Storage<ST>::from_float(fmaf(z, ys[j], dcv));
-                    }
+                for (int jj = 0; jj < 8; ++jj) {
+                    const int j = ASC ? jj : 7 - jj;
+                    const float z = zin * pr[jj];
+                    cur.o0[j] += z;
+                    if constexpr (BWD) cur.o1[j] = fmaf(z, cur.ys[j], cur.o1[j]);
                 }
+                store8<ST, VEC>(o0, cur.m0, L, cur.o0);
+                if constexpr (BWD) store8<ST, VEC>(o1, cur.m0, L, cur.o1);
             }
             v = v * total;
-            __syncthreads();   // wprod is rewritten by the next step
+            cur = nxt;
         }
-        if (BWD) {
+        if constexpr (BWD) {
             // the scan-last element multiplies with y of the NEXT shard's scan-first element, which
             // the local pass could not know
             __syncthreads();
-            if (tid == 0 && have_next) {
-                const int nxt = shard_at<ASC>(my_pos + 1, p.nshards);
-                const float y_edge = p.carries[((long long)nxt * p.numseq + row) * p.rec + 3];
-                const long long last = ASC ? p.seqlen - 1 : 0;
+            if (tid == 0 && my_pos + 1 < p.nshards) {
+                const int nxt_shard = shard_at<ASC>(my_pos + 1, p.nshards);
+                const float y_edge = p.carries[((long long)nxt_shard * p.numseq + row) * p.rec + 3];
+                const long long last = ASC ? L - 1 : 0;
                 o1[last] = Storage<ST>::from_float(Storage<ST>::to_float(o0[last]) * y_edge);
             }
         }
-        __syncthreads();   // v_in_s is rewritten for the next row
+        __syncthreads();   // v_in_s and wprod are rewritten for the next row
     }
 }
 

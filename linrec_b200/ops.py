@@ -37,7 +37,8 @@ def _workspace(device: torch.device, stream_ptr: int, nbytes: int) -> torch.Tens
     with _ws_lock:
         ws = _workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
-            ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+            # zeroed once; every launch leaves the workspace ready for the next one
+            ws = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
             _workspaces[key] = ws
         return ws
 

@@ -32,7 +32,7 @@ def _with_workspace(_capi, L, x, c, rev):
     rows, n = x.shape
     y = torch.empty_like(x)
     nbytes = L.linrec_b200_workspace_size(rows, n, _capi.DTYPE_F32)
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device=x.device)
     stream = torch.cuda.current_stream().cuda_stream
     rc = L.linrec_b200_fwd(_capi.KIND_PIPE, x.data_ptr(), c.data_ptr(), y.data_ptr(), rows, n, n, int(rev),
                            _capi.DTYPE_F32, None, ws.data_ptr(), nbytes, stream)
