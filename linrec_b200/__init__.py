@@ -21,7 +21,9 @@ from .ops import (  # noqa: F401
     linrec_tile_fwd,
 )
 
+from .general import linrec_general  # noqa: E402,F401
+
 linrec = linrec_pipe
 
 __version__ = "0.1.0"
-__all__ = ["linrec", "linrec_ref", "linrec_tile", "linrec_pipe", "check_status"]
+__all__ = ["linrec", "linrec_ref", "linrec_tile", "linrec_pipe", "linrec_general", "check_status"]

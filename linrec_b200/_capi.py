@@ -69,6 +69,14 @@ def _load() -> ctypes.CDLL:
     lib.linrec_b200_bwd_carry.restype = i32
     lib.linrec_b200_bwd_fixup.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
     lib.linrec_b200_bwd_fixup.restype = i32
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    lib.linrec_b200_exchange_size.argtypes = [i64, i32]
+    lib.linrec_b200_exchange_size.restype = sz
+    lib.linrec_b200_fwd_seq_p2p.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, pp, i64, ctypes.c_uint32, po, vp, sz, vp]
+    lib.linrec_b200_fwd_seq_p2p.restype = i32
+    lib.linrec_b200_bwd_seq_p2p.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, pp, i64, ctypes.c_uint32, po,
+                                            vp, sz, vp]
+    lib.linrec_b200_bwd_seq_p2p.restype = i32
     lib.linrec_b200_launch_count.argtypes = []
     lib.linrec_b200_launch_count.restype = ctypes.c_uint64
     lib.linrec_b200_strerror.argtypes = [i32]

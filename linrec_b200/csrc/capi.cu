@@ -38,6 +38,7 @@ struct Options {
     int wait_budget_ms = 2000;   // budget of every device-side wait
     int ctas_per_sm = 0;         // 0 = as many as fit
     int first_ticket = 0;        // diagnostics only: tickets start here instead of 0
+    int p2p_phase = 0;           // peer-exchange calls: 0 = scan and fix-up, 1 = scan only, 2 = fix-up only
 };
 
 int parse_options(const linrec_opts* o, Options& out)
@@ -56,6 +57,7 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "waitBudgetMs")) out.wait_budget_ms = v;
         else if (!strcmp(n, "ctasPerSm")) out.ctas_per_sm = v;
         else if (!strcmp(n, "firstTicket")) out.first_ticket = v;
+        else if (!strcmp(n, "p2pPhase")) out.p2p_phase = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
     }
     return LINREC_OK;
@@ -395,7 +397,7 @@ int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seq
 
 // The one launcher behind forward, backward and the carry-emitting forward.
 int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
-                float* carry_out, int carry_stride, int open_start, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                float* carry_out, int carry_stride, int open_start, const linrec::PeerExchange* px, int64_t numseq, int64_t seqlen, int64_t row_stride,
                 int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
                 void* stream_)
 {
@@ -419,6 +421,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.carry_out = carry_out;
     p.carry_stride = carry_stride;
     p.open_start = open_start;
+    if (px) p.px = *px;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
     // the gradient scan runs against the direction of the forward pass
@@ -463,12 +466,8 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     long long grid = (long long)dev.sm_count * occ;
     if (grid > pl.ntiles) grid = pl.ntiles;
 
-    // The workspace cleans up after every launch by itself (see scan_core.cuh); nothing to prepare
-    // here, except for the diagnostics option that moves the first ticket.
-    if (opt.first_ticket != 0) {
-        linrec::linrec_set_first_ticket_kernel<<<1, 32, 0, stream>>>(p.header, (uint32_t)opt.first_ticket);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-    }
+    // The workspace cleans up after every launch by itself (see scan_core.cuh): nothing to prepare.
+    p.first_ticket = (uint32_t)opt.first_ticket;
 
     if (pl.tma) {
         CUtensorMap m[5];
@@ -518,18 +517,20 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
 }
 
 int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
-                 int64_t numseq, int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
-                 void* stream_)
+                 const linrec::PeerExchange* px, uint32_t* status_word, int64_t numseq, int64_t seqlen,
+                 int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_)
 {
     const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
-    if (!carries && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    if (!carries && !px && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     int rc = check_common(ptrs, 2, numseq, seqlen, row_stride, dtype);
     if (rc != LINREC_OK) return rc;
     if (bwd && (!out1 || !yin) && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
     if (numseq == 0 || seqlen == 0) return LINREC_OK;
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
-    if (holds_scan_start(asc, shard, nshards) && !bwd) return LINREC_OK;   // nothing enters this shard
+    // nothing enters the shard that holds the scan start; with a peer exchange the kernel still runs
+    // because it is the one that acknowledges the epoch to the other ranks
+    if (holds_scan_start(asc, shard, nshards) && !bwd && !px) return LINREC_OK;
     DeviceInfo dev;
     rc = device_info(dev);
     if (rc != LINREC_OK) return rc;
@@ -537,6 +538,9 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     fp.out0 = out0; fp.out1 = out1; fp.c = c; fp.yin = yin; fp.carries = carries;
     fp.numseq = numseq; fp.seqlen = seqlen; fp.row_stride = row_stride;
     fp.shard = shard; fp.nshards = nshards; fp.rec = bwd ? 4 : 2;
+    if (px) fp.px = *px;
+    fp.status = status_word;
+    fp.wait_budget = 2000LL * dev.clock_khz;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     return dtype == LINREC_DTYPE_F32 ? launch_fixup_t<float>(bwd, asc, fp, stream, dev.sm_count)
                                      : launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count);
@@ -566,7 +570,7 @@ int linrec_b200_fwd(int kind, const void* x, const void* c, void* y, int64_t num
                     int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
                     size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, numseq, seqlen, row_stride, reverse,
+    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride, reverse,
                        dtype, opts, workspace, workspace_bytes, stream);
 }
 
@@ -574,7 +578,7 @@ int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y, void
                     int64_t seqlen, int64_t row_stride, int reverse, int dtype, const linrec_opts* opts,
                     void* workspace, size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, 0, numseq, seqlen, row_stride, reverse, dtype, opts,
+    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride, reverse, dtype, opts,
                        workspace, workspace_bytes, stream);
 }
 
@@ -678,15 +682,15 @@ int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
     if (!records && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
     const int open = holds_scan_start(reverse == 0, shard, nshards) ? 0 : 1;
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, records, 2, open, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, records, 2, open, nullptr, numseq, seqlen, row_stride,
                        reverse, dtype, opts, workspace, workspace_bytes, stream);
 }
 
 int linrec_b200_fwd_fixup(void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
                           int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream)
 {
-    return launch_fixup(false, y, nullptr, c, nullptr, records, numseq, seqlen, row_stride, reverse, dtype, shard,
-                        nshards, stream);
+    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, nullptr, numseq, seqlen, row_stride, reverse, dtype,
+                        shard, nshards, stream);
 }
 
 int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx, void* dc, float* records,
@@ -697,28 +701,77 @@ int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx
     if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
     const bool asc = reverse != 0;   // the gradient scan runs against the forward direction
     const int open = holds_scan_start(asc, shard, nshards) ? 0 : 1;
-    int rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, records, 4, open, numseq, seqlen, row_stride, reverse,
-                         dtype, opts, workspace, workspace_bytes, stream_);
-    if (rc != LINREC_OK || numseq == 0 || seqlen == 0) return rc;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    const unsigned blocks = (unsigned)ceil_div(numseq, 128);
-    if (dtype == LINREC_DTYPE_F32) {
-        if (asc) linrec::linrec_edges_kernel<float, true><<<blocks, 128, 0, stream>>>((const float*)c, (const float*)y, records, numseq, seqlen, row_stride);
-        else     linrec::linrec_edges_kernel<float, false><<<blocks, 128, 0, stream>>>((const float*)c, (const float*)y, records, numseq, seqlen, row_stride);
-    } else {
-        using B = __nv_bfloat16;
-        if (asc) linrec::linrec_edges_kernel<B, true><<<blocks, 128, 0, stream>>>((const B*)c, (const B*)y, records, numseq, seqlen, row_stride);
-        else     linrec::linrec_edges_kernel<B, false><<<blocks, 128, 0, stream>>>((const B*)c, (const B*)y, records, numseq, seqlen, row_stride);
-    }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+    // the scan kernel writes the whole record, edge elements included
+    return launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, records, 4, open, nullptr, numseq, seqlen, row_stride,
+                       reverse, dtype, opts, workspace, workspace_bytes, stream_);
 }
 
 int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y, const float* records, int64_t numseq,
                           int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
                           void* stream)
 {
-    return launch_fixup(true, dx, dc, c, y, records, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
+    return launch_fixup(true, dx, dc, c, y, records, nullptr, nullptr, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
+                        stream);
+}
+
+// ---- sequence sharding with a peer exchange instead of a collective call ---------------------------------
+size_t linrec_b200_exchange_size(int64_t max_rows, int nranks)
+{
+    if (max_rows < 1 || nranks < 1 || nranks > linrec::kMaxPeers) return 0;
+    return linrec::px_total_bytes(max_rows, nranks);
+}
+
+static int make_exchange(linrec::PeerExchange& px, void* const* peer_bufs, int64_t max_rows, uint32_t epoch, int shard,
+                         int nshards, int64_t numseq)
+{
+    if (!peer_bufs || nshards < 1 || nshards > linrec::kMaxPeers || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
+    if (epoch == 0 || max_rows < numseq) return LINREC_ERR_INVALID_ARG;
+    for (int i = 0; i < nshards; ++i) {
+        if (!peer_bufs[i] || reinterpret_cast<uintptr_t>(peer_bufs[i]) % 16 != 0) return LINREC_ERR_INVALID_ARG;
+        px.base[i] = peer_bufs[i];
+    }
+    px.nranks = nshards; px.me = shard; px.epoch = epoch; px.max_rows = max_rows;
+    return LINREC_OK;
+}
+
+int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                            int reverse, int dtype, int shard, int nshards, void* const* peer_bufs, int64_t max_rows,
+                            uint32_t epoch, const linrec_opts* opts, void* workspace, size_t workspace_bytes, void* stream)
+{
+    linrec::PeerExchange px{};
+    int rc = make_exchange(px, peer_bufs, max_rows, epoch, shard, nshards, numseq);
+    if (rc != LINREC_OK) return rc;
+    Options opt;
+    rc = parse_options(opts, opt);
+    if (rc != LINREC_OK) return rc;
+    const int open = holds_scan_start(reverse == 0, shard, nshards) ? 0 : 1;
+    if (opt.p2p_phase != 2)
+        rc = launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, open, &px, numseq, seqlen, row_stride,
+                         reverse, dtype, opts, workspace, workspace_bytes, stream);
+    if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
+    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, &px, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen,
+                        row_stride, reverse, dtype, shard, nshards, stream);
+}
+
+int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* dx, void* dc, int64_t numseq,
+                            int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
+                            void* const* peer_bufs, int64_t max_rows, uint32_t epoch, const linrec_opts* opts,
+                            void* workspace, size_t workspace_bytes, void* stream)
+{
+    linrec::PeerExchange px{};
+    int rc = make_exchange(px, peer_bufs, max_rows, epoch, shard, nshards, numseq);
+    if (rc != LINREC_OK) return rc;
+    Options opt;
+    rc = parse_options(opts, opt);
+    if (rc != LINREC_OK) return rc;
+    const bool asc = reverse != 0;
+    const int open = holds_scan_start(asc, shard, nshards) ? 0 : 1;
+    if (opt.p2p_phase != 2)
+        rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, nullptr, 0, open, &px, numseq, seqlen, row_stride, reverse,
+                         dtype, opts, workspace, workspace_bytes, stream);
+    if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
+    return launch_fixup(true, dx, dc, c, y, nullptr, &px, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen, row_stride,
+                        reverse, dtype, shard, nshards, stream);
 }
 
 // ---- forward scan on a built-in scratch buffer ----------------------------------------------------
@@ -774,7 +827,7 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
     if (rc != LINREC_OK) return rc;
     // launch_scan rewrites the header words and zeroes the descriptors this call uses, so whatever
     // an earlier call left in the buffer does not matter
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride,
                        reverse, dtype, nullptr, scratch, (size_t)LINREC_STATIC_SCRATCH_BYTES, stream);
 }
 

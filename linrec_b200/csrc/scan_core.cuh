@@ -34,6 +34,7 @@ namespace linrec {
 constexpr int kHeaderBytes = 256;
 constexpr uint32_t kStatusLookbackTimeout = 1u;
 constexpr uint32_t kStatusCopyTimeout = 2u;
+constexpr uint32_t kStatusPeerTimeout = 4u;
 
 // One look-back descriptor per chained tile: 16 bytes that are always read and written with ONE
 // 128-bit access, so that a reader sees the status together with the value it belongs to.
@@ -60,6 +61,73 @@ __device__ __forceinline__ Pair combine(Pair far, Pair near)
     return Pair{fmaf(far.y, near.p, near.y), far.p * near.p};
 }
 
+// ---- peer exchange (sequence sharding without a collective call) ------------------------------------
+// Every rank owns one exchange buffer that all ranks of the node can address (peer-mapped memory).
+// A rank's scan kernel stores each row's record directly into the buffer of EVERY rank and then
+// releases a per-row flag there; the fix-up kernel of a rank waits on the flags in its OWN buffer.
+// Slots are double-buffered by the parity of the exchange epoch, and a rank acknowledges an epoch to
+// all peers when its fix-up has finished, so that a slot is only overwritten (two epochs later)
+// after every reader is done with it.
+//   records [2][nranks][max_rows] x 16 B   (P, Y, c_edge, y_edge)
+//   flags   [2][nranks][max_rows] x 4 B    epoch of the record
+//   acks    [nranks] x 4 B                 last epoch rank i has finished reading
+//   done    4 B                            fix-up CTAs finished (local bookkeeping)
+constexpr int kMaxPeers = 16;
+struct PeerExchange {
+    void* base[kMaxPeers];   // base[i]: rank i's exchange buffer as mapped here (base[me] is local)
+    int nranks, me;
+    uint32_t epoch;          // 0: no peer exchange in this launch; real epochs start at 1
+    long long max_rows;
+};
+__host__ __device__ inline size_t px_flags_offset(long long max_rows, int nranks) { return (size_t)2 * nranks * max_rows * 16; }
+__host__ __device__ inline size_t px_acks_offset(long long max_rows, int nranks)
+{
+    return (px_flags_offset(max_rows, nranks) + (size_t)2 * nranks * max_rows * 4 + 255) / 256 * 256;
+}
+__host__ __device__ inline size_t px_done_offset(long long max_rows, int nranks) { return px_acks_offset(max_rows, nranks) + 256; }
+__host__ __device__ inline size_t px_total_bytes(long long max_rows, int nranks) { return px_done_offset(max_rows, nranks) + 256; }
+__device__ __forceinline__ float4* px_record(const PeerExchange& px, int buf_of, int par, int from, long long row)
+{
+    return reinterpret_cast<float4*>(px.base[buf_of]) + ((size_t)(par * px.nranks + from) * px.max_rows + row);
+}
+__device__ __forceinline__ uint32_t* px_flag(const PeerExchange& px, int buf_of, int par, int from, long long row)
+{
+    return reinterpret_cast<uint32_t*>(static_cast<char*>(px.base[buf_of]) + px_flags_offset(px.max_rows, px.nranks)) +
+           ((size_t)(par * px.nranks + from) * px.max_rows + row);
+}
+__device__ __forceinline__ uint32_t* px_ack(const PeerExchange& px, int buf_of, int of_rank)
+{
+    return reinterpret_cast<uint32_t*>(static_cast<char*>(px.base[buf_of]) + px_acks_offset(px.max_rows, px.nranks)) + of_rank;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_f32x4(float4* p, float4 v)
+{
+    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+// Bounded wait until *p has reached `target` (epochs only grow); false when the budget ran out.
+__device__ __forceinline__ bool wait_epoch_reached(const uint32_t* p, uint32_t target, long long budget)
+{
+    if ((int32_t)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    const long long t0 = clock64();
+    unsigned ns = 64;
+    while ((int32_t)(ld_acquire_sys_u32(p) - target) < 0) {
+        if (clock64() - t0 > budget) return false;
+        __nanosleep(ns);
+        if (ns < 2048) ns <<= 1;
+    }
+    return true;
+}
+
 // ---- kernel parameters --------------------------------------------------------------------------
 struct ScanParams {
     const void* in0;   // forward: x        backward: dy
@@ -80,7 +148,11 @@ struct ScanParams {
     int carry_stride;    // floats between the records of consecutive rows in carry_out
     int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
                          //    coefficient that lies before the shard is taken as 1 (folded in later)
+    uint32_t first_ticket;  // diagnostics: added to every ticket (0 in normal use)
+    PeerExchange px;        // sequence sharding: where the rows' records are pushed (epoch 0: nowhere)
 };
+
+// Storage helpers are declared further down; the record emitter needs them, so it follows them.
 
 // ---- storage-type helpers -----------------------------------------------------------------------
 template <typename ST>
@@ -130,6 +202,47 @@ struct Storage<__nv_bfloat16> {
     __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
 };
+
+// Sequence sharding: the record of one row of this shard -- (P, Y) of the whole shard and, for the
+// backward pass, c at the shard's scan-last element and y at its scan-first element (what the
+// neighbouring shards need).  Written to the local record array and/or pushed to every peer.
+template <typename ST, bool BWD, bool ASC>
+__device__ __forceinline__ void emit_record(const ScanParams& p, long long row, Pair tot)
+{
+    float ce = 0.0f, ye = 0.0f;
+    if (BWD) {
+        const long long first = ASC ? 0 : p.seqlen - 1, last = ASC ? p.seqlen - 1 : 0;
+        ce = Storage<ST>::to_float(reinterpret_cast<const ST*>(p.c)[row * p.row_stride + last]);
+        ye = Storage<ST>::to_float(reinterpret_cast<const ST*>(p.yin)[row * p.row_stride + first]);
+    }
+    if (p.carry_out) {
+        float* r = p.carry_out + p.carry_stride * row;
+        r[0] = tot.p;
+        r[1] = tot.y;
+        if (BWD && p.carry_stride >= 4) {
+            r[2] = ce;
+            r[3] = ye;
+        }
+    }
+    if (p.px.epoch != 0u) {
+        const int par = (int)(p.px.epoch & 1u);
+        const float4 rec = make_float4(tot.p, tot.y, ce, ye);
+        for (int i = 0; i < p.px.nranks; ++i) {
+            st_relaxed_sys_f32x4(px_record(p.px, i, par, p.px.me, row), rec);
+            st_release_sys_u32(px_flag(p.px, i, par, p.px.me, row), p.px.epoch);
+        }
+    }
+}
+
+// Before a launch pushes records of epoch e it makes sure that every rank has acknowledged epoch
+// e-2, whose slots it is about to overwrite (lanes 0..nranks-1 of the calling warp check one rank each).
+__device__ __forceinline__ void wait_for_slot_release(const ScanParams& p, int lane)
+{
+    if (p.px.epoch >= 3u && lane < p.px.nranks) {
+        if (!wait_epoch_reached(px_ack(p.px, p.px.me, lane), p.px.epoch - 2u, p.wait_budget))
+            atomicOr(p.header + 1, kStatusPeerTimeout);
+    }
+}
 
 // Byte offset of slot `i` inside a swizzled tile buffer (buffer base 1024-byte aligned).
 template <typename ST>

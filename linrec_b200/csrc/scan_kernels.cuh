@@ -61,7 +61,7 @@ struct ChainShared {
 // is in shared memory before the barrier and nobody waits for the look-back.  Slow path: publish
 // the aggregate, walk back over the predecessors, one more barrier.  Either way the warp then
 // fetches the descriptor that the NEXT tile (`next_tk`) will want.
-template <int E, int NT, bool BWD, bool ASC, typename AfterRead>
+template <typename ST, int E, int NT, bool BWD, bool ASC, typename AfterRead>
 __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g,
                                           const Operands<E, BWD>& op, const TileCoord& tc,
                                           uint32_t tk, uint32_t next_tk, uint32_t epoch, uint4& probe, Pair* wagg,
@@ -107,11 +107,7 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
                     cs->tprefix = tp;
                 }
             }
-            if (g.lane == 0 && last_piece && p.carry_out) {
-                const Pair tot = combine(tp, bagg);
-                p.carry_out[p.carry_stride * tc.row] = tot.p;
-                p.carry_out[p.carry_stride * tc.row + 1] = tot.y;
-            }
+            if (g.lane == 0 && last_piece && (p.carry_out || p.px.epoch)) emit_record<ST, BWD, ASC>(p, tc.row, combine(tp, bagg));
             // fetch ahead what the next tile of this CTA will ask for
             probe = make_uint4(0u, 0u, 0u, 0u);
             if (next_tk < (uint32_t)p.ntiles && next_tk >= (uint32_t)p.numseq)
@@ -122,13 +118,9 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
     }
     if (g.need_wp) pre = combine(pre, wp);
     pre = combine(pre, ts.excl);
-    if (!p.chain && p.carry_out && g.k == g.tpr - 1 && g.row_in_tile < p.rows_per_tile) {
+    if (!p.chain && (p.carry_out || p.px.epoch) && g.k == g.tpr - 1 && g.row_in_tile < p.rows_per_tile) {
         const long long row = tc.row + g.row_in_tile;
-        if (row < p.numseq) {
-            const Pair tot = combine(pre, ts.agg);
-            p.carry_out[p.carry_stride * row] = tot.p;
-            p.carry_out[p.carry_stride * row + 1] = tot.y;
-        }
+        if (row < p.numseq) emit_record<ST, BWD, ASC>(p, row, combine(pre, ts.agg));
     }
     apply_carry<E, BWD, ASC>(op, pre.y, o0, o1);
 }
@@ -180,6 +172,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
                                  : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
 
+    if (tid < 32) wait_for_slot_release(p, tid);
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
@@ -224,14 +217,20 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         if (BWD) ptx::tma_load_3d(in_buf(s, 2), &tm_y, &full[s], 0, c1, c2);
     };
 
-    uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket drawn one step ahead
+    // Tickets.  The first S+1 tickets of every CTA are fixed round-robin (ticket = round*grid + CTA), so
+    // that neighbouring tickets start on different CTAs at the same time; drawing them from the counter
+    // would hand each CTA S+1 CONSECUTIVE tickets, and with few rows those are consecutive pieces of
+    // one row that would wait for each other across CTAs.  All later tickets come from the counter.
+    const uint32_t grid = gridDim.x;
+    const uint32_t dyn_base = p.first_ticket + (uint32_t)(S + 1) * grid;
+    uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket held one step ahead
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
-            const uint32_t tk = atomicAdd(p.header, 1u);
+            const uint32_t tk = p.first_ticket + (uint32_t)s * grid + blockIdx.x;
             tile_of_stage[s] = tk;
             if (tk < ntiles) issue(s, tk);
         }
-        next_ticket = atomicAdd(p.header, 1u);
+        next_ticket = p.first_ticket + (uint32_t)S * grid + blockIdx.x;
     }
     __syncthreads();
 
@@ -273,7 +272,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
                                                  tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         bool alive = true;
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+        tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             // the output buffer about to be reused must have been drained by its bulk store
             if (tid == 0) ptx::tma_wait_group_read<OB - 1>();
             __syncthreads();
@@ -284,7 +283,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             if (tid == 0) {   // ring slot s is free again: refill it with the ticket drawn earlier
                 tile_of_stage[s] = next_ticket;
                 if (next_ticket < ntiles) issue(s, next_ticket);
-                next_ticket = atomicAdd(p.header, 1u);
+                next_ticket = dyn_base + atomicAdd(p.header, 1u);
             }
             return true;
         });
@@ -343,9 +342,14 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     ST* gout0 = reinterpret_cast<ST*>(p.out0);
     ST* gout1 = reinterpret_cast<ST*>(p.out1);
     const int spr = p.chain ? T : p.slots_per_row;
+    if (tid < 32) wait_for_slot_release(p, tid);
 
+    bool first_round = true;
     for (;;) {
-        if (tid == 0) ticket_s = atomicAdd(p.header, 1u);
+        // first ticket fixed (one per CTA), later ones from the counter
+        if (tid == 0)
+            ticket_s = first_round ? p.first_ticket + blockIdx.x : p.first_ticket + gridDim.x + atomicAdd(p.header, 1u);
+        first_round = false;
         __syncthreads();   // also: everybody has finished storing the previous tile
         const uint32_t tk = ticket_s;
         if (tk >= ntiles) break;
@@ -388,7 +392,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
                                                   (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
         float o0[E], o1[BWD ? E : 1];
         uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // no look-ahead here: the linking warp probes when it needs to
-        tile_scan<E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+        tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             __syncthreads();
             return true;
         });
@@ -453,13 +457,6 @@ __global__ void linrec_seq_kernel(const ScanParams p, int reverse)
     }
 }
 
-// =================================================================================================
-//  Workspace header: diagnostics hook
-// =================================================================================================
-// Diagnostics only: lets the tickets of the next launch start past the first tiles.
-__global__ void linrec_set_first_ticket_kernel(uint32_t* header, uint32_t first_ticket)
-{
-    if (threadIdx.x == 0) header[0] = first_ticket;
-}
+
 
 }  // namespace linrec

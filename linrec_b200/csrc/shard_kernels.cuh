@@ -28,7 +28,23 @@ struct FixupParams {
     long long numseq, seqlen, row_stride;
     int shard, nshards;
     int rec;             // floats per record: 2 forward, 4 backward
+    PeerExchange px;     // epoch != 0: the records arrive in this rank's exchange buffer (16-byte records,
+                         // one flag per row and sender) instead of `carries`
+    long long wait_budget;   // clock ticks a wait for a peer's record may last
+    uint32_t* status;    // status word that receives kStatusPeerTimeout
 };
+
+// Where the record of (shard s, row) is, once it is known to have arrived.
+__device__ __forceinline__ const float* fixup_record(const FixupParams& p, int s, long long row)
+{
+    if (p.px.epoch != 0u) {
+        const int par = (int)(p.px.epoch & 1u);
+        if (!wait_epoch_reached(px_flag(p.px, p.px.me, par, s, row), p.px.epoch, p.wait_budget))
+            atomicOr(p.status, kStatusPeerTimeout);
+        return reinterpret_cast<const float*>(px_record(p.px, p.px.me, par, s, row));
+    }
+    return p.carries + ((long long)s * p.numseq + row) * p.rec;
+}
 
 // Shards in scan order: ascending scans visit shard 0 first, descending scans the last shard first.
 template <bool ASC>
@@ -112,14 +128,16 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
         if (tid == 0) {
             float v = 0.0f;
             int prev = -1;
+            float prev_edge = 1.0f;   // c at the scan-last element of the shard folded last
             for (int n = 0; n < my_pos; ++n) {
                 const int s = shard_at<ASC>(n, p.nshards);
-                const float* rec = p.carries + ((long long)s * p.numseq + row) * p.rec;
-                if (BWD && prev >= 0) v *= p.carries[((long long)prev * p.numseq + row) * p.rec + 2];
+                const volatile float* rec = fixup_record(p, s, row);
+                if (BWD && prev >= 0) v *= prev_edge;
                 v = fmaf(v, rec[0], rec[1]);
+                if (BWD) prev_edge = rec[2];
                 prev = s;
             }
-            if (BWD && prev >= 0) v *= p.carries[((long long)prev * p.numseq + row) * p.rec + 2];
+            if (BWD && prev >= 0) v *= prev_edge;
             v_in_s = v;
         }
         __syncthreads();
@@ -220,12 +238,22 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             __syncthreads();
             if (tid == 0 && my_pos + 1 < p.nshards) {
                 const int nxt_shard = shard_at<ASC>(my_pos + 1, p.nshards);
-                const float y_edge = p.carries[((long long)nxt_shard * p.numseq + row) * p.rec + 3];
+                const float y_edge = reinterpret_cast<const volatile float*>(fixup_record(p, nxt_shard, row))[3];
                 const long long last = ASC ? L - 1 : 0;
                 o1[last] = Storage<ST>::from_float(Storage<ST>::to_float(o0[last]) * y_edge);
             }
         }
         __syncthreads();   // v_in_s and wprod are rewritten for the next row
+    }
+    // Peer exchange: once every CTA of this rank is done reading, tell all ranks that the slots of
+    // this epoch may be reused (they will be, two epochs from now).
+    if (p.px.epoch != 0u && tid == 0) {
+        __threadfence();
+        uint32_t* done = reinterpret_cast<uint32_t*>(static_cast<char*>(p.px.base[p.px.me]) + px_done_offset(p.px.max_rows, p.px.nranks));
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0u;
+            for (int i = 0; i < p.px.nranks; ++i) st_release_sys_u32(px_ack(p.px, i, p.px.me), p.px.epoch);
+        }
     }
 }
 

@@ -23,7 +23,7 @@ import torch.distributed as dist
 from . import _capi
 from .ops import _DTYPES, _check_same, _row_layout, _workspace, linrec_pipe
 
-__all__ = ["linrec_channel_sharded", "linrec_seq_sharded", "seq_sharded_fwd", "seq_sharded_bwd"]
+__all__ = ["linrec_channel_sharded", "linrec_seq_sharded", "seq_sharded_fwd", "seq_sharded_bwd", "PeerExchange"]
 
 
 def linrec_channel_sharded(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False) -> torch.Tensor:
@@ -97,6 +97,78 @@ class CudaShardKernels:
 _CUDA_KERNELS = CudaShardKernels()
 
 
+class PeerExchange:
+    """Exchange buffers for sequence sharding without a collective call.
+
+    Every rank allocates one buffer in symmetric (peer-mapped) memory; the scan kernels store each
+    row's record straight into all ranks' buffers over NVLink and the fix-up kernels wait on flags in
+    their own buffer, so a sharded scan is two kernel launches and nothing else.  Create one per
+    process group and reuse it for every call (`linrec_seq_sharded(..., exchange=ex)`); calls are
+    collective and must be made in the same order on all ranks.
+    """
+
+    def __init__(self, max_rows: int, group=None, device=None, peer_ptrs=None, rank=None, world=None):
+        import ctypes
+        self.max_rows = int(max_rows)
+        self.epoch = 0
+        if peer_ptrs is not None:          # buffers handed in (tests: all "ranks" on one device)
+            self.rank, self.world, ptrs = rank, world, list(peer_ptrs)
+            self._keep = None
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = group if group is not None else dist.group.WORLD
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            nbytes = _capi.lib.linrec_b200_exchange_size(self.max_rows, self.world)
+            dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+            buf.zero_()
+            handle = symm_mem.rendezvous(buf, group)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            torch.cuda.synchronize(dev)
+            handle.barrier()               # every rank's buffer is zeroed before anyone pushes into it
+            self._keep = (buf, handle)
+        self.ptr_array = (ctypes.c_void_p * self.world)(*ptrs)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def _env(self, ref, numseq, seqlen):
+        stream = torch.cuda.current_stream(ref.device).cuda_stream
+        dtype = _DTYPES[ref.dtype]
+        ws = _workspace(ref.device, stream, _capi.lib.linrec_b200_workspace_size(numseq, seqlen, dtype))
+        return stream, dtype, ws
+
+    def fwd(self, x, c, reverse, opts=None):
+        (x, c), (numseq, seqlen, stride) = CudaShardKernels._prep(x, c)
+        if numseq > self.max_rows:
+            raise RuntimeError("linrec: more rows than the peer exchange was created for")
+        y = torch.empty_like(x)
+        o, keep = _capi.make_opts(opts or {})
+        with torch.cuda.device(x.device):
+            stream, dtype, ws = self._env(x, numseq, seqlen)
+            rc = _capi.lib.linrec_b200_fwd_seq_p2p(x.data_ptr(), c.data_ptr(), y.data_ptr(), numseq, seqlen, stride,
+                                                   int(bool(reverse)), dtype, self.rank, self.world, self.ptr_array,
+                                                   self.max_rows, self.next_epoch(), o, ws.data_ptr(), ws.numel(), stream)
+        _capi.raise_for(rc, "linrec_b200_fwd_seq_p2p")
+        return y
+
+    def bwd(self, dy, c, y, reverse, opts=None):
+        (dy, c, y), (numseq, seqlen, stride) = CudaShardKernels._prep(dy, c, y)
+        if numseq > self.max_rows:
+            raise RuntimeError("linrec: more rows than the peer exchange was created for")
+        dx, dc = torch.empty_like(dy), torch.empty_like(dy)
+        o, keep = _capi.make_opts(opts or {})
+        with torch.cuda.device(dy.device):
+            stream, dtype, ws = self._env(dy, numseq, seqlen)
+            rc = _capi.lib.linrec_b200_bwd_seq_p2p(dy.data_ptr(), c.data_ptr(), y.data_ptr(), dx.data_ptr(), dc.data_ptr(),
+                                                   numseq, seqlen, stride, int(bool(reverse)), dtype, self.rank, self.world,
+                                                   self.ptr_array, self.max_rows, self.next_epoch(), o, ws.data_ptr(),
+                                                   ws.numel(), stream)
+        _capi.raise_for(rc, "linrec_b200_bwd_seq_p2p")
+        return dx, dc
+
+
 def _gather(records: torch.Tensor, group) -> torch.Tensor:
     """All-gather of the per-row records in rank order: result[(rank, row, k)]."""
     world = dist.get_world_size(group)
@@ -106,8 +178,12 @@ def _gather(records: torch.Tensor, group) -> torch.Tensor:
     return out.view((world, rows) + tuple(records.shape[1:]))
 
 
-def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None):
-    """Forward scan of a row that is split over the ranks of `group` (this rank holds shard `rank`)."""
+def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None, exchange=None):
+    """Forward scan of a row that is split over the ranks of `group` (this rank holds shard `rank`).
+    With `exchange` (a PeerExchange) the records travel by peer stores inside the kernels; without it
+    by one all-gather."""
+    if exchange is not None:
+        return exchange.fwd(x, c, reverse)
     k = kernels or _CUDA_KERNELS
     shard, nshards = dist.get_rank(group), dist.get_world_size(group)
     y, rec = k.fwd_carry(x, c, reverse, shard, nshards)
@@ -118,8 +194,10 @@ def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, gro
 
 
 def seq_sharded_bwd(dy: torch.Tensor, c: torch.Tensor, y: torch.Tensor, reverse: bool = False, group=None,
-                    kernels=None):
+                    kernels=None, exchange=None):
     """Backward of `seq_sharded_fwd`: (dx, dc) of this rank's shard; `y` is the forward output shard."""
+    if exchange is not None:
+        return exchange.bwd(dy, c, y, reverse)
     k = kernels or _CUDA_KERNELS
     shard, nshards = dist.get_rank(group), dist.get_world_size(group)
     dx, dc, rec, c2, y2 = k.bwd_carry(dy, c, y, reverse, shard, nshards)
@@ -131,10 +209,10 @@ def seq_sharded_bwd(dy: torch.Tensor, c: torch.Tensor, y: torch.Tensor, reverse:
 
 class _SeqShardedFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, c, reverse, group):
-        y = seq_sharded_fwd(x, c, reverse, group)
+    def forward(ctx, x, c, reverse, group, exchange):
+        y = seq_sharded_fwd(x, c, reverse, group, exchange=exchange)
         ctx.save_for_backward(c, y)
-        ctx.reverse, ctx.group = reverse, group
+        ctx.reverse, ctx.group, ctx.exchange = reverse, group, exchange
         return y
 
     @staticmethod
@@ -142,10 +220,12 @@ class _SeqShardedFn(torch.autograd.Function):
         c, y = ctx.saved_tensors
         if dy.stride() != c.stride():
             dy = torch.empty_like(c).copy_(dy)
-        dx, dc = seq_sharded_bwd(dy, c, y, ctx.reverse, ctx.group)
-        return dx, dc, None, None
+        dx, dc = seq_sharded_bwd(dy, c, y, ctx.reverse, ctx.group, exchange=ctx.exchange)
+        return dx, dc, None, None, None
 
 
-def linrec_seq_sharded(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False, group=None) -> torch.Tensor:
-    """Differentiable scan over a sequence that is sharded across the ranks of `group`."""
-    return _SeqShardedFn.apply(inputs, coeffs, reverse, group)
+def linrec_seq_sharded(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False, group=None,
+                       exchange=None) -> torch.Tensor:
+    """Differentiable scan over a sequence that is sharded across the ranks of `group`; `exchange`
+    (a PeerExchange) selects the peer-store path instead of the all-gather."""
+    return _SeqShardedFn.apply(inputs, coeffs, reverse, group, exchange)

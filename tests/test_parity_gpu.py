@@ -232,6 +232,65 @@ def test_guard_bands_untouched():
                     assert not torch.any(body[:, :L] == -777.0)
 
 
+def test_general_signature_logc_and_dim():
+    """logc and dim of the reference's Python operator; gradients against fp64 autograd through the
+    plain recurrence (the derivative of the forward that is actually computed)."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(3)
+    x = torch.randn(4, 300, 6, generator=g)
+    logc = torch.log(0.5 + 0.5 * torch.rand(4, 300, 6, generator=g))
+    dy = torch.randn(4, 300, 6, generator=g)
+    for rev in (False, True):
+        xd, ld = x.to(dev).requires_grad_(True), logc.to(dev).requires_grad_(True)
+        y = lb.linrec_general(xd, ld, logc=True, dim=1, reverse=rev)
+        gx, gl = torch.autograd.grad(y, (xd, ld), dy.to(dev))
+        x64, l64 = x.double().requires_grad_(True), logc.double().requires_grad_(True)
+        c64 = torch.exp(l64)
+        prev = torch.zeros(4, 6, dtype=torch.float64)
+        outs = [None] * 300
+        for i in (range(299, -1, -1) if rev else range(300)):
+            prev = prev * c64[:, i] + x64[:, i]
+            outs[i] = prev
+        y64 = torch.stack(outs, dim=1)
+        rx, rl = torch.autograd.grad(y64, (x64, l64), dy.double())
+        np.testing.assert_allclose(y.detach().cpu().numpy(), y64.detach().numpy(), rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gx.cpu().numpy(), rx.numpy(), rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gl.cpu().numpy(), rl.numpy(), rtol=RTOL, atol=2 * ATOL)
+
+
+try:
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    _HAVE_HYPOTHESIS = True
+except Exception:  # pragma: no cover
+    _HAVE_HYPOTHESIS = False
+
+if _HAVE_HYPOTHESIS:
+    @settings(max_examples=60, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+    @given(rows=st.integers(1, 40), length=st.integers(1, 5000), pad=st.integers(0, 9), off=st.integers(0, 5),
+           rev=st.booleans(), seed=st.integers(0, 1000))
+    def test_fuzz_small_shapes(rows, length, pad, off, rev, seed):
+        """Random small shapes, row strides and base offsets, both directions, forward and backward."""
+        lb = _ops()
+        dev = torch.device("cuda:0")
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        stride = length + pad
+        n = rows * stride + off
+        bx, bc, bd = torch.randn(n, generator=g), 0.3 + 0.7 * torch.rand(n, generator=g), torch.randn(n, generator=g)
+        view = lambda t: torch.as_strided(t, (rows, length), (stride, 1), off)
+        xh, ch, dh = (view(t).contiguous() for t in (bx, bc, bd))
+        xd, cd, dd = (view(t.to(dev)) for t in (bx, bc, bd))
+        y = lb.linrec(xd, cd, reverse=rev)
+        y_ref = oracle.fwd_f32(xh.numpy(), ch.numpy(), reverse=rev)
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+        yv = view(torch.zeros(n).to(dev))
+        yv.copy_(torch.from_numpy(y_ref))
+        dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dd, coeffs=cd, outputs=yv, reverse=rev)
+        dx_ref, dc_ref = oracle.bwd_f32(dh.numpy(), ch.numpy(), y_ref, reverse=rev)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
+
+
 def test_host_streamed_path():
     """Tensors in host memory, streamed through the device in row slabs (ragged last slab)."""
     from linrec_b200 import host

@@ -90,6 +90,56 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
     linrec_b200.check_status()
 
 
+@pytest.mark.parametrize("rows,L,G,clo", [(6, 4 * 96, 4, 0.5), (3, 2 * 8192 * 3, 2, 0.9), (5, 3 * 2080, 3, 0.99), (40, 8 * 512, 8, 0.3)],
+                         ids=["short", "chained", "ragged", "eight"])
+def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
+    """The peer-store path with every "rank" on one device: G exchange buffers in local memory, scan
+    phase of all ranks first, then the fix-up phase of all ranks (so no launch ever waits for a later
+    one).  Four exchanges in a row (forward and backward, both directions) exercise slot reuse and the
+    acknowledgements."""
+    import ctypes
+    from linrec_b200 import _capi
+    dev = torch.device("cuda:0")
+    nbytes = _capi.lib.linrec_b200_exchange_size(rows, G)
+    assert nbytes > 0
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(G)]
+    x, c, dy = _data((rows, L), clo, seed=11)
+    Ls = L // G
+    cut = lambda t, s: t[:, s * Ls:(s + 1) * Ls].contiguous().to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = torch.zeros(_capi.lib.linrec_b200_workspace_size(rows, Ls, 0), dtype=torch.uint8, device=dev)
+    ptrs = (ctypes.c_void_p * G)(*[b.data_ptr() for b in bufs])
+    epoch = 0
+    for rev in (False, True, False):
+        y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+        dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+        xs, cs, dys = ([cut(t, s) for s in range(G)] for t in (x, c, dy))
+        ygs = [cut(torch.from_numpy(y_ref), s) for s in range(G)]
+        ys = [torch.empty_like(t) for t in xs]
+        dxs, dcs = [torch.empty_like(t) for t in xs], [torch.empty_like(t) for t in xs]
+        epoch += 1
+        for phase in (1, 2):
+            o, keep = _capi.make_opts({"p2pPhase": phase})
+            for s in range(G):
+                rc = _capi.lib.linrec_b200_fwd_seq_p2p(xs[s].data_ptr(), cs[s].data_ptr(), ys[s].data_ptr(), rows, Ls, Ls,
+                                                       int(rev), 0, s, G, ptrs, rows, epoch, o, ws.data_ptr(), ws.numel(), stream)
+                assert rc == 0, _capi.strerror(rc)
+        epoch += 1
+        for phase in (1, 2):
+            o, keep = _capi.make_opts({"p2pPhase": phase})
+            for s in range(G):
+                rc = _capi.lib.linrec_b200_bwd_seq_p2p(dys[s].data_ptr(), cs[s].data_ptr(), ygs[s].data_ptr(), dxs[s].data_ptr(),
+                                                       dcs[s].data_ptr(), rows, Ls, Ls, int(rev), 0, s, G, ptrs, rows, epoch, o,
+                                                       ws.data_ptr(), ws.numel(), stream)
+                assert rc == 0, _capi.strerror(rc)
+        torch.cuda.synchronize()
+        assert _capi.lib.linrec_b200_status(ws.data_ptr(), stream) == 0
+        cat = lambda ts: torch.cat([t.cpu() for t in ts], dim=1).numpy()
+        np.testing.assert_allclose(cat(ys), y_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(cat(dxs), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(cat(dcs), dc_ref, rtol=RTOL, atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+
+
 def _nccl_worker(rank, world, port, tmp):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -99,8 +149,9 @@ def _nccl_worker(rank, world, port, tmp):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         import linrec_b200
-        from linrec_b200.sharded import linrec_seq_sharded
+        from linrec_b200.sharded import PeerExchange, linrec_seq_sharded
         rows, L = 12, world * 3 * 4096
+        exchange = PeerExchange(rows)
         Ls = L // world
         x, c, dy = _data((rows, L), 0.9, seed=77)
         sl = slice(rank * Ls, (rank + 1) * Ls)
@@ -115,6 +166,15 @@ def _nccl_worker(rank, world, port, tmp):
             torch.testing.assert_close(ys, y_full[:, sl], rtol=RTOL, atol=ATOL)
             torch.testing.assert_close(gx, gx_full[:, sl], rtol=RTOL, atol=ATOL)
             torch.testing.assert_close(gc, gc_full[:, sl], rtol=RTOL, atol=4 * ATOL)
+            # the same through peer stores instead of the all-gather (several exchanges in a row)
+            for _ in range(3):
+                xs2 = xs.detach().clone().requires_grad_(True)
+                cs2 = cs.detach().clone().requires_grad_(True)
+                ys2 = linrec_seq_sharded(xs2, cs2, reverse=rev, exchange=exchange)
+                gx2, gc2 = torch.autograd.grad(ys2, (xs2, cs2), dy[:, sl].contiguous().to(dev))
+                torch.testing.assert_close(ys2, y_full[:, sl], rtol=RTOL, atol=ATOL)
+                torch.testing.assert_close(gx2, gx_full[:, sl], rtol=RTOL, atol=ATOL)
+                torch.testing.assert_close(gc2, gc_full[:, sl], rtol=RTOL, atol=4 * ATOL)
         linrec_b200.check_status()
         open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
     finally:
