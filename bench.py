@@ -315,34 +315,52 @@ def run_ours(args):
         cs = 0.99 + 0.01 * torch.rand((rows_s, L_s), device=dev, generator=gs)
         dys = torch.randn((rows_s, L_s), device=dev, generator=gs)
 
-        def seq_step():
+        exchange = None
+        if world > 1:
+            try:
+                exchange = sharded.PeerExchange(rows_s)
+            except Exception as exc:      # symmetric memory unavailable: the all-gather path still runs
+                exchange = None
+                if rank == 0:
+                    print(f"peer exchange unavailable: {exc}", file=sys.stderr)
+
+        def seq_step(ex=None):
             if world == 1:
                 ys = C.linrec_pipe_fwd(inputs=xs, coeffs=cs, reverse=False)
                 return C.linrec_pipe_bwd(d_outputs=dys, coeffs=cs, outputs=ys, reverse=False)
-            ys = sharded.seq_sharded_fwd(xs, cs, False)
-            return sharded.seq_sharded_bwd(dys, cs, ys, False)
+            ys = sharded.seq_sharded_fwd(xs, cs, False, exchange=ex)
+            return sharded.seq_sharded_bwd(dys, cs, ys, False, exchange=ex)
 
-        for _ in range(3):
-            seq_step()
-        barrier()
         k_seq = max(1, min(args.steps, 10))
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(k_seq):
-            seq_step()
-        s1.record()
-        barrier()
-        seq_ms = s0.elapsed_time(s1)
-        if world > 1:
-            t = torch.tensor([seq_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            seq_ms = float(t.item())
+
+        def seq_time(ex):
+            for _ in range(3):
+                seq_step(ex)
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(k_seq):
+                seq_step(ex)
+            s1.record()
+            barrier()
+            ms = s0.elapsed_time(s1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms
+
+        seq_ms = seq_time(None)
+        p2p_ms = seq_time(exchange) if exchange is not None else None
         linrec_b200.check_status()
         seq_bytes = rows_s * L_s * world * 32
         seq = {"value": seq_bytes * k_seq / (seq_ms * 1e-3) / 1e9, "unit": "GB/s", "scaling": "strong",
                "workload": "fwd+bwd, (1024, 2^20) fp32 global, c~U(0.99,1), columns split over the ranks",
                "ms_per_step": seq_ms / k_seq, "steps": k_seq,
-               "collective": "one all-gather of 8 B (fwd) / 16 B (bwd) per row and rank" if world > 1 else "none"}
+               "collective": "one all-gather of 8 B (fwd) / 16 B (bwd) per row and rank" if world > 1 else "none",
+               "peer_store_exchange": None if p2p_ms is None else
+               {"value": seq_bytes * k_seq / (p2p_ms * 1e-3) / 1e9, "ms_per_step": p2p_ms / k_seq,
+                "collective": "none: records pushed into the peers' memory by the scan kernel"}}
 
     if rank != 0:
         if world > 1:

@@ -145,28 +145,31 @@ LINREC_API int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const vo
                                      int reverse, int dtype, int shard, int nshards, void* stream);
 
 /* Sequence sharding without a collective call.  Each rank owns an "exchange buffer" of
- * linrec_b200_exchange_size(max_rows, nranks) bytes that every rank of the node can address
- * (peer-mapped / symmetric memory), zeroed once.  `peer_bufs[i]` is rank i's buffer as mapped in the
- * calling process (peer_bufs[shard] is the local one).  One call = local scan whose kernel stores
- * each row's record straight into every rank's buffer and releases a per-row flag there, followed by
- * the fix-up kernel, which waits (bounded) for the flags it needs in its own buffer.  No NCCL kernel,
- * no host synchronisation.  `epoch` must be 1 for the first exchange on these buffers and grow by one
- * with every call, identically on all ranks (the calls are collective: every rank makes the same
- * sequence of them).  Slots are double-buffered by epoch parity and released by acknowledgements, so
- * ranks may run ahead of each other by at most one exchange.  A wait that runs out of its budget sets
- * the status word of `workspace` (linrec_b200_status).  No counterpart in the reference. */
+ * linrec_b200_exchange_size(max_rows, nranks) bytes, 256-byte aligned, that every rank of the node can
+ * address (peer-mapped / symmetric memory).  linrec_b200_exchange_init zeroes the local buffer and
+ * stores in it the addresses of all ranks' buffers as mapped in the calling process
+ * (peer_bufs[rank] must be the local buffer); the ranks must synchronise once after it (a barrier)
+ * before the first exchange.  One *_seq_p2p call = local scan whose kernel stores each row's record
+ * straight into every rank's buffer and releases a per-row flag there, followed by the fix-up kernel,
+ * which waits (bounded) for the flags it needs in its own buffer.  No NCCL kernel, no host
+ * synchronisation.  `epoch` must be 1 for the first exchange on these buffers and grow by one with
+ * every call, identically on all ranks (the calls are collective: every rank makes the same sequence
+ * of them, with numseq <= max_rows).  Slots are double-buffered by epoch parity and released by
+ * acknowledgements, so ranks may run ahead of each other by at most one exchange.  A wait that runs
+ * out of its budget sets the status word of `workspace` (linrec_b200_status).
+ * No counterpart in the reference. */
 LINREC_API size_t linrec_b200_exchange_size(int64_t max_rows, int nranks);
+LINREC_API int linrec_b200_exchange_init(void* local_buf, void* const* peer_bufs, int rank, int nranks,
+                                         int64_t max_rows, void* stream);
 LINREC_API int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y,
                                        int64_t numseq, int64_t seqlen, int64_t row_stride,
                                        int reverse, int dtype, int shard, int nshards,
-                                       void* const* peer_bufs, int64_t max_rows, uint32_t epoch,
-                                       const linrec_opts* opts,
+                                       void* exchange, uint32_t epoch, const linrec_opts* opts,
                                        void* workspace, size_t workspace_bytes, void* stream);
 LINREC_API int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* dx, void* dc,
                                        int64_t numseq, int64_t seqlen, int64_t row_stride,
                                        int reverse, int dtype, int shard, int nshards,
-                                       void* const* peer_bufs, int64_t max_rows, uint32_t epoch,
-                                       const linrec_opts* opts,
+                                       void* exchange, uint32_t epoch, const linrec_opts* opts,
                                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* Forward scan for callers that cannot give the library any scratch memory.

@@ -35,10 +35,10 @@ class LinrecOpts(ctypes.Structure):
 
 def _load() -> ctypes.CDLL:
     path = _build.LIB_PATH
-    if not os.path.exists(path):
-        try:
-            _build.build_library()
-        except Exception as exc:  # no nvcc, compile error, ...
+    try:
+        _build.build_library()          # no-op when the library is newer than its sources
+    except Exception as exc:            # no nvcc on this machine, compile error, ...
+        if not os.path.exists(path):
             raise ImportError(
                 f"linrec_b200: the CUDA library {path} is missing and could not be built ({exc}). "
                 "Build it with `python -m linrec_b200.build`; there is no fallback implementation."
@@ -72,9 +72,11 @@ def _load() -> ctypes.CDLL:
     pp = ctypes.POINTER(ctypes.c_void_p)
     lib.linrec_b200_exchange_size.argtypes = [i64, i32]
     lib.linrec_b200_exchange_size.restype = sz
-    lib.linrec_b200_fwd_seq_p2p.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, pp, i64, ctypes.c_uint32, po, vp, sz, vp]
+    lib.linrec_b200_exchange_init.argtypes = [vp, pp, i32, i32, i64, vp]
+    lib.linrec_b200_exchange_init.restype = i32
+    lib.linrec_b200_fwd_seq_p2p.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp, ctypes.c_uint32, po, vp, sz, vp]
     lib.linrec_b200_fwd_seq_p2p.restype = i32
-    lib.linrec_b200_bwd_seq_p2p.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, pp, i64, ctypes.c_uint32, po,
+    lib.linrec_b200_bwd_seq_p2p.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp, ctypes.c_uint32, po,
                                             vp, sz, vp]
     lib.linrec_b200_bwd_seq_p2p.restype = i32
     lib.linrec_b200_launch_count.argtypes = []

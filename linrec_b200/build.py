@@ -36,11 +36,29 @@ def _sources(*names):
     return [os.path.join(CSRC, n) for n in names]
 
 
+def _digest(deps) -> str:
+    import hashlib
+    h = hashlib.sha256()
+    for d in sorted(deps):
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
 def _stale(target: str, deps) -> bool:
-    if not os.path.exists(target):
+    """Content based (a digest of the sources is stored next to the target): file times do not
+    survive every way of copying a tree."""
+    stamp = target + ".srchash"
+    if not (os.path.exists(target) and os.path.exists(stamp)):
         return True
-    t = os.path.getmtime(target)
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(stamp) as f:
+        return f.read().strip() != _digest(deps)
+
+
+def _stamp(target: str, deps) -> None:
+    with open(target + ".srchash", "w") as f:
+        f.write(_digest(deps))
 
 
 def _all_deps():
@@ -58,6 +76,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True)
+    _stamp(LIB_PATH, _all_deps())
     return LIB_PATH
 
 
@@ -71,6 +90,7 @@ def build_executable(force: bool = False) -> str:
     cmd = [_nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-I", INCLUDE, "-o", EXE_PATH, src,
            lib, "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."]
     subprocess.run(cmd, check=True)
+    _stamp(EXE_PATH, _all_deps())
     return EXE_PATH
 
 

@@ -397,7 +397,7 @@ int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seq
 
 // The one launcher behind forward, backward and the carry-emitting forward.
 int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
-                float* carry_out, int carry_stride, int open_start, const linrec::PeerExchange* px, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                float* carry_out, int carry_stride, int open_start, const void* exchange, uint32_t px_epoch, int64_t numseq, int64_t seqlen, int64_t row_stride,
                 int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
                 void* stream_)
 {
@@ -421,7 +421,8 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.carry_out = carry_out;
     p.carry_stride = carry_stride;
     p.open_start = open_start;
-    if (px) p.px = *px;
+    p.px = static_cast<const linrec::PeerTable*>(exchange);
+    p.px_epoch = exchange ? px_epoch : 0u;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
     // the gradient scan runs against the direction of the forward pass
@@ -517,7 +518,7 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
 }
 
 int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
-                 const linrec::PeerExchange* px, uint32_t* status_word, int64_t numseq, int64_t seqlen,
+                 const void* px, uint32_t px_epoch, uint32_t* status_word, int64_t numseq, int64_t seqlen,
                  int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_)
 {
     const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
@@ -538,7 +539,8 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     fp.out0 = out0; fp.out1 = out1; fp.c = c; fp.yin = yin; fp.carries = carries;
     fp.numseq = numseq; fp.seqlen = seqlen; fp.row_stride = row_stride;
     fp.shard = shard; fp.nshards = nshards; fp.rec = bwd ? 4 : 2;
-    if (px) fp.px = *px;
+    fp.px = static_cast<const linrec::PeerTable*>(px);
+    fp.px_epoch = px ? px_epoch : 0u;
     fp.status = status_word;
     fp.wait_budget = 2000LL * dev.clock_khz;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -570,7 +572,7 @@ int linrec_b200_fwd(int kind, const void* x, const void* c, void* y, int64_t num
                     int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
                     size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride, reverse,
+    return launch_scan(kind, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, 0u, numseq, seqlen, row_stride, reverse,
                        dtype, opts, workspace, workspace_bytes, stream);
 }
 
@@ -578,7 +580,7 @@ int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y, void
                     int64_t seqlen, int64_t row_stride, int reverse, int dtype, const linrec_opts* opts,
                     void* workspace, size_t workspace_bytes, void* stream)
 {
-    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride, reverse, dtype, opts,
+    return launch_scan(kind, true, dy, c, y, dx, dc, nullptr, 0, 0, nullptr, 0u, numseq, seqlen, row_stride, reverse, dtype, opts,
                        workspace, workspace_bytes, stream);
 }
 
@@ -682,14 +684,14 @@ int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
     if (!records && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
     const int open = holds_scan_start(reverse == 0, shard, nshards) ? 0 : 1;
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, records, 2, open, nullptr, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, records, 2, open, nullptr, 0u, numseq, seqlen, row_stride,
                        reverse, dtype, opts, workspace, workspace_bytes, stream);
 }
 
 int linrec_b200_fwd_fixup(void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
                           int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream)
 {
-    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, nullptr, numseq, seqlen, row_stride, reverse, dtype,
+    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, 0u, nullptr, numseq, seqlen, row_stride, reverse, dtype,
                         shard, nshards, stream);
 }
 
@@ -702,7 +704,7 @@ int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx
     const bool asc = reverse != 0;   // the gradient scan runs against the forward direction
     const int open = holds_scan_start(asc, shard, nshards) ? 0 : 1;
     // the scan kernel writes the whole record, edge elements included
-    return launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, records, 4, open, nullptr, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, records, 4, open, nullptr, 0u, numseq, seqlen, row_stride,
                        reverse, dtype, opts, workspace, workspace_bytes, stream_);
 }
 
@@ -710,7 +712,7 @@ int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y, cons
                           int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
                           void* stream)
 {
-    return launch_fixup(true, dx, dc, c, y, records, nullptr, nullptr, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
+    return launch_fixup(true, dx, dc, c, y, records, nullptr, 0u, nullptr, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
                         stream);
 }
 
@@ -721,57 +723,63 @@ size_t linrec_b200_exchange_size(int64_t max_rows, int nranks)
     return linrec::px_total_bytes(max_rows, nranks);
 }
 
-static int make_exchange(linrec::PeerExchange& px, void* const* peer_bufs, int64_t max_rows, uint32_t epoch, int shard,
-                         int nshards, int64_t numseq)
+int linrec_b200_exchange_init(void* local_buf, void* const* peer_bufs, int rank, int nranks, int64_t max_rows, void* stream_)
 {
-    if (!peer_bufs || nshards < 1 || nshards > linrec::kMaxPeers || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
-    if (epoch == 0 || max_rows < numseq) return LINREC_ERR_INVALID_ARG;
-    for (int i = 0; i < nshards; ++i) {
-        if (!peer_bufs[i] || reinterpret_cast<uintptr_t>(peer_bufs[i]) % 16 != 0) return LINREC_ERR_INVALID_ARG;
-        px.base[i] = peer_bufs[i];
+    if (!local_buf || !peer_bufs || nranks < 1 || nranks > linrec::kMaxPeers || rank < 0 || rank >= nranks || max_rows < 1)
+        return LINREC_ERR_INVALID_ARG;
+    linrec::PeerTableArg a{};
+    for (int i = 0; i < nranks; ++i) {
+        if (!peer_bufs[i] || reinterpret_cast<uintptr_t>(peer_bufs[i]) % 256 != 0) return LINREC_ERR_INVALID_ARG;
+        a.t.base[i] = peer_bufs[i];
     }
-    px.nranks = nshards; px.me = shard; px.epoch = epoch; px.max_rows = max_rows;
-    return LINREC_OK;
+    if (peer_bufs[rank] != local_buf) return LINREC_ERR_INVALID_ARG;
+    a.t.nranks = nranks; a.t.me = rank; a.t.max_rows = max_rows;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (cudaMemsetAsync(local_buf, 0, linrec::px_total_bytes(max_rows, nranks), stream) != cudaSuccess) {
+        cudaGetLastError();
+        return LINREC_ERR_CUDA;
+    }
+    linrec::linrec_exchange_init_kernel<<<1, 32, 0, stream>>>(static_cast<linrec::PeerTable*>(local_buf), a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
 }
 
 int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen, int64_t row_stride,
-                            int reverse, int dtype, int shard, int nshards, void* const* peer_bufs, int64_t max_rows,
-                            uint32_t epoch, const linrec_opts* opts, void* workspace, size_t workspace_bytes, void* stream)
+                            int reverse, int dtype, int shard, int nshards, void* exchange, uint32_t epoch,
+                            const linrec_opts* opts, void* workspace, size_t workspace_bytes, void* stream)
 {
-    linrec::PeerExchange px{};
-    int rc = make_exchange(px, peer_bufs, max_rows, epoch, shard, nshards, numseq);
-    if (rc != LINREC_OK) return rc;
+    if (!exchange || epoch == 0 || nshards < 1 || nshards > linrec::kMaxPeers || shard < 0 || shard >= nshards)
+        return LINREC_ERR_INVALID_ARG;
     Options opt;
-    rc = parse_options(opts, opt);
+    int rc = parse_options(opts, opt);
     if (rc != LINREC_OK) return rc;
     const int open = holds_scan_start(reverse == 0, shard, nshards) ? 0 : 1;
     if (opt.p2p_phase != 2)
-        rc = launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, open, &px, numseq, seqlen, row_stride,
-                         reverse, dtype, opts, workspace, workspace_bytes, stream);
+        rc = launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, open, exchange, epoch, numseq, seqlen,
+                         row_stride, reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, &px, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen,
-                        row_stride, reverse, dtype, shard, nshards, stream);
+    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1, numseq,
+                        seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
 
 int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* dx, void* dc, int64_t numseq,
                             int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
-                            void* const* peer_bufs, int64_t max_rows, uint32_t epoch, const linrec_opts* opts,
-                            void* workspace, size_t workspace_bytes, void* stream)
+                            void* exchange, uint32_t epoch, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
+                            void* stream)
 {
-    linrec::PeerExchange px{};
-    int rc = make_exchange(px, peer_bufs, max_rows, epoch, shard, nshards, numseq);
-    if (rc != LINREC_OK) return rc;
+    if (!exchange || epoch == 0 || nshards < 1 || nshards > linrec::kMaxPeers || shard < 0 || shard >= nshards)
+        return LINREC_ERR_INVALID_ARG;
     Options opt;
-    rc = parse_options(opts, opt);
+    int rc = parse_options(opts, opt);
     if (rc != LINREC_OK) return rc;
     const bool asc = reverse != 0;
     const int open = holds_scan_start(asc, shard, nshards) ? 0 : 1;
     if (opt.p2p_phase != 2)
-        rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, nullptr, 0, open, &px, numseq, seqlen, row_stride, reverse,
-                         dtype, opts, workspace, workspace_bytes, stream);
+        rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, nullptr, 0, open, exchange, epoch, numseq, seqlen, row_stride,
+                         reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(true, dx, dc, c, y, nullptr, &px, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen, row_stride,
-                        reverse, dtype, shard, nshards, stream);
+    return launch_fixup(true, dx, dc, c, y, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen,
+                        row_stride, reverse, dtype, shard, nshards, stream);
 }
 
 // ---- forward scan on a built-in scratch buffer ----------------------------------------------------
@@ -827,7 +835,7 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
     if (rc != LINREC_OK) return rc;
     // launch_scan rewrites the header words and zeroes the descriptors this call uses, so whatever
     // an earlier call left in the buffer does not matter
-    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, numseq, seqlen, row_stride,
+    return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, 0u, numseq, seqlen, row_stride,
                        reverse, dtype, nullptr, scratch, (size_t)LINREC_STATIC_SCRATCH_BYTES, stream);
 }
 

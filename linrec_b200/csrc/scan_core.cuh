@@ -72,32 +72,37 @@ __device__ __forceinline__ Pair combine(Pair far, Pair near)
 //   flags   [2][nranks][max_rows] x 4 B    epoch of the record
 //   acks    [nranks] x 4 B                 last epoch rank i has finished reading
 //   done    4 B                            fix-up CTAs finished (local bookkeeping)
+// preceded by a 256-byte table of the peers' buffer addresses.
 constexpr int kMaxPeers = 16;
-struct PeerExchange {
-    void* base[kMaxPeers];   // base[i]: rank i's exchange buffer as mapped here (base[me] is local)
+constexpr size_t kPeerTableBytes = 256;
+// Lives at the start of every exchange buffer (global memory, written once by the init call), so the
+// kernels reach the peers through one pointer instead of carrying the table in their parameters.
+struct PeerTable {
+    void* base[kMaxPeers];   // base[i]: rank i's exchange buffer as mapped here (base[me] is this buffer)
     int nranks, me;
-    uint32_t epoch;          // 0: no peer exchange in this launch; real epochs start at 1
     long long max_rows;
 };
-__host__ __device__ inline size_t px_flags_offset(long long max_rows, int nranks) { return (size_t)2 * nranks * max_rows * 16; }
+static_assert(sizeof(PeerTable) <= kPeerTableBytes, "peer table must fit its slot");
+__host__ __device__ inline size_t px_flags_offset(long long max_rows, int nranks) { return kPeerTableBytes + (size_t)2 * nranks * max_rows * 16; }
 __host__ __device__ inline size_t px_acks_offset(long long max_rows, int nranks)
 {
     return (px_flags_offset(max_rows, nranks) + (size_t)2 * nranks * max_rows * 4 + 255) / 256 * 256;
 }
 __host__ __device__ inline size_t px_done_offset(long long max_rows, int nranks) { return px_acks_offset(max_rows, nranks) + 256; }
 __host__ __device__ inline size_t px_total_bytes(long long max_rows, int nranks) { return px_done_offset(max_rows, nranks) + 256; }
-__device__ __forceinline__ float4* px_record(const PeerExchange& px, int buf_of, int par, int from, long long row)
+__device__ __forceinline__ float4* px_record(const PeerTable& t, int buf_of, int par, int from, long long row)
 {
-    return reinterpret_cast<float4*>(px.base[buf_of]) + ((size_t)(par * px.nranks + from) * px.max_rows + row);
+    return reinterpret_cast<float4*>(static_cast<char*>(t.base[buf_of]) + kPeerTableBytes) +
+           ((size_t)(par * t.nranks + from) * t.max_rows + row);
 }
-__device__ __forceinline__ uint32_t* px_flag(const PeerExchange& px, int buf_of, int par, int from, long long row)
+__device__ __forceinline__ uint32_t* px_flag(const PeerTable& t, int buf_of, int par, int from, long long row)
 {
-    return reinterpret_cast<uint32_t*>(static_cast<char*>(px.base[buf_of]) + px_flags_offset(px.max_rows, px.nranks)) +
-           ((size_t)(par * px.nranks + from) * px.max_rows + row);
+    return reinterpret_cast<uint32_t*>(static_cast<char*>(t.base[buf_of]) + px_flags_offset(t.max_rows, t.nranks)) +
+           ((size_t)(par * t.nranks + from) * t.max_rows + row);
 }
-__device__ __forceinline__ uint32_t* px_ack(const PeerExchange& px, int buf_of, int of_rank)
+__device__ __forceinline__ uint32_t* px_ack(const PeerTable& t, int buf_of, int of_rank)
 {
-    return reinterpret_cast<uint32_t*>(static_cast<char*>(px.base[buf_of]) + px_acks_offset(px.max_rows, px.nranks)) + of_rank;
+    return reinterpret_cast<uint32_t*>(static_cast<char*>(t.base[buf_of]) + px_acks_offset(t.max_rows, t.nranks)) + of_rank;
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p)
 {
@@ -149,7 +154,8 @@ struct ScanParams {
     int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
                          //    coefficient that lies before the shard is taken as 1 (folded in later)
     uint32_t first_ticket;  // diagnostics: added to every ticket (0 in normal use)
-    PeerExchange px;        // sequence sharding: where the rows' records are pushed (epoch 0: nowhere)
+    const PeerTable* px;    // sequence sharding: this rank's exchange buffer (records are pushed to all ranks)
+    uint32_t px_epoch;      // epoch of this exchange; 0: no peer exchange in this launch (real epochs start at 1)
 };
 
 // Storage helpers are declared further down; the record emitter needs them, so it follows them.
@@ -206,41 +212,53 @@ struct Storage<__nv_bfloat16> {
 // Sequence sharding: the record of one row of this shard -- (P, Y) of the whole shard and, for the
 // backward pass, c at the shard's scan-last element and y at its scan-first element (what the
 // neighbouring shards need).  Written to the local record array and/or pushed to every peer.
+// (Deliberately NOT inlined and fed by value: it runs once per row; inlined into the tile loop its
+// peer loop cost the backward kernel 37 registers and with them one resident CTA per SM.)
 template <typename ST, bool BWD, bool ASC>
-__device__ __forceinline__ void emit_record(const ScanParams& p, long long row, Pair tot)
+__device__ __noinline__ void emit_record(float* carry_out, int carry_stride, const PeerTable* px, uint32_t px_epoch,
+                                         const ST* c, const ST* yin, long long seqlen, long long row_stride,
+                                         long long row, float tot_p, float tot_y)
 {
     float ce = 0.0f, ye = 0.0f;
     if (BWD) {
-        const long long first = ASC ? 0 : p.seqlen - 1, last = ASC ? p.seqlen - 1 : 0;
-        ce = Storage<ST>::to_float(reinterpret_cast<const ST*>(p.c)[row * p.row_stride + last]);
-        ye = Storage<ST>::to_float(reinterpret_cast<const ST*>(p.yin)[row * p.row_stride + first]);
+        const long long first = ASC ? 0 : seqlen - 1, last = ASC ? seqlen - 1 : 0;
+        ce = Storage<ST>::to_float(c[row * row_stride + last]);
+        ye = Storage<ST>::to_float(yin[row * row_stride + first]);
     }
-    if (p.carry_out) {
-        float* r = p.carry_out + p.carry_stride * row;
-        r[0] = tot.p;
-        r[1] = tot.y;
-        if (BWD && p.carry_stride >= 4) {
+    if (carry_out) {
+        float* r = carry_out + carry_stride * row;
+        r[0] = tot_p;
+        r[1] = tot_y;
+        if (BWD && carry_stride >= 4) {
             r[2] = ce;
             r[3] = ye;
         }
     }
-    if (p.px.epoch != 0u) {
-        const int par = (int)(p.px.epoch & 1u);
-        const float4 rec = make_float4(tot.p, tot.y, ce, ye);
-        for (int i = 0; i < p.px.nranks; ++i) {
-            st_relaxed_sys_f32x4(px_record(p.px, i, par, p.px.me, row), rec);
-            st_release_sys_u32(px_flag(p.px, i, par, p.px.me, row), p.px.epoch);
+    if (px_epoch != 0u) {
+        const PeerTable& t = *px;
+        const int par = (int)(px_epoch & 1u);
+        const float4 rec = make_float4(tot_p, tot_y, ce, ye);
+        for (int i = 0; i < t.nranks; ++i) {
+            st_relaxed_sys_f32x4(px_record(t, i, par, t.me, row), rec);
+            st_release_sys_u32(px_flag(t, i, par, t.me, row), px_epoch);
         }
     }
 }
 
+template <typename ST, bool BWD, bool ASC>
+__device__ __forceinline__ void emit_record(const ScanParams& p, long long row, Pair tot)
+{
+    emit_record<ST, BWD, ASC>(p.carry_out, p.carry_stride, p.px, p.px_epoch, reinterpret_cast<const ST*>(p.c),
+                              reinterpret_cast<const ST*>(p.yin), p.seqlen, p.row_stride, row, tot.p, tot.y);
+}
+
 // Before a launch pushes records of epoch e it makes sure that every rank has acknowledged epoch
 // e-2, whose slots it is about to overwrite (lanes 0..nranks-1 of the calling warp check one rank each).
-__device__ __forceinline__ void wait_for_slot_release(const ScanParams& p, int lane)
+__device__ __noinline__ void wait_for_slot_release(const PeerTable* px, uint32_t px_epoch, long long budget,
+                                                   uint32_t* status, int lane)
 {
-    if (p.px.epoch >= 3u && lane < p.px.nranks) {
-        if (!wait_epoch_reached(px_ack(p.px, p.px.me, lane), p.px.epoch - 2u, p.wait_budget))
-            atomicOr(p.header + 1, kStatusPeerTimeout);
+    if (lane < px->nranks) {
+        if (!wait_epoch_reached(px_ack(*px, px->me, lane), px_epoch - 2u, budget)) atomicOr(status, kStatusPeerTimeout);
     }
 }
 

@@ -107,7 +107,7 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
                     cs->tprefix = tp;
                 }
             }
-            if (g.lane == 0 && last_piece && (p.carry_out || p.px.epoch)) emit_record<ST, BWD, ASC>(p, tc.row, combine(tp, bagg));
+            if (g.lane == 0 && last_piece && (p.carry_out || p.px_epoch)) emit_record<ST, BWD, ASC>(p, tc.row, combine(tp, bagg));
             // fetch ahead what the next tile of this CTA will ask for
             probe = make_uint4(0u, 0u, 0u, 0u);
             if (next_tk < (uint32_t)p.ntiles && next_tk >= (uint32_t)p.numseq)
@@ -118,7 +118,7 @@ __device__ __forceinline__ void tile_scan(const ScanParams& p, const Geometry& g
     }
     if (g.need_wp) pre = combine(pre, wp);
     pre = combine(pre, ts.excl);
-    if (!p.chain && (p.carry_out || p.px.epoch) && g.k == g.tpr - 1 && g.row_in_tile < p.rows_per_tile) {
+    if (!p.chain && (p.carry_out || p.px_epoch) && g.k == g.tpr - 1 && g.row_in_tile < p.rows_per_tile) {
         const long long row = tc.row + g.row_in_tile;
         if (row < p.numseq) emit_record<ST, BWD, ASC>(p, row, combine(pre, ts.agg));
     }
@@ -136,10 +136,14 @@ struct TmaLayout {
     static constexpr size_t kTileBytes = (size_t)T * sizeof(ST);
     static constexpr size_t kDynSmem = kTileBytes * (S * NIN + OB * NOUT) + 1024;   // + alignment slack
     static_assert(kTileBytes % 1024 == 0, "tile buffers must keep 1024-byte alignment");
+    // CTAs per SM the kernel is compiled for: what shared memory allows, at no more than 512 threads
+    // per SM (so that the register allocator keeps at least 128 registers per thread)
+    static constexpr int kFitSmem = (int)((size_t)232448 / (kDynSmem + 1024 + 512));
+    static constexpr int kMinBlocks = kFitSmem < 1 ? 1 : (kFitSmem < 512 / NT ? kFitSmem : (512 / NT < 1 ? 1 : 512 / NT));
 };
 
 template <typename ST, int E, int NT, int S, int OB, bool BWD, bool ASC>
-__global__ void __launch_bounds__(NT, (E <= 8 && NT >= 512) ? 2 : 1)
+__global__ void __launch_bounds__(NT, (TmaLayout<ST, E, NT, S, OB, BWD>::kMinBlocks))
 linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_constant__ CUtensorMap tm_c,
                   const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_out0,
                   const __grid_constant__ CUtensorMap tm_out1, const ScanParams p)
@@ -172,7 +176,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
                                  : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
 
-    if (tid < 32) wait_for_slot_release(p, tid);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
@@ -342,7 +346,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     ST* gout0 = reinterpret_cast<ST*>(p.out0);
     ST* gout1 = reinterpret_cast<ST*>(p.out1);
     const int spr = p.chain ? T : p.slots_per_row;
-    if (tid < 32) wait_for_slot_release(p, tid);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
 
     bool first_round = true;
     for (;;) {

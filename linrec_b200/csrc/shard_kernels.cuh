@@ -28,8 +28,8 @@ struct FixupParams {
     long long numseq, seqlen, row_stride;
     int shard, nshards;
     int rec;             // floats per record: 2 forward, 4 backward
-    PeerExchange px;     // epoch != 0: the records arrive in this rank's exchange buffer (16-byte records,
-                         // one flag per row and sender) instead of `carries`
+    const PeerTable* px; // with px_epoch != 0: the records arrive in this rank's exchange buffer (16-byte
+    uint32_t px_epoch;   // records, one flag per row and sender) instead of `carries`
     long long wait_budget;   // clock ticks a wait for a peer's record may last
     uint32_t* status;    // status word that receives kStatusPeerTimeout
 };
@@ -37,13 +37,22 @@ struct FixupParams {
 // Where the record of (shard s, row) is, once it is known to have arrived.
 __device__ __forceinline__ const float* fixup_record(const FixupParams& p, int s, long long row)
 {
-    if (p.px.epoch != 0u) {
-        const int par = (int)(p.px.epoch & 1u);
-        if (!wait_epoch_reached(px_flag(p.px, p.px.me, par, s, row), p.px.epoch, p.wait_budget))
-            atomicOr(p.status, kStatusPeerTimeout);
-        return reinterpret_cast<const float*>(px_record(p.px, p.px.me, par, s, row));
+    if (p.px_epoch != 0u) {
+        const PeerTable& t = *p.px;
+        const int par = (int)(p.px_epoch & 1u);
+        if (!wait_epoch_reached(px_flag(t, t.me, par, s, row), p.px_epoch, p.wait_budget)) atomicOr(p.status, kStatusPeerTimeout);
+        return reinterpret_cast<const float*>(px_record(t, t.me, par, s, row));
     }
     return p.carries + ((long long)s * p.numseq + row) * p.rec;
+}
+
+// Writes the peer table into a (zeroed) exchange buffer.
+struct PeerTableArg {
+    PeerTable t;
+};
+__global__ void linrec_exchange_init_kernel(PeerTable* dst, const PeerTableArg a)
+{
+    if (threadIdx.x == 0) *dst = a.t;
 }
 
 // Shards in scan order: ascending scans visit shard 0 first, descending scans the last shard first.
@@ -247,12 +256,13 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
     }
     // Peer exchange: once every CTA of this rank is done reading, tell all ranks that the slots of
     // this epoch may be reused (they will be, two epochs from now).
-    if (p.px.epoch != 0u && tid == 0) {
+    if (p.px_epoch != 0u && tid == 0) {
+        const PeerTable& t = *p.px;
         __threadfence();
-        uint32_t* done = reinterpret_cast<uint32_t*>(static_cast<char*>(p.px.base[p.px.me]) + px_done_offset(p.px.max_rows, p.px.nranks));
+        uint32_t* done = reinterpret_cast<uint32_t*>(static_cast<char*>(t.base[t.me]) + px_done_offset(t.max_rows, t.nranks));
         if (atomicAdd(done, 1u) == gridDim.x - 1) {
             *done = 0u;
-            for (int i = 0; i < p.px.nranks; ++i) st_release_sys_u32(px_ack(p.px, i, p.px.me), p.px.epoch);
+            for (int i = 0; i < t.nranks; ++i) st_release_sys_u32(px_ack(t, i, t.me), p.px_epoch);
         }
     }
 }

@@ -107,27 +107,26 @@ class PeerExchange:
     collective and must be made in the same order on all ranks.
     """
 
-    def __init__(self, max_rows: int, group=None, device=None, peer_ptrs=None, rank=None, world=None):
+    def __init__(self, max_rows: int, group=None, device=None):
         import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
         self.max_rows = int(max_rows)
         self.epoch = 0
-        if peer_ptrs is not None:          # buffers handed in (tests: all "ranks" on one device)
-            self.rank, self.world, ptrs = rank, world, list(peer_ptrs)
-            self._keep = None
-        else:
-            import torch.distributed._symmetric_memory as symm_mem
-            group = group if group is not None else dist.group.WORLD
-            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-            nbytes = _capi.lib.linrec_b200_exchange_size(self.max_rows, self.world)
-            dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
-            buf.zero_()
-            handle = symm_mem.rendezvous(buf, group)
-            ptrs = [int(p) for p in handle.buffer_ptrs]
-            torch.cuda.synchronize(dev)
-            handle.barrier()               # every rank's buffer is zeroed before anyone pushes into it
-            self._keep = (buf, handle)
-        self.ptr_array = (ctypes.c_void_p * self.world)(*ptrs)
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        nbytes = _capi.lib.linrec_b200_exchange_size(self.max_rows, self.world)
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        handle = symm_mem.rendezvous(buf, group)
+        ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        with torch.cuda.device(dev):
+            rc = _capi.lib.linrec_b200_exchange_init(buf.data_ptr(), ptrs, self.rank, self.world, self.max_rows,
+                                                     torch.cuda.current_stream(dev).cuda_stream)
+        _capi.raise_for(rc, "linrec_b200_exchange_init")
+        torch.cuda.synchronize(dev)
+        handle.barrier()                   # every rank's buffer is initialised before anyone pushes into it
+        self.buffer = buf
+        self._keep = handle
 
     def next_epoch(self) -> int:
         self.epoch += 1
@@ -148,8 +147,8 @@ class PeerExchange:
         with torch.cuda.device(x.device):
             stream, dtype, ws = self._env(x, numseq, seqlen)
             rc = _capi.lib.linrec_b200_fwd_seq_p2p(x.data_ptr(), c.data_ptr(), y.data_ptr(), numseq, seqlen, stride,
-                                                   int(bool(reverse)), dtype, self.rank, self.world, self.ptr_array,
-                                                   self.max_rows, self.next_epoch(), o, ws.data_ptr(), ws.numel(), stream)
+                                                   int(bool(reverse)), dtype, self.rank, self.world,
+                                                   self.buffer.data_ptr(), self.next_epoch(), o, ws.data_ptr(), ws.numel(), stream)
         _capi.raise_for(rc, "linrec_b200_fwd_seq_p2p")
         return y
 
@@ -163,7 +162,7 @@ class PeerExchange:
             stream, dtype, ws = self._env(dy, numseq, seqlen)
             rc = _capi.lib.linrec_b200_bwd_seq_p2p(dy.data_ptr(), c.data_ptr(), y.data_ptr(), dx.data_ptr(), dc.data_ptr(),
                                                    numseq, seqlen, stride, int(bool(reverse)), dtype, self.rank, self.world,
-                                                   self.ptr_array, self.max_rows, self.next_epoch(), o, ws.data_ptr(),
+                                                   self.buffer.data_ptr(), self.next_epoch(), o, ws.data_ptr(),
                                                    ws.numel(), stream)
         _capi.raise_for(rc, "linrec_b200_bwd_seq_p2p")
         return dx, dc

@@ -102,13 +102,15 @@ def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
     dev = torch.device("cuda:0")
     nbytes = _capi.lib.linrec_b200_exchange_size(rows, G)
     assert nbytes > 0
-    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(G)]
+    bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(G)]
     x, c, dy = _data((rows, L), clo, seed=11)
     Ls = L // G
     cut = lambda t, s: t[:, s * Ls:(s + 1) * Ls].contiguous().to(dev)
     stream = torch.cuda.current_stream().cuda_stream
     ws = torch.zeros(_capi.lib.linrec_b200_workspace_size(rows, Ls, 0), dtype=torch.uint8, device=dev)
     ptrs = (ctypes.c_void_p * G)(*[b.data_ptr() for b in bufs])
+    for s in range(G):
+        assert _capi.lib.linrec_b200_exchange_init(bufs[s].data_ptr(), ptrs, s, G, rows, stream) == 0
     epoch = 0
     for rev in (False, True, False):
         y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
@@ -122,14 +124,14 @@ def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
             o, keep = _capi.make_opts({"p2pPhase": phase})
             for s in range(G):
                 rc = _capi.lib.linrec_b200_fwd_seq_p2p(xs[s].data_ptr(), cs[s].data_ptr(), ys[s].data_ptr(), rows, Ls, Ls,
-                                                       int(rev), 0, s, G, ptrs, rows, epoch, o, ws.data_ptr(), ws.numel(), stream)
+                                                       int(rev), 0, s, G, bufs[s].data_ptr(), epoch, o, ws.data_ptr(), ws.numel(), stream)
                 assert rc == 0, _capi.strerror(rc)
         epoch += 1
         for phase in (1, 2):
             o, keep = _capi.make_opts({"p2pPhase": phase})
             for s in range(G):
                 rc = _capi.lib.linrec_b200_bwd_seq_p2p(dys[s].data_ptr(), cs[s].data_ptr(), ygs[s].data_ptr(), dxs[s].data_ptr(),
-                                                       dcs[s].data_ptr(), rows, Ls, Ls, int(rev), 0, s, G, ptrs, rows, epoch, o,
+                                                       dcs[s].data_ptr(), rows, Ls, Ls, int(rev), 0, s, G, bufs[s].data_ptr(), epoch, o,
                                                        ws.data_ptr(), ws.numel(), stream)
                 assert rc == 0, _capi.strerror(rc)
         torch.cuda.synchronize()
