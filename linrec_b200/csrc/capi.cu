@@ -38,6 +38,7 @@ struct Options {
     int wait_budget_ms = 2000;   // budget of every device-side wait
     int ctas_per_sm = 0;         // 0 = as many as fit
     int first_ticket = 0;        // diagnostics only: tickets start here instead of 0
+    int lazy = -1;               // -1 = selector decides, 0/1 = one-ticket-at-a-time mode off/on (one ring slot only)
     int p2p_phase = 0;           // peer-exchange calls: 0 = scan and fix-up, 1 = scan only, 2 = fix-up only
 };
 
@@ -58,6 +59,7 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "ctasPerSm")) out.ctas_per_sm = v;
         else if (!strcmp(n, "firstTicket")) out.first_ticket = v;
         else if (!strcmp(n, "p2pPhase")) out.p2p_phase = v;
+        else if (!strcmp(n, "lazyTickets")) out.lazy = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
     }
     return LINREC_OK;
@@ -131,6 +133,8 @@ const std::vector<TmaVariant>& tma_variants()
         make_tma_variant<8, 512, 2, 1>(),
         make_tma_variant<16, 512, 2, 1>(),
         make_tma_variant<16, 512, 1, 1>(),
+        make_tma_variant<16, 256, 1, 1>(),
+        make_tma_variant<16, 128, 1, 1>(),
         make_tma_variant<32, 128, 2, 1>(),
         make_tma_variant<32, 128, 3, 1>(),
         make_tma_variant<32, 256, 2, 1>(),
@@ -258,6 +262,7 @@ struct Plan {
     int E = 0, NT = 0, T = 0;
     int chain = 0, slots_per_row = 0, rows_per_tile = 1, chunks_per_row = 1;
     long long ntiles = 0;
+    bool lazy_default = false;
 };
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -324,7 +329,13 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             // tile is often still in flight, and fewer, larger CTAs do better
             const bool short_rows = seqlen <= 2048;
             const bool few_rows = !short_rows && numseq < 4LL * sm_count;
-            if (sz == 4) {
+            // a handful of very long rows: consecutive tickets are consecutive pieces of the same row,
+            // so CTAs hold one ticket at a time (see the kernel's "lazy" mode)
+            const bool handful = !short_rows && seqlen > 8192 && numseq < 32;
+            pl.lazy_default = handful;
+            if (handful) {
+                E = 16; NT = 512; S = 1; OB = 1;
+            } else if (sz == 4) {
                 if (!bwd)          { E = 16; NT = 512; S = 2; OB = 1; }
                 else if (few_rows) { E = 16; NT = 512; S = 1; OB = 1; }
                 else               { E = 16; NT = 128; S = 2; OB = 1; }
@@ -469,6 +480,14 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
 
     // The workspace cleans up after every launch by itself (see scan_core.cuh): nothing to prepare.
     p.first_ticket = (uint32_t)opt.first_ticket;
+    p.lazy = pl.tma && pl.chain && pl.tv->S == 1 && (opt.lazy >= 0 ? opt.lazy != 0 : pl.lazy_default);
+    {
+        // 16-byte global accesses in the any-alignment kernel: aligned rows of whole 16-byte chunks
+        const int sz = di == 0 ? 4 : 2;
+        bool al = (row_stride * sz) % 16 == 0 && (seqlen * sz) % 16 == 0;
+        for (int i = 0; i < 5 && al; ++i) al = reinterpret_cast<uintptr_t>(ptrs[i]) % 16 == 0;
+        p.vec = al ? 1 : 0;
+    }
 
     if (pl.tma) {
         CUtensorMap m[5];

@@ -154,6 +154,8 @@ struct ScanParams {
     int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
                          //    coefficient that lies before the shard is taken as 1 (folded in later)
     uint32_t first_ticket;  // diagnostics: added to every ticket (0 in normal use)
+    int vec;                // any-alignment kernel: rows allow 16-byte global accesses
+    int lazy;               // bulk-copy kernel: draw the next ticket only when the current tile is finished
     const PeerTable* px;    // sequence sharding: this rank's exchange buffer (records are pushed to all ranks)
     uint32_t px_epoch;      // epoch of this exchange; 0: no peer exchange in this launch (real epochs start at 1)
 };

@@ -225,8 +225,15 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     // that neighbouring tickets start on different CTAs at the same time; drawing them from the counter
     // would hand each CTA S+1 CONSECUTIVE tickets, and with few rows those are consecutive pieces of
     // one row that would wait for each other across CTAs.  All later tickets come from the counter.
+    //
+    // "Lazy" mode (one ring slot; chosen when a handful of very long rows is all there is): a CTA holds
+    // ONE ticket at a time and draws the next only when its tile is finished.  Holding tickets ahead is
+    // what hides the load latency, but when consecutive tickets are consecutive pieces of the same row,
+    // a ticket parked behind a tile that is itself waiting in its look-back stalls every CTA behind
+    // it; with one ticket per CTA the oldest unfinished tiles are always the ones being worked on.
     const uint32_t grid = gridDim.x;
-    const uint32_t dyn_base = p.first_ticket + (uint32_t)(S + 1) * grid;
+    const bool lazy = (S == 1) && p.lazy;
+    const uint32_t dyn_base = p.first_ticket + (lazy ? 1u : (uint32_t)(S + 1)) * grid;
     uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket held one step ahead
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -284,7 +291,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
                 alive = false;
                 return false;
             }
-            if (tid == 0) {   // ring slot s is free again: refill it with the ticket drawn earlier
+            if (tid == 0 && !lazy) {   // ring slot s is free again: refill it with the ticket drawn earlier
                 tile_of_stage[s] = next_ticket;
                 if (next_ticket < ntiles) issue(s, next_ticket);
                 next_ticket = dyn_base + atomicAdd(p.header, 1u);
@@ -304,7 +311,13 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             ptx::tma_store_3d(&tm_out0, out_buf(ob, 0), 0, c1, c2);
             if (BWD) ptx::tma_store_3d(&tm_out1, out_buf(ob, 1), 0, c1, c2);
             ptx::tma_commit_group();
+            if (lazy) {   // the tile is done: only now take the next ticket and start its copies
+                const uint32_t nt = dyn_base + atomicAdd(p.header, 1u);
+                tile_of_stage[s] = nt;
+                if (nt < ntiles) issue(s, nt);
+            }
         }
+        if (lazy) __syncthreads();   // the new ticket must be visible before the next round reads it
     }
 
     if (tid == 0) {
@@ -361,19 +374,49 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
         const long long col0 = (long long)tc.piece * T;
 
         // ---- cooperative, coalesced load with identity fill ------------------------------------
-        for (int i = tid; i < T; i += NT) {
-            const int j = p.chain ? 0 : i / spr;
-            const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
-            const long long row = tc.row + j;
-            const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
-            const long long off = row * p.row_stride + col;
-            write_slot<ST>(buf_in0, i, ok ? Storage<ST>::to_float(gin0[off]) : 0.0f);
-            float cv = ok ? Storage<ST>::to_float(gc[off]) : 1.0f;
-            // the coefficient of a row's very first element has no effect (closed rows only); with
-            // padded rows that element need not be a thread's first slot, so it is cleared here
-            if (!BWD && !p.open_start && col == (ASC ? 0 : p.seqlen - 1)) cv = 0.0f;
-            write_slot<ST>(buf_c, i, cv);
-            if (BWD) write_slot<ST>(buf_y, i, ok ? Storage<ST>::to_float(gy[off]) : 0.0f);
+        if (p.vec) {
+            // 16-byte chunks: rows are 16-byte aligned and a whole number of chunks long, so a chunk
+            // lies entirely inside or entirely outside its row
+            constexpr int PC = Storage<ST>::kPerChunk;
+            constexpr uint32_t kOne = sizeof(ST) == 4 ? 0x3f800000u : 0x3f803f80u;
+            const int cpr = spr / PC;
+            const long long first_col = ASC ? 0 : p.seqlen - PC;   // chunk that holds the row's scan-first element
+            for (int ci = tid; ci < T / PC; ci += NT) {
+                const int j = p.chain ? 0 : ci / cpr;
+                const long long col = p.chain ? col0 + (long long)ci * PC : (long long)(ci - j * cpr) * PC;
+                const long long row = tc.row + j;
+                const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+                const long long off = row * p.row_stride + col;
+                const int phys = ci ^ ((ci >> 3) & 7);
+                uint4 q0 = make_uint4(0u, 0u, 0u, 0u), qc = make_uint4(kOne, kOne, kOne, kOne), qy = make_uint4(0u, 0u, 0u, 0u);
+                if (ok) {
+                    q0 = *reinterpret_cast<const uint4*>(gin0 + off);
+                    qc = *reinterpret_cast<const uint4*>(gc + off);
+                    if (BWD) qy = *reinterpret_cast<const uint4*>(gy + off);
+                    if (!BWD && !p.open_start && col == first_col) {
+                        if (ASC) qc.x = sizeof(ST) == 4 ? 0u : (qc.x & 0xffff0000u);
+                        else     qc.w = sizeof(ST) == 4 ? 0u : (qc.w & 0x0000ffffu);
+                    }
+                }
+                reinterpret_cast<uint4*>(buf_in0)[phys] = q0;
+                reinterpret_cast<uint4*>(buf_c)[phys] = qc;
+                if (BWD) reinterpret_cast<uint4*>(buf_y)[phys] = qy;
+            }
+        } else {
+            for (int i = tid; i < T; i += NT) {
+                const int j = p.chain ? 0 : i / spr;
+                const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
+                const long long row = tc.row + j;
+                const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+                const long long off = row * p.row_stride + col;
+                write_slot<ST>(buf_in0, i, ok ? Storage<ST>::to_float(gin0[off]) : 0.0f);
+                float cv = ok ? Storage<ST>::to_float(gc[off]) : 1.0f;
+                // the coefficient of a row's very first element has no effect (closed rows only); with
+                // padded rows that element need not be a thread's first slot, so it is cleared here
+                if (!BWD && !p.open_start && col == (ASC ? 0 : p.seqlen - 1)) cv = 0.0f;
+                write_slot<ST>(buf_c, i, cv);
+                if (BWD) write_slot<ST>(buf_y, i, ok ? Storage<ST>::to_float(gy[off]) : 0.0f);
+            }
         }
         if (BWD && p.chain && tid < 2) {
             const long long lo = col0 - 1, hi = col0 + T;
@@ -406,15 +449,32 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
         __syncthreads();
 
         // ---- cooperative, coalesced store ------------------------------------------------------
-        for (int i = tid; i < T; i += NT) {
-            const int j = p.chain ? 0 : i / spr;
-            const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
-            const long long row = tc.row + j;
-            const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
-            if (ok) {
-                const long long off = row * p.row_stride + col;
-                gout0[off] = Storage<ST>::from_float(read_slot<ST>(buf_in0, i));
-                if (BWD) gout1[off] = Storage<ST>::from_float(read_slot<ST>(buf_y, i));
+        if (p.vec) {
+            constexpr int PC = Storage<ST>::kPerChunk;
+            const int cpr = spr / PC;
+            for (int ci = tid; ci < T / PC; ci += NT) {
+                const int j = p.chain ? 0 : ci / cpr;
+                const long long col = p.chain ? col0 + (long long)ci * PC : (long long)(ci - j * cpr) * PC;
+                const long long row = tc.row + j;
+                const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+                if (ok) {
+                    const long long off = row * p.row_stride + col;
+                    const int phys = ci ^ ((ci >> 3) & 7);
+                    *reinterpret_cast<uint4*>(gout0 + off) = reinterpret_cast<const uint4*>(buf_in0)[phys];
+                    if (BWD) *reinterpret_cast<uint4*>(gout1 + off) = reinterpret_cast<const uint4*>(buf_y)[phys];
+                }
+            }
+        } else {
+            for (int i = tid; i < T; i += NT) {
+                const int j = p.chain ? 0 : i / spr;
+                const long long col = p.chain ? col0 + i : (long long)(i - j * spr);
+                const long long row = tc.row + j;
+                const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
+                if (ok) {
+                    const long long off = row * p.row_stride + col;
+                    gout0[off] = Storage<ST>::from_float(read_slot<ST>(buf_in0, i));
+                    if (BWD) gout1[off] = Storage<ST>::from_float(read_slot<ST>(buf_y, i));
+                }
             }
         }
     }

@@ -291,6 +291,16 @@ if _HAVE_HYPOTHESIS:
         np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
 
 
+@pytest.mark.parametrize("rev", [False, True])
+def test_handful_of_very_long_rows(rev):
+    """Few rows, many tiles each: the selector's one-ticket-at-a-time mode (every tile looks back at
+    tiles that are in flight at the same moment)."""
+    x, c, dy = _data((3, 40 * 8192 + 4096), clo=0.9)
+    _check_fwd_bwd(x, c, dy, rev)
+    _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=128, kStages=1, lazyTickets=1)
+    _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=256, kStages=1, lazyTickets=0)
+
+
 def test_host_streamed_path():
     """Tensors in host memory, streamed through the device in row slabs (ragged last slab)."""
     from linrec_b200 import host
