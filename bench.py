@@ -66,12 +66,14 @@ class ClockSampler:
 
     NVML is initialised and the first sample is taken BEFORE the timed region: attaching a
     monitoring client to the GPU (which is what starting `nvidia-smi` does) stalls kernel launches
-    for tens of milliseconds, which must not land inside the measurement."""
+    for tens of milliseconds, which must not land inside the measurement.  Even an NVML query now and
+    then costs a step a few milliseconds (seen: one 11 ms step in 200 at a 20 ms period, none without
+    sampling), so the period is 100 ms: a few samples per timed region."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = float(os.environ.get("LINREC_BENCH_CLOCK_PERIOD", "0.02"))):
         self.index, self.period, self.rows = index, period_s, []
         self.active = threading.Event()
         self.done = threading.Event()
@@ -418,7 +420,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-seq-sharded", action="store_true", help="skip the sequence-sharded extra measurement")
