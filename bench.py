@@ -73,7 +73,7 @@ class ClockSampler:
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int, period_s: float = float(os.environ.get("LINREC_BENCH_CLOCK_PERIOD", "0.02"))):
+    def __init__(self, index: int, period_s: float = float(os.environ.get("LINREC_BENCH_CLOCK_PERIOD", "0.1"))):
         self.index, self.period, self.rows = index, period_s, []
         self.active = threading.Event()
         self.done = threading.Event()
