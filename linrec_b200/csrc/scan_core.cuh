@@ -114,6 +114,10 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
 {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_relaxed_sys_f32x4(float4* p, float4 v)
 {
     asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
@@ -240,10 +244,11 @@ __device__ __noinline__ void emit_record(float* carry_out, int carry_stride, con
         const PeerTable& t = *px;
         const int par = (int)(px_epoch & 1u);
         const float4 rec = make_float4(tot_p, tot_y, ce, ye);
-        for (int i = 0; i < t.nranks; ++i) {
-            st_relaxed_sys_f32x4(px_record(t, i, par, t.me, row), rec);
-            st_release_sys_u32(px_flag(t, i, par, t.me, row), px_epoch);
-        }
+        // all payloads, ONE system-scope fence, then all flags: a release store per peer would make this
+        // lane wait for a round trip over NVLink once per peer
+        for (int i = 0; i < t.nranks; ++i) st_relaxed_sys_f32x4(px_record(t, i, par, t.me, row), rec);
+        __threadfence_system();
+        for (int i = 0; i < t.nranks; ++i) st_relaxed_sys_u32(px_flag(t, i, par, t.me, row), px_epoch);
     }
 }
 
