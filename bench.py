@@ -323,8 +323,12 @@ def run_ours(args):
                 exchange = sharded.PeerExchange(rows_s)
             except Exception as exc:      # symmetric memory unavailable: the all-gather path still runs
                 exchange = None
-                if rank == 0:
-                    print(f"peer exchange unavailable: {exc}", file=sys.stderr)
+                print(f"rank {rank}: peer exchange unavailable: {exc}", file=sys.stderr)
+            # the exchange is collective: use it only if EVERY rank has one
+            ok = torch.tensor([1 if exchange is not None else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                exchange = None
 
         def seq_step(ex=None):
             if world == 1:
