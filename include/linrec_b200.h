@@ -46,6 +46,7 @@ extern "C" {
 /* ---- element storage types (arithmetic is always fp32) -------------------------------------- */
 #define LINREC_DTYPE_F32   0
 #define LINREC_DTYPE_BF16  1
+#define LINREC_DTYPE_F16   2
 
 /* ---- which family of kernels a call may use --------------------------------------------------
  * The reference exposes three operator families with one signature

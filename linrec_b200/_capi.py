@@ -23,7 +23,7 @@ ERR_TIMEOUT = -5
 ERR_TOO_LONG = -6
 ERR_UNALIGNED = -7
 
-DTYPE_F32, DTYPE_BF16 = 0, 1
+DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
 KIND_REF, KIND_TILE, KIND_PIPE = 0, 1, 2
 
 

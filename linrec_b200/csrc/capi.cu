@@ -39,6 +39,7 @@ struct Options {
     int ctas_per_sm = 0;         // 0 = as many as fit
     int first_ticket = 0;        // diagnostics only: tickets start here instead of 0
     int lazy = -1;               // -1 = selector decides, 0/1 = one-ticket-at-a-time mode off/on (one ring slot only)
+    int l2_promotion = 3;        // tensor-map L2 promotion: 0 none, 1 64 B, 2 128 B, 3 256 B
     int p2p_phase = 0;           // peer-exchange calls: 0 = scan and fix-up, 1 = scan only, 2 = fix-up only
 };
 
@@ -60,6 +61,7 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "firstTicket")) out.first_ticket = v;
         else if (!strcmp(n, "p2pPhase")) out.p2p_phase = v;
         else if (!strcmp(n, "lazyTickets")) out.lazy = v;
+        else if (!strcmp(n, "l2Promotion")) out.l2_promotion = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
     }
     return LINREC_OK;
@@ -72,8 +74,8 @@ using GenericFn = void (*)(const ScanParams);
 
 struct TmaVariant {
     int E, NT, S, OB;
-    size_t smem[2][2];      // [dtype][bwd]
-    TmaFn fn[2][2][2];      // [dtype][bwd][asc]
+    size_t smem[3][2];      // [dtype][bwd]
+    TmaFn fn[3][2][2];      // [dtype][bwd][asc]
 };
 
 template <int E, int NT, int S, int OB>
@@ -94,12 +96,18 @@ TmaVariant make_tma_variant()
     v.fn[1][0][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, false, true>;
     v.fn[1][1][0] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, false>;
     v.fn[1][1][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, true>;
+    v.smem[2][0] = TmaLayout<__half, E, NT, S, OB, false>::kDynSmem;
+    v.smem[2][1] = TmaLayout<__half, E, NT, S, OB, true>::kDynSmem;
+    v.fn[2][0][0] = linrec_tma_kernel<__half, E, NT, S, OB, false, false>;
+    v.fn[2][0][1] = linrec_tma_kernel<__half, E, NT, S, OB, false, true>;
+    v.fn[2][1][0] = linrec_tma_kernel<__half, E, NT, S, OB, true, false>;
+    v.fn[2][1][1] = linrec_tma_kernel<__half, E, NT, S, OB, true, true>;
     return v;
 }
 
 struct GenericVariant {
     int E, NT;
-    GenericFn fn[2][2][2];  // [dtype][bwd][asc]
+    GenericFn fn[3][2][2];  // [dtype][bwd][asc]
 };
 
 template <int E, int NT>
@@ -116,6 +124,10 @@ GenericVariant make_generic_variant()
     v.fn[1][0][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, false, true>;
     v.fn[1][1][0] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, false>;
     v.fn[1][1][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, true>;
+    v.fn[2][0][0] = linrec_generic_kernel<__half, E, NT, false, false>;
+    v.fn[2][0][1] = linrec_generic_kernel<__half, E, NT, false, true>;
+    v.fn[2][1][0] = linrec_generic_kernel<__half, E, NT, true, false>;
+    v.fn[2][1][1] = linrec_generic_kernel<__half, E, NT, true, true>;
     return v;
 }
 
@@ -124,13 +136,8 @@ const std::vector<TmaVariant>& tma_variants()
     static const std::vector<TmaVariant> v = {
         make_tma_variant<16, 256, 2, 1>(),
         make_tma_variant<16, 256, 3, 1>(),
-        make_tma_variant<16, 256, 2, 2>(),
         make_tma_variant<16, 128, 3, 1>(),
-        make_tma_variant<16, 128, 4, 2>(),
         make_tma_variant<16, 128, 2, 1>(),
-        make_tma_variant<8, 256, 3, 1>(),
-        make_tma_variant<8, 256, 2, 1>(),
-        make_tma_variant<8, 512, 2, 1>(),
         make_tma_variant<16, 512, 2, 1>(),
         make_tma_variant<16, 512, 1, 1>(),
         make_tma_variant<16, 256, 1, 1>(),
@@ -237,7 +244,7 @@ EncodeTiledFn encode_tiled_fn()
 // Rank-3 view (elements of a 128-byte line, lines of a row, rows) of a row-major matrix with a
 // 128-byte swizzle; box = (one line, `box_lines`, `box_rows`).
 int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64_t seqlen,
-             int64_t row_stride, int box_lines, int box_rows)
+             int64_t row_stride, int box_lines, int box_rows, int l2_promotion)
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return LINREC_ERR_CUDA;
@@ -247,9 +254,13 @@ int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64
     const cuuint64_t strides[2] = {128, (cuuint64_t)row_stride * (cuuint64_t)sz};
     const cuuint32_t box[3] = {(cuuint32_t)epl, (cuuint32_t)box_lines, (cuuint32_t)box_rows};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(map, dtype == LINREC_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+    const CUresult r = enc(map, dtype == LINREC_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == LINREC_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                            3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_SWIZZLE_128B,
+                           l2_promotion == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                           : l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                           : l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? LINREC_OK : LINREC_ERR_CUDA;
 }
@@ -315,7 +326,7 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
     if (memcode != 0 && memcode != 1) return LINREC_ERR_NOT_IMPLEMENTED;
     if (memcode == 1 && !can_tma) return LINREC_ERR_UNALIGNED;
     pl.tma = memcode == 1;
-    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     if (pl.tma) {
         // Defaults of the selector (measured on B200, see the sweep of the standalone harness):
         // forward: 512 threads x 16 elements, two ring slots; backward: 128 x 16, two ring slots
@@ -394,7 +405,7 @@ size_t workspace_need(const Plan& pl)
 
 int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seqlen, int64_t row_stride, int dtype)
 {
-    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16 && dtype != LINREC_DTYPE_F16) return LINREC_ERR_NOT_IMPLEMENTED;
     if (numseq < 0 || seqlen < 0) return LINREC_ERR_INVALID_ARG;
     if (numseq == 0 || seqlen == 0) return LINREC_OK;
     if (row_stride < seqlen) return LINREC_ERR_INVALID_ARG;
@@ -435,7 +446,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.px = static_cast<const linrec::PeerTable*>(exchange);
     p.px_epoch = exchange ? px_epoch : 0u;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
-    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     // the gradient scan runs against the direction of the forward pass
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
 
@@ -446,9 +457,12 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
         if (di == 0) {
             if (bwd) linrec::linrec_seq_kernel<float, true><<<blocks, threads, 0, stream>>>(p, reverse);
             else     linrec::linrec_seq_kernel<float, false><<<blocks, threads, 0, stream>>>(p, reverse);
-        } else {
+        } else if (di == 1) {
             if (bwd) linrec::linrec_seq_kernel<__nv_bfloat16, true><<<blocks, threads, 0, stream>>>(p, reverse);
             else     linrec::linrec_seq_kernel<__nv_bfloat16, false><<<blocks, threads, 0, stream>>>(p, reverse);
+        } else {
+            if (bwd) linrec::linrec_seq_kernel<__half, true><<<blocks, threads, 0, stream>>>(p, reverse);
+            else     linrec::linrec_seq_kernel<__half, false><<<blocks, threads, 0, stream>>>(p, reverse);
         }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
@@ -495,7 +509,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
         const int box_rows = pl.chain ? 1 : pl.rows_per_tile;
         const void* src[5] = {in0, c, bwd ? yin : c, out0, bwd ? out1 : out0};
         for (int i = 0; i < 5; ++i) {
-            rc = make_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows);
+            rc = make_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows, opt.l2_promotion);
             if (rc != LINREC_OK) return rc;
         }
         pl.tv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
@@ -564,7 +578,8 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     fp.wait_budget = 2000LL * dev.clock_khz;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     return dtype == LINREC_DTYPE_F32 ? launch_fixup_t<float>(bwd, asc, fp, stream, dev.sm_count)
-                                     : launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count);
+           : dtype == LINREC_DTYPE_BF16 ? launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count)
+                                        : launch_fixup_t<__half>(bwd, asc, fp, stream, dev.sm_count);
 }
 }  // namespace
 
@@ -619,18 +634,19 @@ int linrec_b200_status(const void* workspace, void* stream)
 int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, const char** names, int* values, int cap)
 {
     if (!names || !values || cap <= 0) return LINREC_ERR_INVALID_ARG;
-    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16 && dtype != LINREC_DTYPE_F16) return LINREC_ERR_NOT_IMPLEMENTED;
     Options opt;
     int rc = parse_options(opts, opt);
     if (rc != LINREC_OK) return rc;
-    const int di = dtype == LINREC_DTYPE_F32 ? 0 : 1;
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     const bool bwd = !fwd;
     const void* fn = nullptr;
     int E = 0, NT = 0, S = 0, OB = 0, memcode = 0;
     size_t dyn = 0;
     if (kind == LINREC_KIND_REF) {
         fn = di == 0 ? (bwd ? (const void*)linrec::linrec_seq_kernel<float, true> : (const void*)linrec::linrec_seq_kernel<float, false>)
-                     : (bwd ? (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, true> : (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, false>);
+                     : di == 1 ? (bwd ? (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, true> : (const void*)linrec::linrec_seq_kernel<__nv_bfloat16, false>)
+                               : (bwd ? (const void*)linrec::linrec_seq_kernel<__half, true> : (const void*)linrec::linrec_seq_kernel<__half, false>);
         E = 1; NT = 128;
     } else {
         // attributes are reported for an aligned problem unless memcode=0 is asked for

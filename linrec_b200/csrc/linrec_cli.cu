@@ -2,12 +2,13 @@
 // and the tuning sweep.  Counterpart of the reference's linrec/impl/cuda/executable.cpp:16-68,
 // which runs its ref and pipe operators on random data and prints registers and max error.
 //
-//   linrec_cli --numseq 512 --seqlen 65536 [--reverse] [--bwd] [--dtype f32|bf16]
+//   linrec_cli --numseq 512 --seqlen 65536 [--reverse] [--bwd] [--dtype f32|bf16|f16]
 //              [--clo 0 --chi 1] [--stride N] [--iters 20 --warmup 3] [--flush]
 //              [--opt name=value ...] [--sweep] [--no-verify] [--kind pipe|tile|ref]
 //
 // Prints one JSON object per measured configuration.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -45,8 +46,13 @@ __device__ inline float cast_to<float>(float v) { return v; }
 template <>
 __device__ inline __nv_bfloat16 cast_to<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+template <>
+__device__ inline __half cast_to<__half>(float v) { return __float2half_rn(v); }
+
 template <typename T>
 __device__ inline float cast_from(T v);
+template <>
+__device__ inline float cast_from<__half>(__half v) { return __half2float(v); }
 template <>
 __device__ inline float cast_from<float>(float v) { return v; }
 template <>
@@ -104,7 +110,7 @@ struct Args {
 static void usage()
 {
     fprintf(stderr,
-            "usage: linrec_cli [--numseq N] [--seqlen L] [--stride S] [--reverse] [--bwd] [--dtype f32|bf16]\n"
+            "usage: linrec_cli [--numseq N] [--seqlen L] [--stride S] [--reverse] [--bwd] [--dtype f32|bf16|f16]\n"
             "                  [--clo a --chi b] [--iters K --warmup W] [--flush] [--opt name=value ...]\n"
             "                  [--sweep] [--no-verify] [--kind pipe|tile|ref]\n");
 }
@@ -140,7 +146,7 @@ static Result run_one(const Args& a, const std::vector<std::string>& names, cons
     CK(cudaDeviceSynchronize());
     r.status = linrec_b200_status(ws, st);
     if (a.verify) {
-        const float rtol = a.dtype == LINREC_DTYPE_F32 ? 1e-4f : 7.8125e-3f, atol = 1e-5f;
+        const float rtol = a.dtype == LINREC_DTYPE_F32 ? 1e-4f : a.dtype == LINREC_DTYPE_BF16 ? 7.8125e-3f : 1.953125e-3f, atol = 1e-5f;
         float hm;
         unsigned long long hb;
         CK(cudaMemset(d_max, 0, sizeof(float)));
@@ -259,7 +265,7 @@ static int run(const Args& a)
         }
         Result r = run_one<T>(a, names, values, in0, c, yfw, out0, out1, ref0, ref1, ws, ws_bytes, flush_buf, flush_n, d_max, d_bad);
         printf("{\"numseq\": %lld, \"seqlen\": %lld, \"stride\": %lld, \"reverse\": %d, \"bwd\": %d, \"dtype\": \"%s\", \"kind\": %d, \"opts\": {",
-               a.numseq, a.seqlen, a.stride, a.reverse, a.bwd, a.dtype == LINREC_DTYPE_F32 ? "f32" : "bf16", a.kind);
+               a.numseq, a.seqlen, a.stride, a.reverse, a.bwd, a.dtype == LINREC_DTYPE_F32 ? "f32" : a.dtype == LINREC_DTYPE_BF16 ? "bf16" : "f16", a.kind);
         for (size_t i = 0; i < names.size(); ++i) printf("%s\"%s\": %d", i ? ", " : "", names[i].c_str(), values[i]);
         printf("}, \"rc\": %d, \"status\": %d", r.rc, r.status);
         if (r.rc == LINREC_OK) {
@@ -299,7 +305,7 @@ int main(int argc, char** argv)
         else if (s == "--stride") a.stride = atoll(next());
         else if (s == "--reverse") a.reverse = 1;
         else if (s == "--bwd") a.bwd = 1;
-        else if (s == "--dtype") a.dtype = !strcmp(next(), "bf16") ? LINREC_DTYPE_BF16 : LINREC_DTYPE_F32;
+        else if (s == "--dtype") { std::string d = next(); a.dtype = d == "bf16" ? LINREC_DTYPE_BF16 : d == "f16" ? LINREC_DTYPE_F16 : LINREC_DTYPE_F32; }
         else if (s == "--clo") a.clo = (float)atof(next());
         else if (s == "--chi") a.chi = (float)atof(next());
         else if (s == "--iters") a.iters = atoi(next());
@@ -326,5 +332,5 @@ int main(int argc, char** argv)
     cudaDeviceProp prop;
     CK(cudaGetDeviceProperties(&prop, 0));
     fprintf(stderr, "# device: %s, %d SMs, library version %d\n", prop.name, prop.multiProcessorCount, linrec_b200_version());
-    return a.dtype == LINREC_DTYPE_F32 ? run<float>(a) : run<__nv_bfloat16>(a);
+    return a.dtype == LINREC_DTYPE_F32 ? run<float>(a) : a.dtype == LINREC_DTYPE_BF16 ? run<__nv_bfloat16>(a) : run<__half>(a);
 }

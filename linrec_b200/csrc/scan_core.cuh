@@ -21,6 +21,7 @@
 // that precede this thread inside the tile).
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "ptx.cuh"
 
@@ -187,6 +188,8 @@ struct Storage<float> {
     }
     __device__ static __forceinline__ float to_float(float v) { return v; }
     __device__ static __forceinline__ float from_float(float v) { return v; }
+    static constexpr uint32_t kOnePair = 0x3f800000u;   // the value 1 as a 32-bit word
+    __device__ static __forceinline__ float half_of_word(uint32_t w, bool) { return __uint_as_float(w); }
 };
 
 template <>
@@ -213,6 +216,46 @@ struct Storage<__nv_bfloat16> {
     }
     __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+    static constexpr uint32_t kOnePair = 0x3f803f80u;   // the value 1 in both halves of a 32-bit word
+    __device__ static __forceinline__ float half_of_word(uint32_t w, bool upper)
+    {
+        return __uint_as_float(upper ? (w & 0xffff0000u) : (w << 16));
+    }
+};
+
+template <>
+struct Storage<__half> {
+    static constexpr int kPerChunk = 8;
+    __device__ static __forceinline__ void unpack(const uint4& q, float* v)
+    {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float* v)
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static __forceinline__ float to_float(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
+    // the value 1 in both halves of a 32-bit word
+    static constexpr uint32_t kOnePair = 0x3c003c00u;
+    // a 2-byte element held in the low / high half of a 32-bit word, as float
+    __device__ static __forceinline__ float half_of_word(uint32_t w, bool upper)
+    {
+        const unsigned short bits = upper ? (unsigned short)(w >> 16) : (unsigned short)(w & 0xffffu);
+        return __half2float(__ushort_as_half(bits));
+    }
 };
 
 // Sequence sharding: the record of one row of this shard -- (P, Y) of the whole shard and, for the

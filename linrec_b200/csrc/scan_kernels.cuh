@@ -210,7 +210,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             // 4-byte copies from the 4-byte-aligned word that contains the element
             // (a coefficient that lies before an open shard start is 1; both halves for 2-byte storage)
             if (c_ok) ptx::cp_async_4(&halo[s][0], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(csrc) & ~(uintptr_t)3));
-            else halo[s][0] = !p.open_start ? 0u : (sizeof(ST) == 4 ? 0x3f800000u : 0x3f803f80u);
+            else halo[s][0] = !p.open_start ? 0u : Storage<ST>::kOnePair;
             if (y_ok) ptx::cp_async_4(&halo[s][1], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ysrc) & ~(uintptr_t)3));
             else halo[s][1] = 0u;
             ptx::cp_async_mbar_arrive_noinc(&full[s]);
@@ -264,15 +264,10 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         if (with_halo) {
             // the halo word holds the element in its low or high half for 2-byte storage
             const uint32_t wc = halo[s][0], wy = halo[s][1];
-            if (sizeof(ST) == 4) {
-                pred_c = __uint_as_float(wc);
-                succ_y = __uint_as_float(wy);
-            } else {
-                // element below the piece has an odd index (upper half), above it an even one
-                const bool c_upper = ASC, y_upper = !ASC;
-                pred_c = __uint_as_float(c_upper ? (wc & 0xffff0000u) : (wc << 16));
-                succ_y = __uint_as_float(y_upper ? (wy & 0xffff0000u) : (wy << 16));
-            }
+            // 2-byte storage: the element below the piece has an odd index (upper half of its word),
+            // the element above it an even one (lower half)
+            pred_c = Storage<ST>::half_of_word(wc, ASC);
+            succ_y = Storage<ST>::half_of_word(wy, !ASC);
         }
         const bool zero_first =
             !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
@@ -378,7 +373,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             // 16-byte chunks: rows are 16-byte aligned and a whole number of chunks long, so a chunk
             // lies entirely inside or entirely outside its row
             constexpr int PC = Storage<ST>::kPerChunk;
-            constexpr uint32_t kOne = sizeof(ST) == 4 ? 0x3f800000u : 0x3f803f80u;
+            constexpr uint32_t kOne = Storage<ST>::kOnePair;
             const int cpr = spr / PC;
             const long long first_col = ASC ? 0 : p.seqlen - PC;   // chunk that holds the row's scan-first element
             for (int ci = tid; ci < T / PC; ci += NT) {

@@ -5,7 +5,7 @@ namespace with fake implementations and autograd registration -- on top of the C
 
     y = linrec_pipe(inputs, coeffs, reverse=False)        # y[i] = y[i-1]*coeffs[i] + inputs[i]
 
-Differences from the reference, all widening: bfloat16 storage is accepted next to float32
+Differences from the reference, all widening: bfloat16 and float16 storage are accepted next to float32
 (arithmetic stays fp32); rows may have a stride larger than their length; tensors whose leading
 dimensions cannot be described by one row stride are made contiguous instead of being read as if
 they were; element counts are 64-bit.
@@ -24,7 +24,7 @@ from . import _capi
 
 __all__ = ["linrec_ref", "linrec_tile", "linrec_pipe"]
 
-_DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
+_DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16, torch.float16: _capi.DTYPE_F16}
 _CHECK_EVERY_CALL = os.environ.get("LINREC_B200_CHECK", "0") not in ("0", "")
 
 # ---- workspace cache: one scratch buffer per (device, stream) --------------------------------------
@@ -71,7 +71,7 @@ def _check_same(*ts: torch.Tensor) -> None:
     if not all(t.is_cuda for t in ts):
         raise RuntimeError("linrec: tensors must be CUDA tensors (there is no CPU implementation)")
     if a.dtype not in _DTYPES:
-        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16)")
+        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16, float16)")
     if a.dim() == 0:
         raise RuntimeError("linrec: need at least one dimension")
     if a.numel() > 0 and a.stride(-1) != 1:

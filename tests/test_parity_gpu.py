@@ -125,17 +125,20 @@ BF16_RTOL = 2.0 ** -7
 @pytest.mark.parametrize("shape", [(64, 512), (300, 64), (5, 3 * 8192), (3, 1000), (7, 4097), (16, 65536), (2, 2 * 8192 + 64)],
                          ids=lambda s: f"{s[0]}x{s[1]}")
 @pytest.mark.parametrize("rev", [False, True])
-def test_bf16_storage(shape, rev):
-    """Inputs rounded to bf16; the oracle runs in fp32 on the upcast inputs; our outputs are fp32
-    accumulations rounded once to bf16 (relative error <= 2^-9), tolerance rtol 2^-7 / atol 1e-5."""
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+def test_bf16_storage(shape, rev, dtype):
+    """Inputs rounded to 2-byte storage; the oracle runs in fp32 on the upcast inputs; our outputs are
+    fp32 accumulations rounded once to the storage type.  bf16 (8 significant bits, rounding <= 2^-9):
+    rtol 2^-7 / atol 1e-5; fp16 (11 bits, rounding <= 2^-12): rtol 2^-9 / atol 1e-5."""
     lb = _ops()
     dev = torch.device("cuda:0")
-    x, c, dy = (t.bfloat16() for t in _data(shape, clo=0.5, chi=1.0))
+    BF16_RTOL = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9
+    x, c, dy = (t.to(dtype) for t in _data(shape, clo=0.5, chi=1.0))
     y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
-    assert y.dtype == torch.bfloat16
+    assert y.dtype == dtype
     y_ref = oracle.fwd_f32(x.float().numpy(), c.float().numpy(), reverse=rev)
     np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=BF16_RTOL, atol=ATOL)
-    yb = torch.from_numpy(y_ref).bfloat16()
+    yb = torch.from_numpy(y_ref).to(dtype)
     dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yb.to(dev), reverse=rev)
     dx_ref, dc_ref = oracle.bwd_f32(dy.float().numpy(), c.float().numpy(), yb.float().numpy(), reverse=rev)
     np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=BF16_RTOL, atol=ATOL)
@@ -299,6 +302,37 @@ def test_handful_of_very_long_rows(rev):
     _check_fwd_bwd(x, c, dy, rev)
     _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=128, kStages=1, lazyTickets=1)
     _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=256, kStages=1, lazyTickets=0)
+
+
+def test_cuda_graph_capture_and_replay():
+    """An operator is one kernel launch on a self-cleaning workspace, so a forward + backward step can
+    be captured into a CUDA graph once and replayed on new data."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    shape = (64, 3 * 8192)
+    x, c, dy = (t.to(dev) for t in _data(shape, clo=0.8))
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):          # warm-up on the capture stream: attributes, workspace
+        for _ in range(2):
+            y = lb._C.linrec_pipe_fwd(inputs=x, coeffs=c)
+            lb._C.linrec_pipe_bwd(d_outputs=dy, coeffs=c, outputs=y)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        y = lb._C.linrec_pipe_fwd(inputs=x, coeffs=c)
+        dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy, coeffs=c, outputs=y)
+    for seed in (1, 2, 3):
+        x2, c2, dy2 = _data(shape, clo=0.8, seed=seed)
+        x.copy_(x2); c.copy_(c2); dy.copy_(dy2)
+        graph.replay()
+        torch.cuda.synchronize()
+        y_ref = oracle.fwd_f32(x2.numpy(), c2.numpy())
+        dx_ref, dc_ref = oracle.bwd_f32(dy2.numpy(), c2.numpy(), y.cpu().numpy())
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=RTOL, atol=4 * ATOL)
+    lb.check_status()
 
 
 def test_host_streamed_path():
