@@ -20,7 +20,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liblinrec_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "liblinrec_refcuda.so")
-DEFAULT_REFERENCE = os.environ.get("LINREC_REFERENCE_DIR", "/root/reference")
+# the reference checkout: $LINREC_REFERENCE_DIR, else a directory "reference" next to this repository
+DEFAULT_REFERENCE = os.environ.get("LINREC_REFERENCE_DIR",
+                                   os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _newer(target: str, *sources: str) -> bool:

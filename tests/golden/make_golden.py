@@ -5,7 +5,7 @@ importing its Python implementation (linrec/impl/python/ops.py: `linrec_ref_fwd`
 `linrec_ref_bwd`, and autograd through `linrec_ref`) on CPU and recording inputs and outputs.
 Run on a machine that has the reference checked out:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path to the safelix/linrec checkout>
 
 The inputs are stored with the outputs, so the fixtures do not depend on a torch RNG stream.
 """
@@ -45,7 +45,8 @@ def load_reference_ops(reference: str):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get(
+        "LINREC_REFERENCE_DIR", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")))
     ap.add_argument("--out", default=os.path.join(HERE, "linrec_golden.npz"))
     args = ap.parse_args()
     ref = load_reference_ops(args.reference)

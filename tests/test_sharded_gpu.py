@@ -65,7 +65,7 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
         np.testing.assert_allclose(y, y_ref, rtol=RTOL, atol=ATOL)
     else:
         # slowly decaying coefficients: two valid fp32 orders differ by more than the nominal
-        # tolerance near zero crossings, so the fp64 evaluation is the judge
+        # tolerance near zero crossings, so the fp64 evaluation is the arbiter
         _judge_against_f64(y, y_ref, y64, "y")
     # backward, from the oracle's forward outputs
     yg = [torch.from_numpy(np.ascontiguousarray(y_ref[:, s * Ls:(s + 1) * Ls])).to(dev) for s in range(G)]
