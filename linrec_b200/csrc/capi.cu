@@ -347,16 +347,17 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             if (handful) {
                 E = 16; NT = 512; S = 1; OB = 1;
             } else if (sz == 4) {
-                if (!bwd)          { E = 16; NT = 512; S = 2; OB = 1; }
-                else if (few_rows) { E = 16; NT = 512; S = 1; OB = 1; }
-                else               { E = 16; NT = 128; S = 2; OB = 1; }
+                // backward: one ring slot and more resident CTAs beat a deeper ring (five arrays per
+                // tile); rows up to 8192 take the 8192-element tile and never chain
+                if (!bwd)                          { E = 16; NT = 512; S = 2; OB = 1; }
+                else if (seqlen <= 8192 || few_rows) { E = 16; NT = 512; S = 1; OB = 1; }
+                else                               { E = 16; NT = 128; S = 1; OB = 1; }
             } else {
                 // 2-byte storage moves half the bytes per element, so instruction issue starts to
                 // matter: 32 elements per thread halve the shuffle and barrier cost per element
-                if (short_rows)    { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
-                else if (few_rows) { E = 32; NT = 256; S = 2; OB = 1; }
-                else if (!bwd)     { E = 32; NT = 128; S = 3; OB = 1; }
-                else               { E = 16; NT = 128; S = 3; OB = 1; }
+                if (short_rows) { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
+                else if (!bwd)  { E = 32; NT = 256; S = 2; OB = 1; }
+                else            { E = 32; NT = 128; S = 2; OB = 1; }
             }
         }
         const TmaVariant* best = nullptr;

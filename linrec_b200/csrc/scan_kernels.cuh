@@ -136,10 +136,13 @@ struct TmaLayout {
     static constexpr size_t kTileBytes = (size_t)T * sizeof(ST);
     static constexpr size_t kDynSmem = kTileBytes * (S * NIN + OB * NOUT) + 1024;   // + alignment slack
     static_assert(kTileBytes % 1024 == 0, "tile buffers must keep 1024-byte alignment");
-    // CTAs per SM the kernel is compiled for: what shared memory allows, at no more than 512 threads
-    // per SM (so that the register allocator keeps at least 128 registers per thread)
+    // CTAs per SM the kernel is compiled for: what shared memory allows, up to a thread count that
+    // leaves the register allocator what the pass needs (forward with 16 elements per thread: ~80
+    // registers -> 768 threads; backward or 32 elements per thread: ~128 -> 512 threads)
     static constexpr int kFitSmem = (int)((size_t)232448 / (kDynSmem + 1024 + 512));
-    static constexpr int kMinBlocks = kFitSmem < 1 ? 1 : (kFitSmem < 512 / NT ? kFitSmem : (512 / NT < 1 ? 1 : 512 / NT));
+    static constexpr int kMaxThreads = (BWD || E >= 32) ? 512 : 768;
+    static constexpr int kByThreads = kMaxThreads / NT < 1 ? 1 : kMaxThreads / NT;
+    static constexpr int kMinBlocks = kFitSmem < 1 ? 1 : (kFitSmem < kByThreads ? kFitSmem : kByThreads);
 };
 
 template <typename ST, int E, int NT, int S, int OB, bool BWD, bool ASC>
