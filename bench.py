@@ -49,7 +49,7 @@ FALLBACK_PEAK_GBS = 6650.0
 # DRAM traffic of the backward kernel measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum
 # per launch, divided by the elements of the captured launch); the capture and its command are in
 # profiles/.
-NCU_DRAM_BYTES_PER_ELEM_BWD = 5.35e9 / 268435456   # full-size capture, profiles/linrec_tma_kernel_bwd_f32_4096x8192.md
+NCU_DRAM_BYTES_PER_ELEM_BWD = 5.32e9 / 268435456   # full-size capture, profiles/linrec_tma_kernel_bwd_f32_4096x8192.md
 
 
 def _peak():
