@@ -124,7 +124,7 @@ LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
  *      gathered[(s*numseq + r)*rec + k]   (one all-gather; rec = 2 forward, 4 backward);
  *   3. *_fixup   folds the records of the shards that come earlier in scan order and adds
  *                carry * running product of the coefficients to this shard's results in place.  The
- *                walk along a row stops once the carried value has underflowed to exactly zero.
+ *                walk along a row stops once the carried value has underflowed below the normal range.
  * `reverse` is the flag of the forward pass in all four. */
 LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,

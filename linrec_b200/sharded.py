@@ -10,7 +10,7 @@ sequence sharding  every rank holds the columns [rank*L, (rank+1)*L) of ALL rows
                    all-gathered once (NCCL over NVLink; 8 or 16 bytes per row and rank), and a fused
                    fix-up kernel folds the records of the earlier shards and adds
                    `carry * running product of c` to the local result, stopping along each row as
-                   soon as that correction has underflowed to exactly zero.
+                   soon as that correction has underflowed below the normal range (it could no longer change a result).
 
 `linrec_seq_sharded(x_shard, c_shard, reverse=False, group=None)` is differentiable; its backward
 does the same three steps with the gradient scan.
