@@ -163,3 +163,25 @@ def test_config5_slab_slow_decay(rev):
     scale = max(1.0, float(np.abs(ys).max()))
     _judge(dc[rows].cpu().numpy() / scale, dc32 / scale, dc64 / scale, "dc")
     lb.check_status()
+
+
+def test_more_than_2_to_31_elements():
+    """64-bit element offsets: (4100, 2^19) = 2.15e9 elements per tensor (the reference's kernels
+    index with int and stop below 2^31, linrec_pipe.cuh:14, linrec_tile.cu:61).  Rows at the far end
+    of the tensor are checked against the CPU oracle, forward and backward."""
+    lb, dev = _lb(), torch.device("cuda:0")
+    n, L = 4100, 1 << 19
+    assert n * L > 2 ** 31
+    g = torch.Generator(device=dev).manual_seed(SEED + 6)
+    x = torch.randn((n, L), device=dev, generator=g)
+    c = torch.rand((n, L), device=dev, generator=g)
+    y = lb.linrec(x, c)
+    rows = torch.tensor([0, 1, 2047, 4095, 4096, 4099])
+    np.testing.assert_allclose(y[rows].cpu().numpy(), oracle.fwd_f32(x[rows].cpu().numpy(), c[rows].cpu().numpy()),
+                               rtol=RTOL, atol=ATOL)
+    # backward writes two tensors: reuse x as the upstream gradient to stay within memory
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=x, coeffs=c, outputs=y)
+    dx_o, dc_o = oracle.bwd_f32(x[rows].cpu().numpy(), c[rows].cpu().numpy(), y[rows].cpu().numpy())
+    np.testing.assert_allclose(dx[rows].cpu().numpy(), dx_o, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(dc[rows].cpu().numpy(), dc_o, rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()
