@@ -31,7 +31,8 @@ std::atomic<uint64_t> g_launches{0};
 const char* const kConfigNames[] = {"kElemsPerThread", "kThreadsPerBlock", "kStages", "kOutBuffers", "memcode"};
 constexpr int kNumConfigNames = 5;
 // memcode: 0 = plain coalesced loads/stores staged through shared memory (any alignment),
-//          1 = tiled bulk-tensor copies (TMA) through an mbarrier ring.
+//          1 = tiled bulk-tensor copies (TMA) through an mbarrier ring (rows of whole 128-byte lines),
+//          2 = 16-byte cp.async through a two-slot ring (16-byte aligned rows of whole 16-byte chunks).
 
 struct Options {
     int E = -1, NT = -1, S = -1, OB = -1, memcode = -1;
@@ -106,7 +107,8 @@ TmaVariant make_tma_variant()
 }
 
 struct GenericVariant {
-    int E, NT;
+    int E, NT, S;
+    size_t smem[3][2];      // [dtype][bwd]: dynamic shared memory (0 for the plain-load kernel)
     GenericFn fn[3][2][2];  // [dtype][bwd][asc]
 };
 
@@ -115,7 +117,7 @@ GenericVariant make_generic_variant()
 {
     using namespace linrec;
     GenericVariant v{};
-    v.E = E; v.NT = NT;
+    v.E = E; v.NT = NT; v.S = 1;
     v.fn[0][0][0] = linrec_generic_kernel<float, E, NT, false, false>;
     v.fn[0][0][1] = linrec_generic_kernel<float, E, NT, false, true>;
     v.fn[0][1][0] = linrec_generic_kernel<float, E, NT, true, false>;
@@ -128,6 +130,33 @@ GenericVariant make_generic_variant()
     v.fn[2][0][1] = linrec_generic_kernel<__half, E, NT, false, true>;
     v.fn[2][1][0] = linrec_generic_kernel<__half, E, NT, true, false>;
     v.fn[2][1][1] = linrec_generic_kernel<__half, E, NT, true, true>;
+    return v;
+}
+
+template <int E, int NT, int S>
+GenericVariant make_async_variant()
+{
+    using namespace linrec;
+    GenericVariant v{};
+    v.E = E; v.NT = NT; v.S = S;
+    v.smem[0][0] = AsyncLayout<float, E, NT, S, false>::kDynSmem;
+    v.smem[0][1] = AsyncLayout<float, E, NT, S, true>::kDynSmem;
+    v.smem[1][0] = AsyncLayout<__nv_bfloat16, E, NT, S, false>::kDynSmem;
+    v.smem[1][1] = AsyncLayout<__nv_bfloat16, E, NT, S, true>::kDynSmem;
+    v.smem[2][0] = AsyncLayout<__half, E, NT, S, false>::kDynSmem;
+    v.smem[2][1] = AsyncLayout<__half, E, NT, S, true>::kDynSmem;
+    v.fn[0][0][0] = linrec_async_kernel<float, E, NT, S, false, false>;
+    v.fn[0][0][1] = linrec_async_kernel<float, E, NT, S, false, true>;
+    v.fn[0][1][0] = linrec_async_kernel<float, E, NT, S, true, false>;
+    v.fn[0][1][1] = linrec_async_kernel<float, E, NT, S, true, true>;
+    v.fn[1][0][0] = linrec_async_kernel<__nv_bfloat16, E, NT, S, false, false>;
+    v.fn[1][0][1] = linrec_async_kernel<__nv_bfloat16, E, NT, S, false, true>;
+    v.fn[1][1][0] = linrec_async_kernel<__nv_bfloat16, E, NT, S, true, false>;
+    v.fn[1][1][1] = linrec_async_kernel<__nv_bfloat16, E, NT, S, true, true>;
+    v.fn[2][0][0] = linrec_async_kernel<__half, E, NT, S, false, false>;
+    v.fn[2][0][1] = linrec_async_kernel<__half, E, NT, S, false, true>;
+    v.fn[2][1][0] = linrec_async_kernel<__half, E, NT, S, true, false>;
+    v.fn[2][1][1] = linrec_async_kernel<__half, E, NT, S, true, true>;
     return v;
 }
 
@@ -154,6 +183,19 @@ const std::vector<GenericVariant>& generic_variants()
     static const std::vector<GenericVariant> v = {
         make_generic_variant<16, 128>(),
         make_generic_variant<8, 128>(),
+    };
+    return v;
+}
+
+// 16-byte cp.async loader, two ring slots: aligned rows whose length is not a multiple of 128 bytes
+const std::vector<GenericVariant>& async_variants()
+{
+    static const std::vector<GenericVariant> v = {
+        make_async_variant<16, 128, 2>(),
+        make_async_variant<16, 128, 3>(),
+        make_async_variant<32, 128, 2>(),
+        make_async_variant<16, 256, 2>(),
+        make_async_variant<16, 512, 2>(),
     };
     return v;
 }
@@ -268,6 +310,7 @@ int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64
 // ---- planning ------------------------------------------------------------------------------------
 struct Plan {
     bool tma = false;
+    bool async_copy = false;
     const TmaVariant* tv = nullptr;
     const GenericVariant* gv = nullptr;
     int E = 0, NT = 0, T = 0;
@@ -286,6 +329,16 @@ bool tma_eligible(int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride,
     if ((row_stride * sz) % 16 != 0) return false;
     if (numseq > 0x7fffffffLL || seqlen / (128 / sz) > 0x7fffffffLL) return false;
     if ((uint64_t)row_stride * sz >= (1ull << 40)) return false;
+    for (int i = 0; i < nptrs; ++i)
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
+    return true;
+}
+
+// 16-byte global accesses outside the bulk-copy kernel: aligned rows of whole 16-byte chunks
+bool vec_eligible(int dtype, int64_t seqlen, int64_t row_stride, const void* const* ptrs, int nptrs)
+{
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    if ((row_stride * sz) % 16 != 0 || (seqlen * sz) % 16 != 0) return false;
     for (int i = 0; i < nptrs; ++i)
         if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
     return true;
@@ -321,11 +374,14 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
               const void* const* ptrs, int nptrs, const Options& opt, int max_smem, int sm_count)
 {
     const bool can_tma = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, nptrs);
+    const bool can_vec = vec_eligible(dtype, seqlen, row_stride, ptrs, nptrs);
     int memcode = opt.memcode;
-    if (memcode < 0) memcode = can_tma ? 1 : 0;
-    if (memcode != 0 && memcode != 1) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (memcode < 0) memcode = can_tma ? 1 : (can_vec ? 2 : 0);
+    if (memcode < 0 || memcode > 2) return LINREC_ERR_NOT_IMPLEMENTED;
     if (memcode == 1 && !can_tma) return LINREC_ERR_UNALIGNED;
+    if (memcode == 2 && !can_vec) return LINREC_ERR_UNALIGNED;
     pl.tma = memcode == 1;
+    pl.async_copy = memcode == 2;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     if (pl.tma) {
         // Defaults of the selector (measured on B200, see the sweep of the standalone harness):
@@ -379,6 +435,36 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
         }
         pl.tv = best;
         pl.E = pl.tv->E; pl.NT = pl.tv->NT;
+    } else if (pl.async_copy) {
+        if (opt.OB > 0) return LINREC_ERR_NOT_IMPLEMENTED;
+        const bool pinned = !(opt.E < 0 && opt.NT < 0 && opt.S < 0);
+        int E = opt.E, NT = opt.NT, S = opt.S;
+        if (!pinned && kind != LINREC_KIND_TILE) {
+            // Many rows: the small tile and many resident CTAs.  Few long rows: consecutive tickets are
+            // pieces of the same row and wait for each other, so larger tiles; a handful of very long
+            // rows: the largest tile, one ticket at a time.
+            const bool few_rows = seqlen > 2048 && numseq < 4LL * sm_count;
+            const bool handful = seqlen > 8192 && numseq < 32;
+            pl.lazy_default = handful;
+            S = 2;
+            if (handful)       { E = 16; NT = 512; }
+            else if (few_rows) { E = 32; NT = 128; }
+            else               { E = 16; NT = 128; }
+        }
+        for (const GenericVariant& v : async_variants()) {
+            if (!((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S))) continue;
+            if (v.smem[di][bwd] > (size_t)max_smem) continue;
+            if (!pinned && kind == LINREC_KIND_TILE) {
+                // smallest tile that holds the (padded) row
+                if (v.E * v.NT < round_up(seqlen, v.E)) continue;
+                if (!pl.gv || v.E * v.NT < pl.gv->E * pl.gv->NT) pl.gv = &v;
+            } else {
+                pl.gv = &v;
+                break;
+            }
+        }
+        if (!pl.gv) return (!pinned && kind == LINREC_KIND_TILE) ? LINREC_ERR_TOO_LONG : LINREC_ERR_NOT_IMPLEMENTED;
+        pl.E = pl.gv->E; pl.NT = pl.gv->NT;
     } else {
         if (opt.S > 1 || opt.OB > 0) return LINREC_ERR_NOT_IMPLEMENTED;
         for (const GenericVariant& v : generic_variants()) {
@@ -485,7 +571,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
 
     const void* fn = pl.tma ? reinterpret_cast<const void*>(pl.tv->fn[di][bwd][asc])
                             : reinterpret_cast<const void*>(pl.gv->fn[di][bwd][asc]);
-    const size_t smem = pl.tma ? pl.tv->smem[di][bwd] : 0;
+    const size_t smem = pl.tma ? pl.tv->smem[di][bwd] : pl.gv->smem[di][bwd];
     int occ = 0;
     rc = occupancy(fn, pl.NT, smem, occ);
     if (rc != LINREC_OK) return rc;
@@ -495,14 +581,8 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
 
     // The workspace cleans up after every launch by itself (see scan_core.cuh): nothing to prepare.
     p.first_ticket = (uint32_t)opt.first_ticket;
-    p.lazy = pl.tma && pl.chain && pl.tv->S == 1 && (opt.lazy >= 0 ? opt.lazy != 0 : pl.lazy_default);
-    {
-        // 16-byte global accesses in the any-alignment kernel: aligned rows of whole 16-byte chunks
-        const int sz = di == 0 ? 4 : 2;
-        bool al = (row_stride * sz) % 16 == 0 && (seqlen * sz) % 16 == 0;
-        for (int i = 0; i < 5 && al; ++i) al = reinterpret_cast<uintptr_t>(ptrs[i]) % 16 == 0;
-        p.vec = al ? 1 : 0;
-    }
+    p.lazy = pl.chain && (pl.tma ? pl.tv->S == 1 : pl.async_copy) && (opt.lazy >= 0 ? opt.lazy != 0 : pl.lazy_default);
+    p.vec = vec_eligible(dtype, seqlen, row_stride, ptrs, 5) ? 1 : 0;
 
     if (pl.tma) {
         CUtensorMap m[5];
@@ -515,7 +595,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
         }
         pl.tv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
     } else {
-        pl.gv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, 0, stream>>>(p);
+        pl.gv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(p);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
@@ -598,6 +678,7 @@ size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype)
         int tmin = 1 << 30;
         for (const TmaVariant& v : tma_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         for (const GenericVariant& v : generic_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
+        for (const GenericVariant& v : async_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         if (seqlen > tmin) n += (size_t)numseq * (size_t)ceil_div(seqlen, tmin) * sizeof(TileDesc);
     }
     return (size_t)round_up((int64_t)n, 256);
@@ -667,7 +748,8 @@ int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, con
             dyn = pl.tv->smem[di][bwd];
         } else {
             fn = reinterpret_cast<const void*>(pl.gv->fn[di][bwd][1]);
-            E = pl.gv->E; NT = pl.gv->NT; S = 1; OB = 0; memcode = 0;
+            E = pl.gv->E; NT = pl.gv->NT; S = pl.gv->S; OB = 0; memcode = pl.async_copy ? 2 : 0;
+            dyn = pl.gv->smem[di][bwd];
         }
     }
     cudaFuncAttributes a;
@@ -710,6 +792,7 @@ int linrec_b200_config_list(int* values, int cap_rows)
     };
     for (const TmaVariant& v : tma_variants()) put(v.E, v.NT, v.S, v.OB, 1);
     for (const GenericVariant& v : generic_variants()) put(v.E, v.NT, 1, 0, 0);
+    for (const GenericVariant& v : async_variants()) put(v.E, v.NT, v.S, 0, 2);
     return row;
 }
 

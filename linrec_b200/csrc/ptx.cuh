@@ -122,6 +122,21 @@ __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gsrc)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's committed cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // The barrier receives one arrival (already included in its expected count) once all earlier
 // cp.async of this thread have landed.
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar)

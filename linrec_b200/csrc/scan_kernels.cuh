@@ -480,6 +480,197 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
 }
 
 // =================================================================================================
+//  Asynchronous-copy kernel: 16-byte aligned rows that the bulk-copy kernel cannot take
+// =================================================================================================
+// Rows that are 16-byte aligned and a whole number of 16-byte chunks long, but not a multiple of 128
+// bytes (L = 1000, 10000, ...): every thread copies its share of a tile with 16-byte cp.async
+// straight into the swizzled layout through a ring of S tiles (the copies of the next S-1 tiles are
+// in flight while tile i is scanned); padding chunks are written as identities.  Results go back through the same
+// shared tile and leave with 16-byte stores.  Same tile algebra and look-back as the other kernels.
+template <typename ST, int E, int NT, int S, bool BWD>
+struct AsyncLayout {
+    static constexpr int T = E * NT;
+    static constexpr int NIN = BWD ? 3 : 2;
+    static constexpr size_t kTileBytes = (size_t)T * sizeof(ST);
+    static constexpr size_t kDynSmem = kTileBytes * S * NIN + 1024;
+};
+
+template <typename ST, int E, int NT, int S, bool BWD, bool ASC>
+__global__ void __launch_bounds__(NT) linrec_async_kernel(const ScanParams p)
+{
+    using L = AsyncLayout<ST, E, NT, S, BWD>;
+    constexpr int T = L::T, NW = NT / 32, NIN = L::NIN;
+    constexpr int PC = Storage<ST>::kPerChunk;
+    constexpr uint32_t kOne = Storage<ST>::kOnePair;
+    extern __shared__ uint8_t dyn_smem[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~(uintptr_t)1023);
+    auto buf = [&](int s, int a) { return reinterpret_cast<ST*>(base + (size_t)(s * NIN + a) * L::kTileBytes); };
+
+    __shared__ uint32_t tile_of_stage[S];
+    __shared__ uint32_t halo[S][2];
+    __shared__ Pair wagg[NW];
+    __shared__ ChainShared chain_sh;
+
+    const Geometry g = make_geometry<E, NT, ASC>(p);
+    const int tid = g.t;
+    const uint32_t ntiles = (uint32_t)p.ntiles;
+    const uint32_t epoch = read_epoch(p.header);
+    const ST* gin0 = reinterpret_cast<const ST*>(p.in0);
+    const ST* gc = reinterpret_cast<const ST*>(p.c);
+    const ST* gy = reinterpret_cast<const ST*>(p.yin);
+    ST* gout0 = reinterpret_cast<ST*>(p.out0);
+    ST* gout1 = reinterpret_cast<ST*>(p.out1);
+    const int spr = p.chain ? T : p.slots_per_row;
+    const int cpr = spr / PC;
+    const bool with_halo = BWD && p.chain;
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
+
+    // The chunks a thread copies are the same in every tile: chunk ci = tid + k*NT of the tile.  Its
+    // place relative to the tile's first element is worked out once (there is an integer division in
+    // it); per tile only the base offset and one comparison remain.
+    constexpr int CPT = T / PC / NT;   // chunks per thread and array
+    long long rel[CPT];                // element offset from the tile's first element
+    int key[CPT];                      // chain: column inside the tile; else row inside the tile
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+        const int ci = tid + k * NT;
+        if (p.chain) {
+            key[k] = ci * PC;
+            rel[k] = (long long)ci * PC;
+        } else {
+            const int j = ci / cpr;
+            const int col = (ci - j * cpr) * PC;
+            key[k] = (j < p.rows_per_tile && col < p.seqlen) ? j : 0x7fffffff;
+            rel[k] = (long long)j * p.row_stride + col;
+        }
+    }
+    // tile -> (offset of its first element, bound that key[] has to stay under)
+    auto tile_base = [&](const TileCoord& tc, int& lim) -> long long {
+        const long long rows_left = p.numseq - tc.row;
+        lim = p.chain ? tc.valid : (int)(rows_left < (long long)p.rows_per_tile ? rows_left : (long long)p.rows_per_tile);
+        return tc.row * p.row_stride + (p.chain ? (long long)tc.piece * T : 0ll);
+    };
+    // every thread starts the copies of its chunks of ticket `tk` into ring slot `s`
+    auto issue = [&](int s, uint32_t tk) {
+        if (tk < ntiles) {
+            const TileCoord tc = decode_ticket<T, ASC>(p, tk);
+            int lim;
+            const long long tb = tile_base(tc, lim);
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const int ci = tid + k * NT;
+                const long long off = tb + rel[k];
+                const int phys = ci ^ ((ci >> 3) & 7);
+                uint4* d0 = reinterpret_cast<uint4*>(buf(s, 0)) + phys;
+                uint4* d1 = reinterpret_cast<uint4*>(buf(s, 1)) + phys;
+                if (key[k] < lim) {
+                    ptx::cp_async_16(d0, gin0 + off);
+                    ptx::cp_async_16(d1, gc + off);
+                    if (BWD) ptx::cp_async_16(reinterpret_cast<uint4*>(buf(s, 2)) + phys, gy + off);
+                } else {
+                    *d0 = make_uint4(0u, 0u, 0u, 0u);
+                    *d1 = make_uint4(kOne, kOne, kOne, kOne);
+                    if (BWD) reinterpret_cast<uint4*>(buf(s, 2))[phys] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (with_halo && tid < 2) {
+                const long long rb = tc.row * p.row_stride;
+                const long long lo = (long long)tc.piece * T - 1, hi = (long long)tc.piece * T + T;
+                // tid 0: coefficient at the scan predecessor of the piece; tid 1: output at its successor
+                const long long idx = tid == 0 ? (ASC ? lo : hi) : (ASC ? hi : lo);
+                const ST* src = (tid == 0 ? gc : gy) + rb + idx;
+                if (idx >= 0 && idx < p.seqlen)
+                    ptx::cp_async_4(&halo[s][tid], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)3));
+                else
+                    halo[s][tid] = (tid == 0 && p.open_start) ? kOne : 0u;
+            }
+        }
+        ptx::cp_async_commit();   // one group per call, empty or not: the wait below counts groups
+    };
+
+    // Tickets as in the bulk-copy kernel: the first S+1 of a CTA are fixed round-robin, later ones come
+    // from the counter.  "Lazy" mode (a handful of very long rows): one ticket at a time in ring slot 0,
+    // the next one drawn only when the tile has been scanned.
+    const uint32_t grid = gridDim.x;
+    const bool lazy = p.lazy != 0;
+    const uint32_t dyn_base = p.first_ticket + (lazy ? 1u : (uint32_t)(S + 1)) * grid;
+    uint32_t next_ticket = p.first_ticket + (uint32_t)S * grid + blockIdx.x;   // used by thread 0
+    if (tid == 0)
+        for (int s = 0; s < S; ++s)
+            tile_of_stage[s] = (lazy && s > 0) ? 0xffffffffu : p.first_ticket + (uint32_t)s * grid + blockIdx.x;
+    __syncthreads();
+    for (int s = 0; s < S; ++s) issue(s, tile_of_stage[s]);
+
+    uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // look-ahead copy of the predecessor's descriptor
+    for (uint32_t it = 0;; ++it) {
+        const int s = lazy ? 0 : (int)(it % S);
+        const uint32_t tk = tile_of_stage[s];
+        if (tk >= ntiles) break;
+        const uint32_t next_tk = lazy ? 0xffffffffu : tile_of_stage[(it + 1) % S];
+        const TileCoord tc = decode_ticket<T, ASC>(p, tk);
+        // this thread's copies of the tile have landed (the S-1 younger groups may still be in flight)
+        if (lazy) ptx::cp_async_wait_group<0>();
+        else ptx::cp_async_wait_group<S - 1>();
+        __syncthreads();                     // ... and everybody else's
+
+        float pred_c = p.open_start ? 1.0f : 0.0f, succ_y = 0.0f;
+        if (with_halo) {
+            pred_c = Storage<ST>::half_of_word(halo[s][0], ASC);
+            succ_y = Storage<ST>::half_of_word(halo[s][1], !ASC);
+        }
+        const bool zero_first = !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
+        Operands<E, BWD> op;
+        load_operands<ST, E, NT, BWD, ASC, true>(op, g, buf(s, 0), buf(s, 1), BWD ? buf(s, 2) : buf(s, 1), pred_c, succ_y,
+                                                 tc.valid, zero_first);
+        if (!BWD && !p.open_start && !ASC && !p.chain) {
+            // padded rows scanned downwards: the row's first element in scan order is its last real
+            // element, which need not be the last slot of a thread's run
+            const int j = (int)p.seqlen - 1 - g.m * E;
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (e == j) op.c[e] = 0.0f;
+        }
+        if (!BWD && !p.open_start && !ASC && p.chain && tc.q == 0) {
+            const int j = tc.valid - 1 - g.t * E;
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (e == j) op.c[e] = 0.0f;
+        }
+        float o0[E], o1[BWD ? E : 1];
+        tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+            __syncthreads();
+            return true;
+        });
+        store_run<ST, E>(buf(s, 0), g.t, o0);
+        if constexpr (BWD) store_run<ST, E>(buf(s, 2), g.t, o1);
+        if (tid == 0) {
+            const uint32_t drawn = dyn_base + atomicAdd(p.header, 1u);
+            tile_of_stage[s] = lazy ? drawn : next_ticket;
+            next_ticket = drawn;
+        }
+        __syncthreads();
+        {
+            int lim;
+            const long long tb = tile_base(tc, lim);
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                if (key[k] < lim) {
+                    const int ci = tid + k * NT;
+                    const long long off = tb + rel[k];
+                    const int phys = ci ^ ((ci >> 3) & 7);
+                    *reinterpret_cast<uint4*>(gout0 + off) = reinterpret_cast<const uint4*>(buf(s, 0))[phys];
+                    if (BWD) *reinterpret_cast<uint4*>(gout1 + off) = reinterpret_cast<const uint4*>(buf(s, 2))[phys];
+                }
+            }
+        }
+        __syncthreads();   // the slot has been read out: refill it
+        issue(s, tile_of_stage[s]);
+    }
+    ptx::cp_async_wait_group<0>();
+    if (tid == 0) finish_launch(p.header, epoch);
+}
+
+// =================================================================================================
 //  Sequential operator: one thread per row
 // =================================================================================================
 template <typename ST, bool BWD>

@@ -57,11 +57,6 @@ def test_golden(golden, name, rev, family):
     dev = torch.device("cuda:0")
     x, c, dy = (torch.from_numpy(golden[f"{name}/{k}"]).to(dev) for k in ("x", "c", "dy"))
     tag = f"{name}/rev{int(rev)}"
-    if family == "tile" and x.shape[-1] > 2048 and x.shape[-1] % 32 != 0:
-        # the tile family keeps a whole row in one tile; 2048 is the any-alignment kernels' tile
-        with pytest.raises(RuntimeError, match="does not fit one tile"):
-            lb._C.linrec_tile_fwd(inputs=x, coeffs=c, reverse=rev)
-        return
     y = getattr(lb._C, f"linrec_{family}_fwd")(inputs=x, coeffs=c, reverse=rev)
     np.testing.assert_allclose(y.cpu().numpy(), golden[f"{tag}/y"], rtol=RTOL, atol=ATOL)
     yg = torch.from_numpy(golden[f"{tag}/y"]).to(dev)
@@ -147,6 +142,70 @@ def test_bf16_storage(shape, rev, dtype):
     y_seq = lb._C.linrec_ref_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
     np.testing.assert_allclose(y_seq.float().cpu().numpy(), y_ref, rtol=BF16_RTOL, atol=ATOL)
     lb.check_status()
+
+
+def test_tile_family_refuses_rows_longer_than_a_tile():
+    """The tile family keeps a whole row in one tile: 8192 elements when rows can be copied in
+    16-byte chunks, 2048 for the plain-load kernel."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    for L, fits in [(2049, False), (2100, True), (8192 + 4, False), (8192 - 4, True)]:
+        x, c, _ = _data((2, L))
+        if fits:
+            y = lb._C.linrec_tile_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=False)
+            np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(x.numpy(), c.numpy()), rtol=RTOL, atol=ATOL)
+        else:
+            with pytest.raises(RuntimeError, match="does not fit one tile"):
+                lb._C.linrec_tile_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=False)
+
+
+# ---- rows of whole 16-byte chunks that are not whole 128-byte lines: the cp.async kernel --------------
+@pytest.mark.parametrize("shape", [(7, 100), (300, 36), (33, 1000), (5, 2100), (3, 10000), (2, 50004), (1, 4)],
+                         ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_async_copy_kernel(shape, rev):
+    lb = _ops()
+    x, c, dy = _data(shape, clo=0.5, chi=1.0)
+    attrs = lb._C.linrec_pipe_attrs(fwd=True, memcode=2)
+    assert attrs["memcode"] == 2 and attrs["kStages"] == 2
+    for kw in ({}, {"memcode": 2}, {"memcode": 2, "kThreadsPerBlock": 128}, {"memcode": 2, "kThreadsPerBlock": 512},
+               {"memcode": 0}):
+        _check_fwd_bwd(x, c, dy, rev, **kw)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(9, 200), (4, 4104), (2, 20008)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_async_copy_kernel_two_byte(dtype, shape):
+    """2-byte storage through the cp.async kernel against the plain-load kernel (same tile algebra,
+    same tile size: bit for bit where a row is one tile) and against the oracle."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.5, chi=1.0)
+    xd, cd, dyd = x.to(dev, dtype), c.to(dev, dtype), dy.to(dev, dtype)
+    for rev in (False, True):
+        ya = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=rev, memcode=2, kThreadsPerBlock=128)
+        yg = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=rev, memcode=0, kElemsPerThread=16)
+        da = lb._C.linrec_pipe_bwd(d_outputs=dyd, coeffs=cd, outputs=yg, reverse=rev, memcode=2, kThreadsPerBlock=128)
+        dg = lb._C.linrec_pipe_bwd(d_outputs=dyd, coeffs=cd, outputs=yg, reverse=rev, memcode=0, kElemsPerThread=16)
+        if shape[1] <= 2048:
+            # one tile per row: no look-back, whose order of combination depends on timing
+            assert torch.equal(ya, yg)
+            assert torch.equal(da[0], dg[0]) and torch.equal(da[1], dg[1])
+        else:
+            for a, b in ((ya, yg), (da[0], dg[0]), (da[1], dg[1])):
+                np.testing.assert_allclose(a.float().cpu().numpy(), b.float().cpu().numpy(), rtol=2e-2, atol=2e-2)
+        yd = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=rev)
+        ref = oracle.fwd_f32(xd.float().cpu().numpy(), cd.float().cpu().numpy(), reverse=rev)
+        np.testing.assert_allclose(yd.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2)
+    lb.check_status()
+
+
+def test_async_copy_kernel_refuses_unaligned_rows():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, _ = _data((4, 1001))
+    with pytest.raises(RuntimeError):
+        lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=False, memcode=2)
 
 
 # ---- every compiled variant ------------------------------------------------------------------------
@@ -302,6 +361,13 @@ def test_handful_of_very_long_rows(rev):
     _check_fwd_bwd(x, c, dy, rev)
     _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=128, kStages=1, lazyTickets=1)
     _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=256, kStages=1, lazyTickets=0)
+    # the same regime for rows that are not whole 128-byte lines (cp.async kernel)
+    x, c, dy = _data((3, 40 * 8192 + 4100), clo=0.9)
+    _check_fwd_bwd(x, c, dy, rev)
+    _check_fwd_bwd(x, c, dy, rev, memcode=2, kThreadsPerBlock=128, kStages=2, lazyTickets=1)
+    _check_fwd_bwd(x, c, dy, rev, memcode=2, kThreadsPerBlock=512, lazyTickets=0)
+    x, c, dy = _data((150, 3 * 8192 + 8), clo=0.9)   # few rows: the 4096-element tile
+    _check_fwd_bwd(x, c, dy, rev)
 
 
 def test_cuda_graph_capture_and_replay():
