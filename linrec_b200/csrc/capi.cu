@@ -440,7 +440,8 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
         const bool pinned = !(opt.E < 0 && opt.NT < 0 && opt.S < 0);
         int E = opt.E, NT = opt.NT, S = opt.S;
         if (!pinned && kind != LINREC_KIND_TILE) {
-            // Many rows: the small tile and many resident CTAs.  Few long rows: consecutive tickets are
+            // Many rows: the small tile and many resident CTAs (4-byte rows that fit it: the 4096-element
+            // tile, three CTAs per SM, measured faster than six small ones).  Few long rows: consecutive tickets are
             // pieces of the same row and wait for each other, so larger tiles; a handful of very long
             // rows: the largest tile, one ticket at a time.
             const bool few_rows = seqlen > 2048 && numseq < 4LL * sm_count;
@@ -449,6 +450,7 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             S = 2;
             if (handful)       { E = 16; NT = 512; }
             else if (few_rows) { E = 32; NT = 128; }
+            else if (di == 0 && seqlen <= 4096) { E = 16; NT = 256; }   // 4-byte rows that fit the 4096-element tile
             else               { E = 16; NT = 128; }
         }
         for (const GenericVariant& v : async_variants()) {

@@ -493,10 +493,16 @@ struct AsyncLayout {
     static constexpr int NIN = BWD ? 3 : 2;
     static constexpr size_t kTileBytes = (size_t)T * sizeof(ST);
     static constexpr size_t kDynSmem = kTileBytes * S * NIN + 1024;
+    // CTAs per SM the kernel is compiled for: what shared memory allows, up to a thread count that
+    // leaves the register allocator what the pass needs
+    static constexpr int kFitSmem = (int)((size_t)232448 / (kDynSmem + 1024 + 512));
+    static constexpr int kMaxThreads = E >= 32 ? 384 : (BWD ? (sizeof(ST) == 2 ? 640 : 512) : 768);
+    static constexpr int kByThreads = kMaxThreads / NT < 1 ? 1 : kMaxThreads / NT;
+    static constexpr int kMinBlocks = kFitSmem < 1 ? 1 : (kFitSmem < kByThreads ? kFitSmem : kByThreads);
 };
 
 template <typename ST, int E, int NT, int S, bool BWD, bool ASC>
-__global__ void __launch_bounds__(NT) linrec_async_kernel(const ScanParams p)
+__global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlocks)) linrec_async_kernel(const ScanParams p)
 {
     using L = AsyncLayout<ST, E, NT, S, BWD>;
     constexpr int T = L::T, NW = NT / 32, NIN = L::NIN;
@@ -644,9 +650,12 @@ __global__ void __launch_bounds__(NT) linrec_async_kernel(const ScanParams p)
         store_run<ST, E>(buf(s, 0), g.t, o0);
         if constexpr (BWD) store_run<ST, E>(buf(s, 2), g.t, o1);
         if (tid == 0) {
-            const uint32_t drawn = dyn_base + atomicAdd(p.header, 1u);
-            tile_of_stage[s] = lazy ? drawn : next_ticket;
-            next_ticket = drawn;
+            if (lazy) {
+                tile_of_stage[s] = dyn_base + atomicAdd(p.header, 1u);
+            } else {   // the ticket drawn one tile ago; nobody waits for the counter's answer
+                tile_of_stage[s] = next_ticket;
+                next_ticket = dyn_base + atomicAdd(p.header, 1u);
+            }
         }
         __syncthreads();
         {
