@@ -4,6 +4,8 @@
 //                          in by tiled bulk-tensor copies (TMA, 128-byte swizzle) through an
 //                          S-stage shared-memory ring with mbarriers, results staged in shared
 //                          memory and written back with bulk-tensor stores.
+//   linrec_async_kernel    same tile algebra for 16-byte aligned rows of whole 16-byte chunks that are
+//                          not whole 128-byte lines: 16-byte cp.async into a ring of shared tiles.
 //   linrec_generic_kernel  same tile algebra, but plain coalesced loads and stores with bounds
 //                          checks: any length, any (element-aligned) pointer, any row stride.
 //   linrec_seq_kernel      one thread walks one row (the slow, obviously-right operator that the
