@@ -203,8 +203,37 @@ LINREC_API int linrec_b200_fwd_static(const void* x, const void* c, void* y,
                                       int64_t numseq, int64_t seqlen, int64_t row_stride,
                                       int reverse, int dtype, void* stream);
 
+/* ---- scan along a dimension other than the last ------------------------------------------------------
+ * The `dim` argument of the reference's Python operator (linrec/impl/python/ops.py:8-14,43-61); the
+ * reference's CUDA operators scan the last dimension only (linrec/impl/cuda/linrec_pipe.cu:17-35), so
+ * its callers transpose in and out.  Here the tensor is taken as contiguous (nb, seqlen, nchan) and
+ * the recurrence runs along the MIDDLE axis in place of those copies: element (b, l, d) follows
+ * (b, l-1, d).  Arguments and error codes as linrec_b200_fwd / linrec_b200_bwd; all tensors have the
+ * same (nb, seqlen, nchan) shape and are dense.  Requirements: 16-byte aligned pointers and
+ * nchan * element size a multiple of 16 bytes (else LINREC_ERR_UNALIGNED: transpose and use the
+ * last-axis operators).  The workspace must be zeroed once by its owner, like the other workspaces
+ * (they are interchangeable), and hold linrec_b200_dim_workspace_size(...) bytes for the same
+ * arguments and options; that size query returns 0 for options no compiled variant matches.
+ * Options: kThreadsPerBlock, kRowsPerChunk, kStages pin a variant; kChunksPerJob (0 = a whole column
+ * per job) sets how finely a column is cut into jobs that are linked by look-back carries. */
+LINREC_API size_t linrec_b200_dim_workspace_size(int bwd, int64_t nb, int64_t seqlen, int64_t nchan,
+                                                 int dtype, const linrec_opts* opts);
+LINREC_API int linrec_b200_fwd_dim(const void* x, const void* c, void* y,
+                                   int64_t nb, int64_t seqlen, int64_t nchan, int reverse, int dtype,
+                                   const linrec_opts* opts, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+LINREC_API int linrec_b200_bwd_dim(const void* dy, const void* c, const void* y, void* dx, void* dc,
+                                   int64_t nb, int64_t seqlen, int64_t nchan, int reverse, int dtype,
+                                   const linrec_opts* opts, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+
 /* Number of kernels this library has launched in this process (all threads). */
 LINREC_API uint64_t linrec_b200_launch_count(void);
+
+/* What LINREC_ERR_CUDA stood for in the last call of the calling thread that returned it: the name of
+ * the failing CUDA call and the runtime's error text ("" if there was none).  The reference reports
+ * such failures through C10_CUDA_KERNEL_LAUNCH_CHECK (linrec/impl/cuda/linrec_pipe.cu:88). */
+LINREC_API const char* linrec_b200_last_cuda_error(void);
 
 /* Text for a status code. */
 LINREC_API const char* linrec_b200_strerror(int code);

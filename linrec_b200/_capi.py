@@ -79,8 +79,16 @@ def _load() -> ctypes.CDLL:
     lib.linrec_b200_bwd_seq_p2p.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp, ctypes.c_uint32, po,
                                             vp, sz, vp]
     lib.linrec_b200_bwd_seq_p2p.restype = i32
+    lib.linrec_b200_dim_workspace_size.argtypes = [i32, i64, i64, i64, i32, po]
+    lib.linrec_b200_dim_workspace_size.restype = sz
+    lib.linrec_b200_fwd_dim.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, po, vp, sz, vp]
+    lib.linrec_b200_fwd_dim.restype = i32
+    lib.linrec_b200_bwd_dim.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, po, vp, sz, vp]
+    lib.linrec_b200_bwd_dim.restype = i32
     lib.linrec_b200_launch_count.argtypes = []
     lib.linrec_b200_launch_count.restype = ctypes.c_uint64
+    lib.linrec_b200_last_cuda_error.argtypes = []
+    lib.linrec_b200_last_cuda_error.restype = ctypes.c_char_p
     lib.linrec_b200_strerror.argtypes = [i32]
     lib.linrec_b200_strerror.restype = ctypes.c_char_p
     lib.linrec_b200_version.argtypes = []
@@ -113,6 +121,8 @@ def raise_for(code: int, what: str) -> None:
     if code == OK:
         return
     msg = f"{what}: {strerror(code)} (status {code})"
+    if code == ERR_CUDA:
+        msg += f" [{lib.linrec_b200_last_cuda_error().decode()}]"
     if code == ERR_NOT_IMPLEMENTED:
         raise NotImplementedError(msg)
     raise RuntimeError(msg)

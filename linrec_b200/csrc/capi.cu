@@ -18,6 +18,7 @@
 #include "../../include/linrec_b200.h"
 #include "scan_kernels.cuh"
 #include "shard_kernels.cuh"
+#include "column_kernels.cuh"
 
 namespace {
 
@@ -25,6 +26,21 @@ using linrec::ScanParams;
 using linrec::TileDesc;
 
 std::atomic<uint64_t> g_launches{0};
+
+// Text of the last CUDA error a call of this thread ran into (what LINREC_ERR_CUDA stands for).
+thread_local char g_last_cuda_error[192] = "";
+void note_cuda_error(const char* where, const char* what)
+{
+    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, what ? what : "unknown error");
+}
+// Result of a kernel launch: reads (and clears) the runtime's last error.
+int launch_result(const char* where)
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return LINREC_OK;
+    note_cuda_error(where, cudaGetErrorString(e));
+    return LINREC_ERR_CUDA;
+}
 
 // ---- options -------------------------------------------------------------------------------------
 // Compile-time configuration names (the counterpart of CONFIG_NAMES, linrec/impl/cuda/linrec.h:8).
@@ -42,6 +58,8 @@ struct Options {
     int lazy = -1;               // -1 = selector decides, 0/1 = one-ticket-at-a-time mode off/on (one ring slot only)
     int l2_promotion = 3;        // tensor-map L2 promotion: 0 none, 1 64 B, 2 128 B, 3 256 B
     int p2p_phase = 0;           // peer-exchange calls: 0 = scan and fix-up, 1 = scan only, 2 = fix-up only
+    int LC = -1;                 // scan along the middle axis: sequence positions per chunk
+    int K = -1;                  // scan along the middle axis: chunks per job (0 = whole column)
 };
 
 int parse_options(const linrec_opts* o, Options& out)
@@ -56,6 +74,8 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "kThreadsPerBlock")) out.NT = v;
         else if (!strcmp(n, "kStages")) out.S = v;
         else if (!strcmp(n, "kOutBuffers")) out.OB = v;
+        else if (!strcmp(n, "kRowsPerChunk")) out.LC = v;
+        else if (!strcmp(n, "kChunksPerJob")) out.K = v;
         else if (!strcmp(n, "memcode")) out.memcode = v;
         else if (!strcmp(n, "waitBudgetMs")) out.wait_budget_ms = v;
         else if (!strcmp(n, "ctasPerSm")) out.ctas_per_sm = v;
@@ -224,6 +244,18 @@ int device_info(DeviceInfo& out)
 {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
+    // Tensor maps are encoded through a driver entry point, which needs the device's primary context
+    // to be current in the calling thread.  The runtime binds it lazily, and a thread that has only
+    // made calls that do not need one (an autograd worker with warm caches) has none yet.
+    thread_local int bound_device = -1;
+    if (bound_device != dev) {
+        if (cudaFree(nullptr) != cudaSuccess) {
+            note_cuda_error("cudaFree(0)", "could not initialise the device context in this thread");
+            cudaGetLastError();
+            return LINREC_ERR_CUDA;
+        }
+        bound_device = dev;
+    }
     std::lock_guard<std::mutex> lock(g_mutex);
     auto it = g_devices.find(dev);
     if (it == g_devices.end()) {
@@ -248,16 +280,21 @@ int occupancy(const void* fn, int threads, size_t smem, int& out)
     auto it = g_occupancy.find(key);
     if (it == g_occupancy.end()) {
         if (smem > 48 * 1024) {
-            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) {
                 cudaGetLastError();
+                note_cuda_error("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", cudaGetErrorString(e));
                 return LINREC_ERR_CUDA;
             }
         }
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem) != cudaSuccess) {
+        const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem);
+        if (e != cudaSuccess) {
             cudaGetLastError();
+            note_cuda_error("cudaOccupancyMaxActiveBlocksPerMultiprocessor", cudaGetErrorString(e));
             return LINREC_ERR_CUDA;
         }
+        if (n <= 0) note_cuda_error("occupancy", "the kernel does not fit an SM with this much shared memory");
         it = g_occupancy.emplace(key, n).first;
     }
     out = it->second;
@@ -289,7 +326,10 @@ int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64
              int64_t row_stride, int box_lines, int box_rows, int l2_promotion)
 {
     EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return LINREC_ERR_CUDA;
+    if (!enc) {
+        note_cuda_error("cudaGetDriverEntryPoint", "cuTensorMapEncodeTiled not found");
+        return LINREC_ERR_CUDA;
+    }
     const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
     const cuuint64_t epl = 128 / sz;
     const cuuint64_t dims[3] = {epl, (cuuint64_t)(seqlen / (int64_t)epl), (cuuint64_t)numseq};
@@ -304,7 +344,13 @@ int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64
                            : l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
                            : l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LINREC_OK : LINREC_ERR_CUDA;
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof(msg), "driver error %d", (int)r);
+        note_cuda_error("cuTensorMapEncodeTiled", msg);
+        return LINREC_ERR_CUDA;
+    }
+    return LINREC_OK;
 }
 
 // ---- planning ------------------------------------------------------------------------------------
@@ -554,7 +600,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
             else     linrec::linrec_seq_kernel<__half, false><<<blocks, threads, 0, stream>>>(p, reverse);
         }
         g_launches.fetch_add(1, std::memory_order_relaxed);
-        return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+        return launch_result("kernel launch");
     }
 
     Plan pl;
@@ -600,7 +646,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
         pl.gv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(p);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+    return launch_result("kernel launch");
 }
 
 }  // namespace
@@ -630,7 +676,7 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
     }
 #undef LINREC_FIXUP
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+    return launch_result("kernel launch");
 }
 
 int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
@@ -663,6 +709,227 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     return dtype == LINREC_DTYPE_F32 ? launch_fixup_t<float>(bwd, asc, fp, stream, dev.sm_count)
            : dtype == LINREC_DTYPE_BF16 ? launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count)
                                         : launch_fixup_t<__half>(bwd, asc, fp, stream, dev.sm_count);
+}
+}  // namespace
+
+
+// ---- scan along the middle axis of (nb, seqlen, nchan) -------------------------------------------------
+namespace {
+using ColFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                       const CUtensorMap, const linrec::ColParams);
+struct ColVariant {
+    int NT, LC, S;
+    size_t smem[3][2];     // [dtype][bwd]
+    ColFn fn[3][2][2];     // [dtype][bwd][asc]; null where the variant does not exist for the type
+};
+
+template <typename ST, int NT, int LC, int S>
+void fill_col_variant(ColVariant& v, int di)
+{
+    using namespace linrec;
+    if constexpr (NT * (4 / (int)sizeof(ST)) <= 256) {
+        v.smem[di][0] = ColLayout<ST, NT, LC, S, false>::kDynSmem;
+        v.smem[di][1] = ColLayout<ST, NT, LC, S, true>::kDynSmem;
+        v.fn[di][0][0] = linrec_column_kernel<ST, NT, LC, S, false, false>;
+        v.fn[di][0][1] = linrec_column_kernel<ST, NT, LC, S, false, true>;
+        v.fn[di][1][0] = linrec_column_kernel<ST, NT, LC, S, true, false>;
+        v.fn[di][1][1] = linrec_column_kernel<ST, NT, LC, S, true, true>;
+    }
+}
+
+template <int NT, int LC, int S>
+ColVariant make_col_variant()
+{
+    ColVariant v{};
+    v.NT = NT; v.LC = LC; v.S = S;
+    fill_col_variant<float, NT, LC, S>(v, 0);
+    fill_col_variant<__nv_bfloat16, NT, LC, S>(v, 1);
+    fill_col_variant<__half, NT, LC, S>(v, 2);
+    return v;
+}
+
+const std::vector<ColVariant>& col_variants()
+{
+    static const std::vector<ColVariant> v = {
+        make_col_variant<128, 32, 3>(),
+        make_col_variant<128, 32, 2>(),
+        make_col_variant<128, 32, 4>(),
+        make_col_variant<64, 64, 3>(),
+        make_col_variant<64, 64, 2>(),
+        make_col_variant<32, 128, 3>(),
+        make_col_variant<32, 128, 2>(),
+        make_col_variant<32, 64, 4>(),
+        make_col_variant<256, 32, 2>(),
+    };
+    return v;
+}
+
+struct ColPlan {
+    const ColVariant* v = nullptr;
+    int DC = 0, dtiles = 0, nq = 0, k = 0, gens = 0;
+    long long units = 0, njobs = 0;
+};
+
+// Resident CTA slots the job count is sized for (148 SMs x 2 CTAs): fixed, so that the workspace a
+// problem needs does not depend on the device the size query runs on.
+constexpr long long kColSlots = 296;
+
+int make_col_plan(ColPlan& pl, bool bwd, int dtype, int64_t nb, int64_t seqlen, int64_t nchan, const Options& opt,
+                  int max_smem)
+{
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
+    const int per_word = di == 0 ? 1 : 2;
+    int NT = opt.NT, LC = opt.LC, S = opt.S;
+    if (NT < 0 && LC < 0 && S < 0) {
+        // Defaults: tiles of 4096 channel words; three stages forward (two operands per stage), two
+        // backward (three operands): two CTAs per SM either way.  The tile is as wide as it can be
+        // while there are still enough columns to give every resident CTA one of its own; with
+        // fewer columns it is narrow and tall, so that a column has fewer chunks in flight.
+        NT = 32;
+        for (int nt = 128; nt >= 32; nt >>= 1) {
+            if (4 * nb * ceil_div(nchan, (int64_t)nt * per_word) >= 3 * kColSlots) {
+                NT = nt;
+                break;
+            }
+        }
+        LC = 4096 / NT;
+        S = bwd ? 2 : 3;
+    }
+    for (const ColVariant& v : col_variants()) {
+        if (!((NT < 0 || v.NT == NT) && (LC < 0 || v.LC == LC) && (S < 0 || v.S == S))) continue;
+        if (!v.fn[di][bwd][0] || v.smem[di][bwd] > (size_t)max_smem) continue;
+        pl.v = &v;
+        break;
+    }
+    if (!pl.v) return LINREC_ERR_NOT_IMPLEMENTED;
+    pl.DC = pl.v->NT * per_word;
+    pl.dtiles = (int)ceil_div(nchan, pl.DC);
+    pl.units = nb * pl.dtiles;
+    pl.nq = (int)ceil_div(seqlen, pl.v->LC);
+    int k = opt.K;
+    if (k < 0) {
+        if (4 * pl.units >= 3 * kColSlots) {
+            // Enough columns to keep the resident CTAs busy with one job per column at a time: jobs of
+            // several chunks that wait for their predecessor's inclusive value, about 32 jobs per
+            // resident CTA so that the last round is short.
+            long long gens = (32 * kColSlots + pl.units - 1) / pl.units;
+            if (gens < 1) gens = 1;
+            if (gens > pl.nq) gens = pl.nq;
+            k = (int)ceil_div(pl.nq, gens);
+        } else {
+            k = 1;   // few columns: every chunk is a job, linked by decoupled look-back
+        }
+    }
+    if (k == 0 || k > pl.nq) k = pl.nq;
+    pl.k = k;
+    pl.gens = (int)ceil_div(pl.nq, k);
+    pl.njobs = pl.units * pl.gens;
+    if (pl.njobs >= 0x7ff00000LL) return LINREC_ERR_INVALID_ARG;   // tickets are 32-bit
+    return LINREC_OK;
+}
+
+size_t col_workspace_need(const ColPlan& pl)
+{
+    size_t n = linrec::kHeaderBytes;
+    if (pl.gens > 1) n += (size_t)pl.njobs * (size_t)pl.DC * sizeof(TileDesc);
+    return n;
+}
+
+bool col_eligible(int dtype, int64_t nb, int64_t seqlen, int64_t nchan, const void* const* ptrs, int nptrs)
+{
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    if ((nchan * sz) % 16 != 0) return false;
+    if (nb > 0x7fffffffLL || seqlen > 0x7fffffffLL - 1024 || nchan > 0x7fffffffLL) return false;
+    if ((uint64_t)nchan * sz >= (1ull << 40) || (uint64_t)nchan * (uint64_t)seqlen * sz >= (1ull << 40)) return false;
+    for (int i = 0; i < nptrs; ++i)
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
+    return true;
+}
+
+// Rank-3 view (channels, positions, batch) of a contiguous (nb, seqlen, nchan) tensor, no swizzle;
+// box = (DC channels, LC positions, 1).  Out-of-range elements read as zero and are not written.
+int make_col_map(CUtensorMap* map, const void* ptr, int dtype, int64_t nb, int64_t seqlen, int64_t nchan, int box_chan,
+                 int box_rows, int l2_promotion)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        note_cuda_error("cudaGetDriverEntryPoint", "cuTensorMapEncodeTiled not found");
+        return LINREC_ERR_CUDA;
+    }
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    const cuuint64_t dims[3] = {(cuuint64_t)nchan, (cuuint64_t)seqlen, (cuuint64_t)nb};
+    const cuuint64_t strides[2] = {(cuuint64_t)nchan * sz, (cuuint64_t)nchan * (cuuint64_t)seqlen * sz};
+    const cuuint32_t box[3] = {(cuuint32_t)box_chan, (cuuint32_t)box_rows, 1u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(map, dtype == LINREC_DTYPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == LINREC_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE,
+                           l2_promotion == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                           : l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                           : l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof(msg), "driver error %d", (int)r);
+        note_cuda_error("cuTensorMapEncodeTiled", msg);
+        return LINREC_ERR_CUDA;
+    }
+    return LINREC_OK;
+}
+
+int launch_col(bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1, int64_t nb,
+               int64_t seqlen, int64_t nchan, int reverse, int dtype, const linrec_opts* opts, void* workspace,
+               size_t workspace_bytes, void* stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16 && dtype != LINREC_DTYPE_F16) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (nb < 0 || seqlen < 0 || nchan < 0) return LINREC_ERR_INVALID_ARG;
+    Options opt;
+    int rc = parse_options(opts, opt);
+    if (rc != LINREC_OK) return rc;
+    if (nb == 0 || seqlen == 0 || nchan == 0) return LINREC_OK;
+    const void* ptrs[5] = {in0, c, out0, bwd ? yin : in0, bwd ? out1 : out0};
+    for (int i = 0; i < 5; ++i)
+        if (!ptrs[i]) return LINREC_ERR_INVALID_ARG;
+    if (!col_eligible(dtype, nb, seqlen, nchan, ptrs, 5)) return LINREC_ERR_UNALIGNED;
+    DeviceInfo dev;
+    rc = device_info(dev);
+    if (rc != LINREC_OK) return rc;
+    ColPlan pl;
+    rc = make_col_plan(pl, bwd, dtype, nb, seqlen, nchan, opt, dev.max_smem_optin);
+    if (rc != LINREC_OK) return rc;
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < col_workspace_need(pl))
+        return LINREC_ERR_WORKSPACE;
+
+    const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
+    const bool asc = bwd ? (reverse != 0) : (reverse == 0);
+    linrec::ColParams p{};
+    p.nb = nb; p.seqlen = seqlen; p.nchan = nchan;
+    p.dtiles = pl.dtiles; p.units = pl.units; p.nq = pl.nq; p.k_chunks = pl.k; p.gens = pl.gens; p.njobs = pl.njobs;
+    p.header = static_cast<uint32_t*>(workspace);
+    p.desc = reinterpret_cast<TileDesc*>(static_cast<char*>(workspace) + linrec::kHeaderBytes);
+    p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
+    p.first_ticket = (uint32_t)opt.first_ticket;
+
+    const ColFn fn = pl.v->fn[di][bwd][asc];
+    const size_t smem = pl.v->smem[di][bwd];
+    int occ = 0;
+    rc = occupancy(reinterpret_cast<const void*>(fn), pl.v->NT + 32, smem, occ);
+    if (rc != LINREC_OK) return rc;
+    if (opt.ctas_per_sm > 0 && opt.ctas_per_sm < occ) occ = opt.ctas_per_sm;
+    long long grid = (long long)dev.sm_count * occ;
+    if (grid > pl.njobs) grid = pl.njobs;
+
+    CUtensorMap m[5];
+    const void* src[5] = {in0, c, bwd ? yin : c, out0, bwd ? out1 : out0};
+    for (int i = 0; i < 5; ++i) {
+        rc = make_col_map(&m[i], src[i], dtype, nb, seqlen, nchan, pl.DC, pl.v->LC, opt.l2_promotion);
+        if (rc != LINREC_OK) return rc;
+    }
+    fn<<<(unsigned)grid, pl.v->NT + 32, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return launch_result("kernel launch");
 }
 }  // namespace
 
@@ -862,7 +1129,7 @@ int linrec_b200_exchange_init(void* local_buf, void* const* peer_bufs, int rank,
     }
     linrec::linrec_exchange_init_kernel<<<1, 32, 0, stream>>>(static_cast<linrec::PeerTable*>(local_buf), a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError() == cudaSuccess ? LINREC_OK : LINREC_ERR_CUDA;
+    return launch_result("kernel launch");
 }
 
 int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen, int64_t row_stride,
@@ -962,6 +1229,35 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
 
 uint64_t linrec_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+/* ---- scan along the middle axis of a contiguous (nb, seqlen, nchan) tensor ------------------------------ */
+size_t linrec_b200_dim_workspace_size(int bwd, int64_t nb, int64_t seqlen, int64_t nchan, int dtype,
+                                      const linrec_opts* opts)
+{
+    Options opt;
+    if (parse_options(opts, opt) != LINREC_OK) return 0;
+    if (nb <= 0 || seqlen <= 0 || nchan <= 0) return (size_t)linrec::kHeaderBytes;
+    ColPlan pl;
+    if (make_col_plan(pl, bwd != 0, dtype, nb, seqlen, nchan, opt, 232448) != LINREC_OK) return 0;
+    return (size_t)round_up((int64_t)col_workspace_need(pl), 256);
+}
+
+int linrec_b200_fwd_dim(const void* x, const void* c, void* y, int64_t nb, int64_t seqlen, int64_t nchan, int reverse,
+                        int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return launch_col(false, x, c, nullptr, y, nullptr, nb, seqlen, nchan, reverse, dtype, opts, workspace,
+                      workspace_bytes, stream);
+}
+
+int linrec_b200_bwd_dim(const void* dy, const void* c, const void* y, void* dx, void* dc, int64_t nb, int64_t seqlen,
+                        int64_t nchan, int reverse, int dtype, const linrec_opts* opts, void* workspace,
+                        size_t workspace_bytes, void* stream)
+{
+    return launch_col(true, dy, c, y, dx, dc, nb, seqlen, nchan, reverse, dtype, opts, workspace, workspace_bytes,
+                      stream);
+}
+
+const char* linrec_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
 const char* linrec_b200_strerror(int code)
 {
     switch (code) {
@@ -972,7 +1268,7 @@ const char* linrec_b200_strerror(int code)
         case LINREC_ERR_CUDA: return "a CUDA call failed";
         case LINREC_ERR_TIMEOUT: return "a bounded device-side wait gave up";
         case LINREC_ERR_TOO_LONG: return "row does not fit one tile";
-        case LINREC_ERR_UNALIGNED: return "bulk-copy path needs 16-byte aligned rows whose length is a multiple of 128 bytes";
+        case LINREC_ERR_UNALIGNED: return "this copy path needs 16-byte aligned rows (bulk copies along the last axis: whole 128-byte lines)";
         case LINREC_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the 1 MiB built into the library (use linrec_b200_fwd with a workspace)";
         default: return "unknown status";
     }

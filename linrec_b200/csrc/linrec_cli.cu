@@ -100,6 +100,7 @@ __global__ void flush_kernel(float* p, size_t n)
 
 struct Args {
     long long numseq = 512, seqlen = 65536, stride = 0;
+    long long chan = 0;   // > 0: tensor (numseq, seqlen, chan), scan along the middle axis
     int reverse = 0, bwd = 0, dtype = LINREC_DTYPE_F32, iters = 20, warmup = 3, flush = 0, sweep = 0, verify = 1;
     int kind = LINREC_KIND_PIPE;
     float clo = 0.0f, chi = 1.0f;
@@ -110,7 +111,7 @@ struct Args {
 static void usage()
 {
     fprintf(stderr,
-            "usage: linrec_cli [--numseq N] [--seqlen L] [--stride S] [--reverse] [--bwd] [--dtype f32|bf16|f16]\n"
+            "usage: linrec_cli [--numseq N] [--seqlen L] [--stride S | --chan D] [--reverse] [--bwd] [--dtype f32|bf16|f16]\n"
             "                  [--clo a --chi b] [--iters K --warmup W] [--flush] [--opt name=value ...]\n"
             "                  [--sweep] [--no-verify] [--kind pipe|tile|ref]\n");
 }
@@ -133,12 +134,22 @@ static Result run_one(const Args& a, const std::vector<std::string>& names, cons
     const linrec_opts* po = names.empty() ? nullptr : &o;
     cudaStream_t st = 0;
     auto call = [&]() -> int {
+        if (a.chan > 0) {
+            if (!a.bwd)
+                return linrec_b200_fwd_dim(in0, c, out0, a.numseq, a.seqlen, a.chan, a.reverse, a.dtype, po, ws, ws_bytes, st);
+            return linrec_b200_bwd_dim(in0, c, yfw, out0, out1, a.numseq, a.seqlen, a.chan, a.reverse, a.dtype, po, ws,
+                                       ws_bytes, st);
+        }
         if (!a.bwd)
             return linrec_b200_fwd(a.kind, in0, c, out0, a.numseq, a.seqlen, a.stride, a.reverse, a.dtype, po, ws, ws_bytes, st);
         return linrec_b200_bwd(a.kind, in0, c, yfw, out0, out1, a.numseq, a.seqlen, a.stride, a.reverse, a.dtype, po, ws,
                                ws_bytes, st);
     };
-    const size_t total = (size_t)a.numseq * a.stride;
+    const size_t total = a.chan > 0 ? (size_t)a.numseq * a.seqlen * a.chan : (size_t)a.numseq * a.stride;
+    // element-wise comparison: with a channel axis the tensor is compared as rows of `chan` elements
+    const long long cmp_rows = a.chan > 0 ? a.numseq * a.seqlen : a.numseq;
+    const long long cmp_len = a.chan > 0 ? a.chan : a.seqlen;
+    const long long cmp_stride = a.chan > 0 ? a.chan : a.stride;
     CK(cudaMemset(out0, 0xff, total * sizeof(T)));
     if (a.bwd) CK(cudaMemset(out1, 0xff, total * sizeof(T)));
     r.rc = call();
@@ -151,7 +162,7 @@ static Result run_one(const Args& a, const std::vector<std::string>& names, cons
         unsigned long long hb;
         CK(cudaMemset(d_max, 0, sizeof(float)));
         CK(cudaMemset(d_bad, 0, sizeof(unsigned long long)));
-        compare_kernel<T><<<1024, 256>>>(out0, ref0, a.numseq, a.seqlen, a.stride, rtol, atol, d_max, d_bad);
+        compare_kernel<T><<<1024, 256>>>(out0, ref0, cmp_rows, cmp_len, cmp_stride, rtol, atol, d_max, d_bad);
         CK(cudaMemcpy(&hm, d_max, sizeof(float), cudaMemcpyDeviceToHost));
         CK(cudaMemcpy(&hb, d_bad, sizeof(hb), cudaMemcpyDeviceToHost));
         r.max_err0 = hm;
@@ -159,7 +170,7 @@ static Result run_one(const Args& a, const std::vector<std::string>& names, cons
         if (a.bwd) {
             CK(cudaMemset(d_max, 0, sizeof(float)));
             CK(cudaMemset(d_bad, 0, sizeof(unsigned long long)));
-            compare_kernel<T><<<1024, 256>>>(out1, ref1, a.numseq, a.seqlen, a.stride, rtol, atol, d_max, d_bad);
+            compare_kernel<T><<<1024, 256>>>(out1, ref1, cmp_rows, cmp_len, cmp_stride, rtol, atol, d_max, d_bad);
             CK(cudaMemcpy(&hm, d_max, sizeof(float), cudaMemcpyDeviceToHost));
             CK(cudaMemcpy(&hb, d_bad, sizeof(hb), cudaMemcpyDeviceToHost));
             r.max_err1 = hm;
@@ -193,10 +204,39 @@ static Result run_one(const Args& a, const std::vector<std::string>& names, cons
     return r;
 }
 
+// Sequential walk down the middle axis of (nb, seqlen, nchan), one thread per (batch, channel): the
+// checker for the --chan mode (same arithmetic as the sequential operator of the library).
+template <typename T>
+__global__ void column_reference_kernel(const T* in0, const T* c, const T* yfw, T* out0, T* out1, long long nb,
+                                        long long L, long long D, int reverse, int bwd)
+{
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= nb * D) return;
+    const long long b = i / D, d = i - b * D;
+    const long long base = b * L * D + d;
+    const bool asc = bwd ? (reverse != 0) : (reverse == 0);
+    float v = 0.0f;
+    for (long long k = 0; k < L; ++k) {
+        const long long l = asc ? k : L - 1 - k;
+        const long long prev = asc ? l - 1 : l + 1, next = asc ? l + 1 : l - 1;
+        const long long at = base + l * D;
+        if (!bwd) {
+            v = k == 0 ? cast_from<T>(in0[at]) : fmaf(v, cast_from<T>(c[at]), cast_from<T>(in0[at]));
+            out0[at] = cast_to<T>(v);
+        } else {
+            const float cp = k == 0 ? 0.0f : cast_from<T>(c[base + prev * D]);
+            v = fmaf(v, cp, cast_from<T>(in0[at]));
+            const float yn = (next < 0 || next >= L) ? 0.0f : cast_from<T>(yfw[base + next * D]);
+            out0[at] = cast_to<T>(v);
+            out1[at] = cast_to<T>(v * yn);
+        }
+    }
+}
+
 template <typename T>
 static int run(const Args& a)
 {
-    const size_t total = (size_t)a.numseq * a.stride;
+    const size_t total = a.chan > 0 ? (size_t)a.numseq * a.seqlen * a.chan : (size_t)a.numseq * a.stride;
     T *in0, *c, *yfw = nullptr, *out0, *out1 = nullptr, *ref0, *ref1 = nullptr;
     CK(cudaMalloc(&in0, total * sizeof(T)));
     CK(cudaMalloc(&c, total * sizeof(T)));
@@ -207,7 +247,15 @@ static int run(const Args& a)
         CK(cudaMalloc(&out1, total * sizeof(T)));
         CK(cudaMalloc(&ref1, total * sizeof(T)));
     }
-    const size_t ws_bytes = linrec_b200_workspace_size(a.numseq, a.seqlen, a.dtype);
+    size_t ws_bytes = linrec_b200_workspace_size(a.numseq, a.chan > 0 ? a.seqlen * a.chan : a.seqlen, a.dtype);
+    if (a.chan > 0) {
+        std::vector<const char*> np;
+        for (auto& n : a.opt_names) np.push_back(n.c_str());
+        linrec_opts o{(int)np.size(), np.data(), a.opt_values.data()};
+        const size_t need = linrec_b200_dim_workspace_size(a.bwd, a.numseq, a.seqlen, a.chan, a.dtype, np.empty() ? nullptr : &o);
+        if (need == 0) { fprintf(stderr, "no compiled variant for these options\n"); return 5; }
+        if (need > ws_bytes) ws_bytes = need;
+    }
     void* ws;
     CK(cudaMalloc(&ws, ws_bytes));
     CK(cudaMemset(ws, 0, ws_bytes));   // once; launches leave the workspace ready for the next one
@@ -222,14 +270,22 @@ static int run(const Args& a)
     fill_kernel<T><<<2048, 256>>>(in0, total, 1, 0, 0, 1);
     fill_kernel<T><<<2048, 256>>>(c, total, 2, a.clo, a.chi, 0);
     CK(cudaDeviceSynchronize());
-    if (a.bwd) {
+    const unsigned col_blocks = a.chan > 0 ? (unsigned)((a.numseq * a.chan + 127) / 128) : 0u;
+    if (a.chan > 0) {
+        if (a.bwd) {
+            column_reference_kernel<T><<<col_blocks, 128>>>(in0, c, nullptr, yfw, nullptr, a.numseq, a.seqlen, a.chan, a.reverse, 0);
+            fill_kernel<T><<<2048, 256>>>(in0, total, 3, 0, 0, 1);   // upstream gradient
+        }
+        if (a.verify) column_reference_kernel<T><<<col_blocks, 128>>>(in0, c, yfw, ref0, ref1, a.numseq, a.seqlen, a.chan, a.reverse, a.bwd);
+        CK(cudaDeviceSynchronize());
+    } else if (a.bwd) {
         // forward outputs feed the backward pass; made by the sequential operator
         int rc = linrec_b200_fwd(LINREC_KIND_REF, in0, c, yfw, a.numseq, a.seqlen, a.stride, a.reverse, a.dtype, nullptr, ws,
                                  ws_bytes, 0);
         if (rc) { fprintf(stderr, "reference forward failed: %s\n", linrec_b200_strerror(rc)); return 1; }
         fill_kernel<T><<<2048, 256>>>(in0, total, 3, 0, 0, 1);   // upstream gradient
     }
-    if (a.verify) {
+    if (a.verify && a.chan == 0) {
         int rc = a.bwd ? linrec_b200_bwd(LINREC_KIND_REF, in0, c, yfw, ref0, ref1, a.numseq, a.seqlen, a.stride, a.reverse,
                                          a.dtype, nullptr, ws, ws_bytes, 0)
                        : linrec_b200_fwd(LINREC_KIND_REF, in0, c, ref0, a.numseq, a.seqlen, a.stride, a.reverse, a.dtype,
@@ -253,7 +309,7 @@ static int run(const Args& a)
         configs.emplace_back();
     }
 
-    const double elems = (double)a.numseq * (double)a.seqlen;
+    const double elems = (double)a.numseq * (double)a.seqlen * (a.chan > 0 ? (double)a.chan : 1.0);
     const double bytes = elems * (a.bwd ? 5.0 : 3.0) * sizeof(T);
     int worst = 0;
     for (const auto& cfg : configs) {
@@ -264,8 +320,8 @@ static int run(const Args& a)
             values.push_back(a.opt_values[i]);
         }
         Result r = run_one<T>(a, names, values, in0, c, yfw, out0, out1, ref0, ref1, ws, ws_bytes, flush_buf, flush_n, d_max, d_bad);
-        printf("{\"numseq\": %lld, \"seqlen\": %lld, \"stride\": %lld, \"reverse\": %d, \"bwd\": %d, \"dtype\": \"%s\", \"kind\": %d, \"opts\": {",
-               a.numseq, a.seqlen, a.stride, a.reverse, a.bwd, a.dtype == LINREC_DTYPE_F32 ? "f32" : a.dtype == LINREC_DTYPE_BF16 ? "bf16" : "f16", a.kind);
+        printf("{\"numseq\": %lld, \"seqlen\": %lld, \"chan\": %lld, \"stride\": %lld, \"reverse\": %d, \"bwd\": %d, \"dtype\": \"%s\", \"kind\": %d, \"opts\": {",
+               a.numseq, a.seqlen, a.chan, a.stride, a.reverse, a.bwd, a.dtype == LINREC_DTYPE_F32 ? "f32" : a.dtype == LINREC_DTYPE_BF16 ? "bf16" : "f16", a.kind);
         for (size_t i = 0; i < names.size(); ++i) printf("%s\"%s\": %d", i ? ", " : "", names[i].c_str(), values[i]);
         printf("}, \"rc\": %d, \"status\": %d", r.rc, r.status);
         if (r.rc == LINREC_OK) {
@@ -303,6 +359,7 @@ int main(int argc, char** argv)
         if (s == "--numseq") a.numseq = atoll(next());
         else if (s == "--seqlen") a.seqlen = atoll(next());
         else if (s == "--stride") a.stride = atoll(next());
+        else if (s == "--chan") a.chan = atoll(next());
         else if (s == "--reverse") a.reverse = 1;
         else if (s == "--bwd") a.bwd = 1;
         else if (s == "--dtype") { std::string d = next(); a.dtype = d == "bf16" ? LINREC_DTYPE_BF16 : d == "f16" ? LINREC_DTYPE_F16 : LINREC_DTYPE_F32; }

@@ -142,6 +142,64 @@ def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
     return outs
 
 
+def dim_eligible(t: torch.Tensor, dim: int) -> bool:
+    """Can the scan run along `dim` of `t` in place of a transposed copy?  Needs a dense tensor,
+    16-byte aligned, whose trailing extent (the product of the sizes after `dim`) is a whole number
+    of 16-byte chunks."""
+    if t.dtype not in _DTYPES or not t.is_cuda or not t.is_contiguous():
+        return False
+    inner = 1
+    for s in t.shape[dim + 1:]:
+        inner *= s
+    return inner > 1 and (inner * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+
+
+def _launch_dim(bwd: bool, ins, dim: int, reverse: bool, kwargs: dict):
+    """Forward or backward scan along `dim` (not the last) of dense tensors of one shape, through
+    linrec_b200_fwd_dim / linrec_b200_bwd_dim: the tensors are taken as (nb, seqlen, nchan)."""
+    ref = ins[0]
+    for t in ins:
+        if t.shape != ref.shape or t.dtype != ref.dtype or t.device != ref.device:
+            raise RuntimeError("linrec: tensors must have the same shape, dtype and device")
+        if not dim_eligible(t, dim):
+            raise RuntimeError("linrec: scan along this dimension needs dense, 16-byte aligned tensors")
+    outs = [torch.empty_like(ref) for _ in range(2 if bwd else 1)]
+    if ref.numel() == 0:
+        return outs
+    nb = 1
+    for s in ref.shape[:dim]:
+        nb *= s
+    seqlen = ref.shape[dim]
+    nchan = ref.numel() // (nb * seqlen)
+    dtype = _DTYPES[ref.dtype]
+    opts, keep = _capi.make_opts(kwargs)
+    with torch.cuda.device(ref.device):
+        stream = torch.cuda.current_stream(ref.device).cuda_stream
+        need = _capi.lib.linrec_b200_dim_workspace_size(int(bwd), nb, seqlen, nchan, dtype, opts)
+        if need == 0:
+            raise NotImplementedError("linrec: no compiled variant for these options")
+        ws = _workspace(ref.device, stream, need)
+        if not bwd:
+            rc = _capi.lib.linrec_b200_fwd_dim(ins[0].data_ptr(), ins[1].data_ptr(), outs[0].data_ptr(), nb, seqlen,
+                                               nchan, int(bool(reverse)), dtype, opts, ws.data_ptr(), ws.numel(), stream)
+        else:
+            rc = _capi.lib.linrec_b200_bwd_dim(ins[0].data_ptr(), ins[1].data_ptr(), ins[2].data_ptr(),
+                                               outs[0].data_ptr(), outs[1].data_ptr(), nb, seqlen, nchan,
+                                               int(bool(reverse)), dtype, opts, ws.data_ptr(), ws.numel(), stream)
+        _capi.raise_for(rc, "linrec_b200_bwd_dim" if bwd else "linrec_b200_fwd_dim")
+        if _CHECK_EVERY_CALL:
+            _capi.raise_for(_capi.lib.linrec_b200_status(ws.data_ptr(), stream), "linrec_b200 device status")
+    return outs
+
+
+def linrec_dim_fwd(inputs, coeffs, dim, reverse=False, **kwargs):
+    return _launch_dim(False, (inputs, coeffs), dim, reverse, kwargs)[0]
+
+
+def linrec_dim_bwd(d_outputs, coeffs, outputs, dim, reverse=False, **kwargs):
+    return tuple(_launch_dim(True, (d_outputs, coeffs, outputs), dim, reverse, kwargs))
+
+
 def _fwd(kind):
     def f(inputs, coeffs, reverse=False, **kwargs):
         return _launch(kind, False, (inputs, coeffs), reverse, kwargs)[0]

@@ -1,0 +1,205 @@
+"""Scan along a dimension other than the last (GPU only; every call goes through the C ABI:
+linrec_b200_fwd_dim / linrec_b200_bwd_dim).  The checker is the CPU oracle run on the transposed
+tensors, i.e. the definition of the reference's `dim` argument (linrec/impl/python/ops.py:8-14).
+
+Tolerances as for the last-dimension operators: fp32 rtol 1e-4 / atol 1e-5 (2e-5 for dc);
+2-byte storage rtol 2^-7 / atol 1e-5 against fp32 on the rounded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-4, 1e-5
+SEED = 12334567890
+
+
+def _lb():
+    import linrec_b200
+    import linrec_b200.ops as ops
+    from linrec_b200.general import linrec_general
+    return linrec_b200, ops, linrec_general
+
+
+def _data(shape, clo=0.5, chi=1.0, seed=SEED):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    c = clo + (chi - clo) * torch.rand(shape, generator=g)
+    dy = torch.randn(shape, generator=g)
+    return x, c, dy
+
+
+def _oracle_dim(x, c, dy, dim, rev):
+    """Oracle along `dim`: move the axis last, scan rows, move it back."""
+    last = x.dim() - 1
+    xt, ct, dyt = (t.transpose(dim, last).contiguous().numpy() for t in (x, c, dy))
+    y = oracle.fwd_f32(xt, ct, reverse=rev)
+    dx, dc = oracle.bwd_f32(dyt, ct, y, reverse=rev)
+    back = lambda a: torch.from_numpy(a).transpose(dim, last).contiguous()
+    return back(y), back(dx), back(dc)
+
+
+def _check(shape, dim, rev, dtype=torch.float32, rtol=RTOL, atol=ATOL, **kw):
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape)
+    if dtype != torch.float32:
+        x, c, dy = (t.to(dtype).float() for t in (x, c, dy))
+    y_ref, dx_ref, dc_ref = _oracle_dim(x, c, dy, dim, rev)
+    xd, cd, dyd = (t.to(dev, dtype) for t in (x, c, dy))
+    y = ops.linrec_dim_fwd(xd, cd, dim, rev, **kw)
+    np.testing.assert_allclose(y.float().cpu().numpy(), y_ref.numpy(), rtol=rtol, atol=atol)
+    yd = y_ref.to(dev, dtype)
+    if dtype != torch.float32:
+        # backward from the rounded forward outputs, as autograd would hand them over
+        _, dx_ref, dc_ref = _oracle_bwd_from(yd.float().cpu(), c, dy, dim, rev)
+    dx, dc = ops.linrec_dim_bwd(dyd, cd, yd, dim, rev, **kw)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref.numpy(), rtol=rtol, atol=atol)
+    np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref.numpy(), rtol=rtol, atol=2 * atol)
+    lb.check_status()
+
+
+def _oracle_bwd_from(y, c, dy, dim, rev):
+    last = y.dim() - 1
+    yt, ct, dyt = (t.transpose(dim, last).contiguous().numpy() for t in (y, c, dy))
+    dx, dc = oracle.bwd_f32(dyt, ct, yt, reverse=rev)
+    back = lambda a: torch.from_numpy(a).transpose(dim, last).contiguous()
+    return None, back(dx), back(dc)
+
+
+SHAPES = [(3, 100, 36), (2, 1000, 4), (1, 5000, 128), (5, 33, 260), (2, 4099, 512), (4, 300, 1024), (1, 1, 8), (7, 2, 4)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("rev", [False, True])
+def test_middle_axis_fp32(shape, rev):
+    for kw in ({}, {"kChunksPerJob": 0}, {"kChunksPerJob": 1}, {"kChunksPerJob": 3}):
+        _check(shape, 1, rev, **kw)
+
+
+@pytest.mark.parametrize("variant", [(128, 32, 3), (128, 32, 2), (128, 32, 4), (64, 64, 3), (64, 64, 2), (32, 128, 3),
+                                     (32, 128, 2), (32, 64, 4), (256, 32, 2)], ids=lambda v: "x".join(map(str, v)))
+def test_every_compiled_variant(variant):
+    nt, lc, s = variant
+    for shape in [(3, 700, 264), (40, 129, 132)]:
+        for rev in (False, True):
+            for k in (1, 2, 0):
+                _check(shape, 1, rev, kThreadsPerBlock=nt, kRowsPerChunk=lc, kStages=s, kChunksPerJob=k)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(3, 100, 40), (2, 1000, 8), (1, 3000, 256), (3, 515, 1032)], ids=lambda s: "x".join(map(str, s)))
+def test_middle_axis_two_byte(dtype, shape):
+    for rev in (False, True):
+        for kw in ({}, {"kChunksPerJob": 1}, {"kChunksPerJob": 0}):
+            _check(shape, 1, rev, dtype=dtype, rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -9,
+                   atol=1e-5 if dtype == torch.bfloat16 else 1e-4, **kw)
+
+
+def test_256_wide_variant_is_fp32_only():
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    x = torch.ones(2, 64, 512, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        ops.linrec_dim_fwd(x, x, 1, False, kThreadsPerBlock=256, kRowsPerChunk=32, kStages=2)
+
+
+def test_many_columns_and_long_sequences():
+    """Enough columns for jobs of several chunks that wait on their predecessor, and few columns with
+    long sequences (decoupled look-back over many chunks)."""
+    _check((600, 2100, 128), 1, False)
+    _check((600, 2100, 128), 1, True)
+    _check((2, 70000, 64), 1, False)
+    _check((1, 50001, 256), 1, True)
+
+
+def test_general_signature_uses_the_axis_kernel_and_matches_the_transposed_path():
+    lb, ops, linrec_general = _lb()
+    dev = torch.device("cuda:0")
+    for shape, dim in [((3, 200, 64), 1), ((2, 3, 150, 32), 2), ((2, 90, 4, 8), 1), ((300, 16), 0)]:
+        x, c, dy = _data(shape)
+        for rev in (False, True):
+            xd = x.to(dev).requires_grad_(True)
+            cd = c.to(dev).requires_grad_(True)
+            n0 = lb._C.launch_count()
+            y = linrec_general(xd, cd, dim=dim, reverse=rev)
+            gx, gc = torch.autograd.grad(y, (xd, cd), dy.to(dev))
+            assert lb._C.launch_count() - n0 == 2        # one kernel forward, one backward, no copies of ours
+            y_ref, dx_ref, dc_ref = _oracle_dim(x, c, dy, dim, rev)
+            np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(gx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(gc.cpu().numpy(), dc_ref.numpy(), rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()
+
+
+def test_general_signature_falls_back_for_unaligned_channels():
+    lb, ops, linrec_general = _lb()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((3, 50, 7))          # 7 channels of 4 bytes: not whole 16-byte chunks
+    assert not ops.dim_eligible(x.to(dev), 1)
+    y = linrec_general(x.to(dev), c.to(dev), dim=1)
+    y_ref, _, _ = _oracle_dim(x, c, dy, 1, False)
+    np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+    with pytest.raises(RuntimeError):
+        ops.linrec_dim_fwd(x.to(dev), c.to(dev), 1, False)
+
+
+def test_first_coefficient_is_ignored():
+    """A non-finite coefficient at the first element of a sequence has no effect, as in the
+    reference kernels that start with y[s] = x[s] (linrec/impl/cuda/linrec_ref.cuh:63)."""
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((2, 77, 16))
+    for rev in (False, True):
+        c2 = c.clone()
+        c2[:, -1 if rev else 0, :] = float("inf")
+        y = ops.linrec_dim_fwd(x.to(dev), c2.to(dev), 1, rev)
+        y_ref, _, _ = _oracle_dim(x, c, dy, 1, rev)
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+
+
+def test_guard_bands_untouched():
+    """Outputs written through the C ABI into the middle of sentinel-filled allocations."""
+    import ctypes
+    from linrec_b200 import _capi
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    for (nb, L, D) in [(3, 45, 12), (2, 130, 260), (1, 33, 516)]:
+        for bwd in (False, True):
+            x, c, dy = _data((nb, L, D))
+            n, pad = nb * L * D, 1024
+            outs = [torch.full((n + 2 * pad,), -777.0, device=dev) for _ in range(2)]
+            xd, cd, yd = x.to(dev), c.to(dev), dy.to(dev)
+            need = _capi.lib.linrec_b200_dim_workspace_size(int(bwd), nb, L, D, 0, None)
+            ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+            st = torch.cuda.current_stream().cuda_stream
+            o0 = outs[0].data_ptr() + pad * 4
+            o1 = outs[1].data_ptr() + pad * 4
+            if not bwd:
+                rc = _capi.lib.linrec_b200_fwd_dim(xd.data_ptr(), cd.data_ptr(), o0, nb, L, D, 0, 0, None, ws.data_ptr(), need, st)
+            else:
+                rc = _capi.lib.linrec_b200_bwd_dim(xd.data_ptr(), cd.data_ptr(), yd.data_ptr(), o0, o1, nb, L, D, 0, 0, None,
+                                                   ws.data_ptr(), need, st)
+            assert rc == 0
+            torch.cuda.synchronize()
+            for o in outs[: 2 if bwd else 1]:
+                assert (o[:pad] == -777.0).all() and (o[pad + n:] == -777.0).all()
+                assert (o[pad:pad + n] != -777.0).all()
+
+
+def test_lookback_wait_gives_up_with_status():
+    """Tickets are started past the first job of every column, so the jobs that run wait for a
+    predecessor that never publishes.  The wait ends by itself and leaves a status code; the context
+    stays usable."""
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    x = torch.ones(1, 4096, 128, device=dev)
+    ops.linrec_dim_fwd(x, x, 1, False, kChunksPerJob=1, firstTicket=3, waitBudgetMs=20)
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        lb.check_status()
+    y = ops.linrec_dim_fwd(x, x * 0.5, 1, False)
+    lb.check_status()
+    assert torch.isfinite(y).all()

@@ -485,6 +485,36 @@ def test_inf_in_first_coefficient_is_ignored():
     np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(x.numpy(), c2.numpy()), rtol=RTOL, atol=ATOL)
 
 
+def test_call_from_a_fresh_host_thread():
+    """The first call a host thread makes finds the caches warm and makes no CUDA runtime call that
+    would bind a device context before the tensor maps are encoded (autograd workers are such
+    threads); the library has to bind it."""
+    import threading
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((64, 4096))
+    xd, cd, dyd = x.to(dev), c.to(dev), dy.to(dev)
+    y0 = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=False)      # warms every cache
+    dx0, dc0 = lb._C.linrec_pipe_bwd(d_outputs=dyd, coeffs=cd, outputs=y0, reverse=False)
+    torch.cuda.synchronize()
+    out = {}
+
+    def work():
+        try:
+            y = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=False)
+            dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dyd, coeffs=cd, outputs=y0, reverse=False)
+            torch.cuda.synchronize()
+            out["ok"] = torch.equal(y, y0) and torch.equal(dx, dx0) and torch.equal(dc, dc0)
+        except Exception as exc:   # reported in the main thread
+            out["exc"] = exc
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "exc" not in out, out.get("exc")
+    assert out["ok"]
+
+
 # ---- bounded waits -----------------------------------------------------------------------------------
 def test_lookback_wait_gives_up_with_status():
     """Tickets are started past the first piece of every row, so the pieces that run wait for a
