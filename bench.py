@@ -256,6 +256,38 @@ def run_ours(args):
     step_bytes = n_elem * (BYTES_PER_ELEM_FWD + BYTES_PER_ELEM_BWD)
     value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
 
+    # ---- two side measurements on rank 0 of a single-GPU run ---------------------------------------
+    # (1) the practical ceiling of this access pattern: an element-wise 2-read / 1-write kernel on the
+    #     same tensors; (2) the same problem laid out (batch, sequence, channel) and scanned along the
+    #     middle axis where it lies (linrec_b200_fwd_dim / linrec_b200_bwd_dim).
+    ceiling = axis = None
+    if world == 1:
+        def timed(fn, n):
+            fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+        tmp = torch.empty_like(x)
+        ms = timed(lambda: torch.mul(x, c, out=tmp), 20)
+        ceiling = {"op": "torch.mul(x, c, out=y), 12 B per element", "ms": ms, "gbps": n_elem * 12 / (ms * 1e-3) / 1e9}
+        del tmp
+        from linrec_b200 import ops as lr_ops
+        xa, ca, dya = (t.view(SHAPE[0], SHAPE[2], SHAPE[1]) for t in (x, c, dy))
+        ya = lr_ops.linrec_dim_fwd(xa, ca, 1, False)
+        f_ms = timed(lambda: lr_ops.linrec_dim_fwd(xa, ca, 1, False), 10)
+        b_ms = timed(lambda: lr_ops.linrec_dim_bwd(dya, ca, ya, 1, False), 10)
+        linrec_b200.check_status()
+        axis = {"workload": "(16, 8192, 2048) fp32, scan along the middle axis, no transposed copies",
+                "fwd_gbps": n_elem * BYTES_PER_ELEM_FWD / (f_ms * 1e-3) / 1e9,
+                "bwd_gbps": n_elem * BYTES_PER_ELEM_BWD / (b_ms * 1e-3) / 1e9,
+                "value": step_bytes / ((f_ms + b_ms) * 1e-3) / 1e9, "unit": "GB/s"}
+        del ya, xa, ca, dya
+
     # ---- end to end from pinned host buffers through the public API -----------------------------
     # linrec_b200.host streams row slabs: copy-in of slab i+1, scan of slab i and copy-out of slab
     # i-1 overlap on three streams; every byte of x, c, dy crosses PCIe in and every byte of y, dx, dc
@@ -379,7 +411,7 @@ def run_ours(args):
             "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
             "traffic": (NCU_DRAM_BYTES_PER_ELEM_BWD * n_elem) if NCU_DRAM_BYTES_PER_ELEM_BWD else None,
             "algorithmic_bytes_per_launch": n_elem * BYTES_PER_ELEM_BWD, "ms_per_launch": bwd_ms,
-            "frac_of_nominal_8TBs": achieved / 8000.0,
+            "frac_of_nominal_8TBs": achieved / 8000.0, "elementwise_ceiling": ceiling,
             "forward": {"achieved": n_elem * BYTES_PER_ELEM_FWD / (fwd_ms * 1e-3) / 1e9, "ms_per_launch": fwd_ms,
                         "frac": n_elem * BYTES_PER_ELEM_FWD / (fwd_ms * 1e-3) / 1e9 / peak}}
 
@@ -413,6 +445,7 @@ def run_ours(args):
                                           "api": "linrec_b200.linrec + torch.autograd.grad"}},
         "gpu_launches": int(launches),
         "seq_sharded": seq,
+        "axis_scan": axis,
         "roofline": roof,
         "cpu_baseline": cpu,
     }

@@ -756,9 +756,9 @@ const std::vector<ColVariant>& col_variants()
         make_col_variant<128, 32, 4>(),
         make_col_variant<64, 64, 3>(),
         make_col_variant<64, 64, 2>(),
-        make_col_variant<32, 128, 3>(),
+        make_col_variant<32, 64, 3>(),
+        make_col_variant<32, 64, 2>(),
         make_col_variant<32, 128, 2>(),
-        make_col_variant<32, 64, 4>(),
         make_col_variant<256, 32, 2>(),
     };
     return v;
@@ -770,9 +770,14 @@ struct ColPlan {
     long long units = 0, njobs = 0;
 };
 
-// Resident CTA slots the job count is sized for (148 SMs x 2 CTAs): fixed, so that the workspace a
-// problem needs does not depend on the device the size query runs on.
-constexpr long long kColSlots = 296;
+// Default tile shapes, widest first, with the CTAs per SM their shared memory allows.  The job
+// count is sized for 148 SMs, fixed, so that the workspace a problem needs does not depend on the
+// device the size query runs on.
+struct ColShape {
+    int NT, LC, S_fwd, S_bwd, ctas_per_sm;
+};
+constexpr ColShape kColShapes[3] = {{128, 32, 3, 2, 2}, {64, 64, 3, 2, 2}, {32, 64, 3, 2, 4}};
+constexpr long long kColSMs = 148;
 
 int make_col_plan(ColPlan& pl, bool bwd, int dtype, int64_t nb, int64_t seqlen, int64_t nchan, const Options& opt,
                   int max_smem)
@@ -780,20 +785,35 @@ int make_col_plan(ColPlan& pl, bool bwd, int dtype, int64_t nb, int64_t seqlen, 
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     const int per_word = di == 0 ? 1 : 2;
     int NT = opt.NT, LC = opt.LC, S = opt.S;
+    // 0 = undecided, 1 = chained jobs of several chunks, 2 = one job per column, 3 = every chunk a job
+    int mode = 0;
+    long long slots = 2 * kColSMs;
     if (NT < 0 && LC < 0 && S < 0) {
-        // Defaults: tiles of 4096 channel words; three stages forward (two operands per stage), two
-        // backward (three operands): two CTAs per SM either way.  The tile is as wide as it can be
-        // while there are still enough columns to give every resident CTA one of its own; with
-        // fewer columns it is narrow and tall, so that a column has fewer chunks in flight.
-        NT = 32;
-        for (int nt = 128; nt >= 32; nt >>= 1) {
-            if (4 * nb * ceil_div(nchan, (int64_t)nt * per_word) >= 3 * kColSlots) {
-                NT = nt;
+        // A job waits for the inclusive value of its predecessor in the same column, which was handed
+        // out `units` tickets earlier; that wait is free only if there are clearly more columns than
+        // resident CTAs.  So: the widest tile that still leaves 1.25 columns per resident CTA.
+        const ColShape* pick = nullptr;
+        for (const ColShape& c : kColShapes) {
+            const long long u = nb * ceil_div(nchan, (int64_t)c.NT * per_word);
+            if (4 * u >= 5 * kColSMs * c.ctas_per_sm) {
+                pick = &c;
+                mode = 1;
                 break;
             }
         }
-        LC = 4096 / NT;
-        S = bwd ? 2 : 3;
+        if (!pick) {
+            // Fewer columns than that: the narrowest tile, and every column gets a CTA of its own for
+            // its whole length, so that nobody waits for anybody (measured 2 to 4 times faster than
+            // cutting such columns into chunks linked by look-back, whose dependent descriptor loads
+            // then dominate).  Only with a handful of columns does the sequence axis have to supply
+            // the parallelism (decoupled look-back); callers that can afford transposed copies are
+            // better off with the last-axis kernels there.
+            pick = &kColShapes[2];
+            const long long u = nb * ceil_div(nchan, (int64_t)pick->NT * per_word);
+            mode = u >= 64 ? 2 : 3;
+        }
+        NT = pick->NT; LC = pick->LC; S = bwd ? pick->S_bwd : pick->S_fwd;
+        slots = kColSMs * pick->ctas_per_sm;
     }
     for (const ColVariant& v : col_variants()) {
         if (!((NT < 0 || v.NT == NT) && (LC < 0 || v.LC == LC) && (S < 0 || v.S == S))) continue;
@@ -808,16 +828,16 @@ int make_col_plan(ColPlan& pl, bool bwd, int dtype, int64_t nb, int64_t seqlen, 
     pl.nq = (int)ceil_div(seqlen, pl.v->LC);
     int k = opt.K;
     if (k < 0) {
-        if (4 * pl.units >= 3 * kColSlots) {
-            // Enough columns to keep the resident CTAs busy with one job per column at a time: jobs of
-            // several chunks that wait for their predecessor's inclusive value, about 32 jobs per
-            // resident CTA so that the last round is short.
-            long long gens = (32 * kColSlots + pl.units - 1) / pl.units;
+        if (mode == 0) mode = 4 * pl.units >= 5 * slots ? 1 : (pl.units >= 64 ? 2 : 3);
+        if (mode == 1) {
+            // about 32 jobs per resident CTA, so that the last round is short, but at least 4 chunks
+            // per job, so that the hand-over between jobs stays a small part of a job
+            long long gens = (32 * slots + pl.units - 1) / pl.units;
+            if (gens > pl.nq / 4) gens = pl.nq / 4;
             if (gens < 1) gens = 1;
-            if (gens > pl.nq) gens = pl.nq;
             k = (int)ceil_div(pl.nq, gens);
         } else {
-            k = 1;   // few columns: every chunk is a job, linked by decoupled look-back
+            k = mode == 2 ? pl.nq : 1;
         }
     }
     if (k == 0 || k > pl.nq) k = pl.nq;

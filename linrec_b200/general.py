@@ -3,8 +3,8 @@ dim=-1, reverse=False)` (linrec/impl/python/ops.py:8-61), on top of the CUDA sca
 
 `dim`   the scan runs along `dim`.  For a dimension other than the last, dense 16-byte aligned
         tensors whose trailing extent is a whole number of 16-byte chunks are scanned where they lie
-        (a kernel that walks down the axis, neighbouring channels on neighbouring threads); anything
-        else costs a transposed copy in and out.
+        (a kernel that walks down the axis, neighbouring channels on neighbouring threads), unless
+        there are only a handful of columns; anything else costs a transposed copy in and out.
 `logc`  coefficients are given as logarithms: c = exp(coeffs).  The gradient with respect to the
         logarithm is d_coeffs * c.  (The reference's own backward multiplies by the SHIFTED
         coefficients, linrec/impl/python/ops.py:33-38, which is not the derivative of its forward;
@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import torch
 
-from .ops import dim_eligible, linrec_dim_bwd, linrec_dim_fwd, linrec_pipe
+from .ops import dim_eligible, dim_worthwhile, linrec_dim_bwd, linrec_dim_fwd, linrec_pipe
 
 __all__ = ["linrec_general"]
 
@@ -48,7 +48,7 @@ def linrec_general(inputs: torch.Tensor, coeffs: torch.Tensor, logc: bool = Fals
     last = inputs.dim() - 1
     d = dim % inputs.dim() if inputs.dim() else 0
     if d != last:
-        if (inputs.shape == coeffs.shape and inputs.dtype == coeffs.dtype and dim_eligible(inputs, d)
+        if (inputs.shape == coeffs.shape and inputs.dtype == coeffs.dtype and dim_worthwhile(inputs, d)
                 and dim_eligible(coeffs, d)):
             return _LinrecDimFn.apply(inputs, coeffs, d, bool(reverse))
         x = inputs.transpose(d, last).contiguous()

@@ -154,6 +154,23 @@ def dim_eligible(t: torch.Tensor, dim: int) -> bool:
     return inner > 1 and (inner * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
 
 
+def dim_worthwhile(t: torch.Tensor, dim: int) -> bool:
+    """Is scanning along `dim` where the tensor lies faster than transposed copies around the
+    last-axis kernel?  Measured on B200: yes unless there are only a few columns (one column = 32
+    channel words of one batch entry), where the kernel has to cut the sequence into chunks linked
+    by look-back and reaches 0.7-1.5 TB/s against about 2 TB/s for the transposed path."""
+    if not dim_eligible(t, dim):
+        return False
+    nb = 1
+    for s in t.shape[:dim]:
+        nb *= s
+    nchan = 1
+    for s in t.shape[dim + 1:]:
+        nchan *= s
+    per_col = 32 * (4 // t.element_size())
+    return nb * -(-nchan // per_col) >= 128
+
+
 def _launch_dim(bwd: bool, ins, dim: int, reverse: bool, kwargs: dict):
     """Forward or backward scan along `dim` (not the last) of dense tensors of one shape, through
     linrec_b200_fwd_dim / linrec_b200_bwd_dim: the tensors are taken as (nb, seqlen, nchan)."""

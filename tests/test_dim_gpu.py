@@ -80,8 +80,8 @@ def test_middle_axis_fp32(shape, rev):
         _check(shape, 1, rev, **kw)
 
 
-@pytest.mark.parametrize("variant", [(128, 32, 3), (128, 32, 2), (128, 32, 4), (64, 64, 3), (64, 64, 2), (32, 128, 3),
-                                     (32, 128, 2), (32, 64, 4), (256, 32, 2)], ids=lambda v: "x".join(map(str, v)))
+@pytest.mark.parametrize("variant", [(128, 32, 3), (128, 32, 2), (128, 32, 4), (64, 64, 3), (64, 64, 2), (32, 64, 3),
+                                     (32, 64, 2), (32, 128, 2), (256, 32, 2)], ids=lambda v: "x".join(map(str, v)))
 def test_every_compiled_variant(variant):
     nt, lc, s = variant
     for shape in [(3, 700, 264), (40, 129, 132)]:
@@ -119,7 +119,7 @@ def test_many_columns_and_long_sequences():
 def test_general_signature_uses_the_axis_kernel_and_matches_the_transposed_path():
     lb, ops, linrec_general = _lb()
     dev = torch.device("cuda:0")
-    for shape, dim in [((3, 200, 64), 1), ((2, 3, 150, 32), 2), ((2, 90, 4, 8), 1), ((300, 16), 0)]:
+    for shape, dim in [((64, 200, 64), 1), ((8, 16, 150, 32), 2), ((130, 90, 4, 8), 1), ((300, 4096), 0)]:
         x, c, dy = _data(shape)
         for rev in (False, True):
             xd = x.to(dev).requires_grad_(True)
@@ -133,6 +133,16 @@ def test_general_signature_uses_the_axis_kernel_and_matches_the_transposed_path(
             np.testing.assert_allclose(gx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=ATOL)
             np.testing.assert_allclose(gc.cpu().numpy(), dc_ref.numpy(), rtol=RTOL, atol=2 * ATOL)
     lb.check_status()
+
+
+def test_general_signature_takes_the_transposed_path_for_a_handful_of_columns():
+    lb, ops, linrec_general = _lb()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((2, 300, 64))
+    assert ops.dim_eligible(x.to(dev), 1) and not ops.dim_worthwhile(x.to(dev), 1)
+    y = linrec_general(x.to(dev), c.to(dev), dim=1, reverse=True)
+    y_ref, _, _ = _oracle_dim(x, c, dy, 1, True)
+    np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
 
 
 def test_general_signature_falls_back_for_unaligned_channels():
