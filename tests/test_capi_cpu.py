@@ -110,3 +110,42 @@ def test_cpu_tensors_are_rejected():
         linrec_b200.linrec(a, a)
     with pytest.raises(RuntimeError):
         linrec_b200._C.linrec_pipe_fwd(inputs=a, coeffs=a)
+
+
+def test_dim_entry_points_host_logic():
+    """Scan along the middle axis: sizing and refusals that need no device."""
+    from linrec_b200 import _capi
+    L = _capi.lib
+    ws = L.linrec_b200_dim_workspace_size
+    assert ws(0, 0, 10, 10, 0, None) == 256
+    # many columns, short sequences: one job per column or few generations -> small workspace
+    assert ws(0, 4096, 64, 128, 0, None) == 256
+    # enough columns for chained jobs: one 16-byte descriptor per channel and job
+    n = ws(0, 256, 1024, 1024, 0, None)
+    assert n % 256 == 0 and 256 < n < 256 * 1024 * 1024 * 4 // 8
+    # a handful of columns: every chunk is a job
+    few = ws(1, 1, 1 << 16, 64, 0, None)
+    assert few >= 256 + (1 << 16) // 64 * 2 * 32 * 16
+    # options that match no compiled variant
+    opts, keep = _capi.make_opts({"kThreadsPerBlock": 96})
+    assert ws(0, 4, 100, 64, 0, opts) == 0
+    buf = (ctypes.c_float * 64)()
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) & ~15
+    assert L.linrec_b200_fwd_dim(None, None, None, 0, 8, 8, 0, 0, None, None, 0, None) == _capi.OK
+    assert L.linrec_b200_fwd_dim(p16, p16, p16, -1, 8, 8, 0, 0, None, None, 0, None) == _capi.ERR_INVALID_ARG
+    assert L.linrec_b200_fwd_dim(p16, p16, p16, 1, 2, 4, 0, 9, None, None, 0, None) == _capi.ERR_NOT_IMPLEMENTED
+    assert L.linrec_b200_fwd_dim(None, p16, p16, 1, 2, 4, 0, 0, None, None, 0, None) == _capi.ERR_INVALID_ARG
+    # 3 channels of 4 bytes are not whole 16-byte chunks; a pointer 4 bytes off is not aligned
+    assert L.linrec_b200_fwd_dim(p16, p16, p16, 1, 2, 3, 0, 0, None, None, 0, None) == _capi.ERR_UNALIGNED
+    assert L.linrec_b200_fwd_dim(p16 + 4, p16, p16, 1, 2, 4, 0, 0, None, None, 0, None) == _capi.ERR_UNALIGNED
+    assert L.linrec_b200_last_cuda_error() is not None
+
+
+def test_dim_eligibility_helpers():
+    from linrec_b200.ops import dim_eligible, dim_worthwhile
+    t = torch.empty(4, 10, 8)
+    assert not dim_eligible(t, 1)                       # not a CUDA tensor
+    m = torch.empty(4, 10, 8, device="meta")
+    assert not dim_eligible(m, 1)
+    assert not dim_worthwhile(t, 1)
