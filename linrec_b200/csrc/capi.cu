@@ -794,7 +794,10 @@ int make_col_plan(ColPlan& pl, bool bwd, int dtype, int64_t nb, int64_t seqlen, 
         // resident CTAs.  So: the widest tile that still leaves 1.25 columns per resident CTA.
         const ColShape* pick = nullptr;
         for (const ColShape& c : kColShapes) {
-            const long long u = nb * ceil_div(nchan, (int64_t)c.NT * per_word);
+            const long long dc = (long long)c.NT * per_word;
+            const long long u = nb * ceil_div(nchan, dc);
+            // a tile much wider than the channel axis would scan mostly padding
+            if (4 * ceil_div(nchan, dc) * dc > 5 * nchan && &c != &kColShapes[2]) continue;
             if (4 * u >= 5 * kColSMs * c.ctas_per_sm) {
                 pick = &c;
                 mode = 1;
