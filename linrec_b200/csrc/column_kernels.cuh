@@ -297,8 +297,11 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
 
         // forward: the coefficient of a sequence's first element is defined away
         // (linrec/impl/cuda/linrec_ref.cuh:63); backward it arrives as an out-of-range zero
-        int first_row = -1;
-        if (!BWD && q == 0) first_row = ASC ? 0 : (int)(p.seqlen - 1 - (long long)(p.nq - 1) * LC);
+        if (!BWD && q == 0) {
+            // (every thread clears its own word of the row, so no synchronisation is needed)
+            const int first_row = ASC ? 0 : (int)(p.seqlen - 1 - (long long)(p.nq - 1) * LC);
+            bc[first_row * NT + tid] = 0u;
+        }
 
         if (job_first) {
             bool have_carry = true;
@@ -352,7 +355,7 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
                 ChanWord<ST>::unpack(bx[r * NT + tid], xv);
                 ChanWord<ST>::unpack(bc[r * NT + tid], cv);
 #pragma unroll
-                for (int v = 0; v < V; ++v) val[v] = (r == first_row) ? xv[v] : fmaf(val[v], cv[v], xv[v]);
+                for (int v = 0; v < V; ++v) val[v] = fmaf(val[v], cv[v], xv[v]);
                 bx[r * NT + tid] = ChanWord<ST>::pack(val);
                 if (BWD) {
                     float yv[V], dc[V];
