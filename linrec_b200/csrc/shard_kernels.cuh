@@ -5,8 +5,8 @@
 // Pipeline on every rank:
 //   1. local scan of the shard with a zero carry-in (the ordinary scan kernels with `open_start`),
 //      which also leaves per row the pair (P, Y) of the whole shard in a carry record;
-//   2. linrec_edges_kernel (backward only) adds the two elements the neighbours need:
-//      c at the shard's scan-last element and y at its scan-first element;
+//   2. backward only, by the same kernel: the record also takes the two elements the neighbours
+//      need, c at the shard's scan-last element and y at its scan-first element;
 //   3. the records of all shards are all-gathered (NCCL) into local memory;
 //   4. a fix-up kernel folds the records of the shards that come earlier in scan order into the
 //      carry v that enters this shard, and adds v * (running product of the coefficients) to the
@@ -58,18 +58,6 @@ __global__ void linrec_exchange_init_kernel(PeerTable* dst, const PeerTableArg a
 // Shards in scan order: ascending scans visit shard 0 first, descending scans the last shard first.
 template <bool ASC>
 __device__ __forceinline__ int shard_at(int n, int nshards) { return ASC ? n : nshards - 1 - n; }
-
-// backward only: c at the shard's scan-last element, y at its scan-first element
-template <typename ST, bool ASC>
-__global__ void linrec_edges_kernel(const ST* c, const ST* y, float* records, long long numseq, long long seqlen,
-                                    long long row_stride)
-{
-    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= numseq) return;
-    const long long first = ASC ? 0 : seqlen - 1, last = ASC ? seqlen - 1 : 0;
-    records[4 * r + 2] = Storage<ST>::to_float(c[r * row_stride + last]);
-    records[4 * r + 3] = Storage<ST>::to_float(y[r * row_stride + first]);
-}
 
 // The walk along a row goes on while the carried value is a normal number (or not finite).  Once it
 // is subnormal (< 1.18e-38) every further correction is smaller still, and adding it to a result
