@@ -446,6 +446,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (1 GiB per tensor, 6 tensors)",
                    "elements_per_gpu": n_elem, "bytes_per_element": 32},
         "step_ms_median": statistics.median(step_ms), "step_ms_max": max(step_ms),
+        "step_ms_argmax": step_ms.index(max(step_ms)),
         "gelem_per_s": world * n_elem * args.steps / (total_ms * 1e-3) / 1e9,
         "frac_of_measured_peak": value / (world * peak),
         "clocks": clocks,
