@@ -213,3 +213,100 @@ def test_lookback_wait_gives_up_with_status():
     y = ops.linrec_dim_fwd(x, x * 0.5, 1, False)
     lb.check_status()
     assert torch.isfinite(y).all()
+
+
+try:
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    _HAVE_HYPOTHESIS = True
+except Exception:  # pragma: no cover
+    _HAVE_HYPOTHESIS = False
+
+if _HAVE_HYPOTHESIS:
+    @settings(max_examples=50, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+    @given(nb=st.integers(1, 6), length=st.integers(1, 700), chan4=st.integers(1, 150), rev=st.booleans(),
+           k=st.sampled_from([None, 0, 1, 2, 5]), seed=st.integers(0, 1000))
+    def test_fuzz_small_shapes(nb, length, chan4, rev, k, seed):
+        """Random small (batch, sequence, channel) shapes, both directions, forward and backward, every
+        way of cutting a column into jobs."""
+        lb, ops, _ = _lb()
+        dev = torch.device("cuda:0")
+        shape = (nb, length, 4 * chan4)
+        x, c, dy = _data(shape, clo=0.3, seed=seed)
+        kw = {} if k is None else {"kChunksPerJob": k}
+        y_ref, dx_ref, dc_ref = _oracle_dim(x, c, dy, 1, rev)
+        y = ops.linrec_dim_fwd(x.to(dev), c.to(dev), 1, rev, **kw)
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+        dx, dc = ops.linrec_dim_bwd(dy.to(dev), c.to(dev), y_ref.to(dev), 1, rev, **kw)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dc.cpu().numpy(), dc_ref.numpy(), rtol=RTOL, atol=2 * ATOL)
+        lb.check_status()
+
+
+def test_cuda_graph_capture_and_replay():
+    """Like the last-axis operators, a middle-axis operator is one kernel launch on a self-cleaning
+    workspace: a forward + backward step is captured once and replayed on new data."""
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    shape = (6, 900, 256)
+    x, c, dy = (t.to(dev) for t in _data(shape, clo=0.8))
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):          # warm-up on the capture stream: attributes, workspace
+        for _ in range(2):
+            y = ops.linrec_dim_fwd(x, c, 1, False)
+            ops.linrec_dim_bwd(dy, c, y, 1, False)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        y = ops.linrec_dim_fwd(x, c, 1, False)
+        dx, dc = ops.linrec_dim_bwd(dy, c, y, 1, False)
+    for seed in (1, 2, 3):
+        x2, c2, dy2 = _data(shape, clo=0.8, seed=seed)
+        x.copy_(x2); c.copy_(c2); dy.copy_(dy2)
+        graph.replay()
+        torch.cuda.synchronize()
+        y_ref, dx_ref, dc_ref = _oracle_dim(x2, c2, dy2, 1, False)
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=4 * ATOL)
+        np.testing.assert_allclose(dc.cpu().numpy(), dc_ref.numpy(), rtol=RTOL, atol=4 * ATOL)
+    lb.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_full_size_against_the_last_axis_kernels(dtype):
+    """The autograd configuration's 2^28 elements laid out (16, 8192, 2048): the scan along the
+    middle axis must agree with the last-axis kernels run on transposed copies (two independent
+    kernels, tile algebra against a sequential walk), forward and backward, and with linearity:
+    scan(a*x) = a*scan(x)."""
+    lb, ops, _ = _lb()
+    dev = torch.device("cuda:0")
+    shape = (16, 8192, 2048)
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    x = torch.randn(shape, device=dev, generator=g).to(dtype)
+    c = (0.9 + 0.1 * torch.rand(shape, device=dev, generator=g)).to(dtype)
+    dy = torch.randn(shape, device=dev, generator=g).to(dtype)
+    rtol, atol = (RTOL, 1e-4) if dtype == torch.float32 else (2 ** -6, 2e-2)
+
+    def close(a, b, what):
+        a, b = a.float(), b.float()
+        bad = ((a - b).abs() > atol + rtol * b.abs()).sum().item()
+        assert bad <= a.numel() * 1e-6, f"{what}: {bad} of {a.numel()} outside tolerance"
+
+    for rev in (False, True):
+        y = ops.linrec_dim_fwd(x, c, 1, rev)
+        xt, ct = x.transpose(1, 2).contiguous(), c.transpose(1, 2).contiguous()
+        yt = lb._C.linrec_pipe_fwd(inputs=xt, coeffs=ct, reverse=rev)
+        close(y, yt.transpose(1, 2), "forward")
+        del xt
+        dx, dc = ops.linrec_dim_bwd(dy, c, y, 1, rev)
+        dyt, y_t = dy.transpose(1, 2).contiguous(), y.transpose(1, 2).contiguous()
+        dxt, dct = lb._C.linrec_pipe_bwd(d_outputs=dyt, coeffs=ct, outputs=y_t, reverse=rev)
+        close(dx, dxt.transpose(1, 2), "d_inputs")
+        close(dc, dct.transpose(1, 2), "d_coeffs")
+        del dyt, y_t, dxt, dct, ct, yt, dx, dc
+        if dtype == torch.float32:
+            y2 = ops.linrec_dim_fwd(x * 2.0, c, 1, rev)
+            assert torch.equal(y2, y * 2.0)       # scaling by a power of two is exact
+            del y2
+        del y
+    lb.check_status()
