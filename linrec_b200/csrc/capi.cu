@@ -60,6 +60,7 @@ struct Options {
     int p2p_phase = 0;           // peer-exchange calls: 0 = scan and fix-up, 1 = scan only, 2 = fix-up only
     int LC = -1;                 // scan along the middle axis: sequence positions per chunk
     int K = -1;                  // scan along the middle axis: chunks per job (0 = whole column)
+    int logc = 0;                // 1: the coefficient tensor holds logarithms
 };
 
 int parse_options(const linrec_opts* o, Options& out)
@@ -76,6 +77,7 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "kOutBuffers")) out.OB = v;
         else if (!strcmp(n, "kRowsPerChunk")) out.LC = v;
         else if (!strcmp(n, "kChunksPerJob")) out.K = v;
+        else if (!strcmp(n, "logCoeffs")) out.logc = v != 0;
         else if (!strcmp(n, "memcode")) out.memcode = v;
         else if (!strcmp(n, "waitBudgetMs")) out.wait_budget_ms = v;
         else if (!strcmp(n, "ctasPerSm")) out.ctas_per_sm = v;
@@ -580,6 +582,9 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.open_start = open_start;
     p.px = static_cast<const linrec::PeerTable*>(exchange);
     p.px_epoch = exchange ? px_epoch : 0u;
+    p.logc = opt.logc;
+    // the carry records and fix-up kernels of sequence sharding work on plain coefficients
+    if (opt.logc && (carry_out || exchange || open_start)) return LINREC_ERR_NOT_IMPLEMENTED;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     // the gradient scan runs against the direction of the forward pass
@@ -934,6 +939,8 @@ int launch_col(bool bwd, const void* in0, const void* c, const void* yin, void* 
     p.desc = reinterpret_cast<TileDesc*>(static_cast<char*>(workspace) + linrec::kHeaderBytes);
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
     p.first_ticket = (uint32_t)opt.first_ticket;
+    p.logc = opt.logc;
+    p.c_raw = c;
 
     const ColFn fn = pl.v->fn[di][bwd][asc];
     const size_t smem = pl.v->smem[di][bwd];

@@ -47,6 +47,8 @@ struct ColParams {
     TileDesc* desc;        // [gens][units][DC] descriptors (unused when gens == 1)
     long long wait_budget;
     uint32_t first_ticket; // test hook: tickets start here
+    int logc;              // 1: `c` holds logarithms (see ScanParams::logc)
+    const void* c_raw;     // the coefficient tensor itself (logc backward: one word per thread and chunk)
 };
 
 template <typename ST, int NT, int LC, int S, bool BWD>
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
         if (!BWD && q == 0) {
             // (every thread clears its own word of the row, so no synchronisation is needed)
             const int first_row = ASC ? 0 : (int)(p.seqlen - 1 - (long long)(p.nq - 1) * LC);
-            bc[first_row * NT + tid] = 0u;
+            bc[first_row * NT + tid] = p.logc ? Storage<ST>::kNegInfPair : 0u;
         }
 
         if (job_first) {
@@ -328,6 +330,10 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
                         float xv[V], cv[V];
                         ChanWord<ST>::unpack(bx[r * NT + tid], xv);
                         ChanWord<ST>::unpack(bc[r * NT + tid], cv);
+                        if (p.logc) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) cv[v] = expf(cv[v]);
+                        }
 #pragma unroll
                         for (int v = 0; v < V; ++v) {
                             agg[v].y = fmaf(agg[v].y, cv[v], xv[v]);
@@ -343,6 +349,23 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
             }
         }
 
+        // logc backward: the shifted coefficient box lacks the OWN coefficient of the chunk's scan-last
+        // row; every thread fetches its word of that row from global memory
+        float own_edge[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) own_edge[v] = 0.0f;
+        if (BWD && p.logc) {
+            const int mq = ASC ? q : p.nq - 1 - q;
+            const long long l_edge = (long long)mq * LC + (ASC ? LC - 1 : 0);
+            const long long b = item.u / (uint32_t)p.dtiles;
+            const long long ch = (long long)(item.u % (uint32_t)p.dtiles) * DC + (long long)tid * V;
+            if (l_edge < p.seqlen && ch < p.nchan) {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(
+                    reinterpret_cast<const ST*>(p.c_raw) + (b * p.seqlen + l_edge) * p.nchan + ch);
+                ChanWord<ST>::unpack(w, own_edge);
+            }
+        }
+
         // ---- the chunk itself: one fused multiply-add per element, results in place ----------------
         {
             float val[V];
@@ -354,12 +377,30 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
                 float xv[V], cv[V];
                 ChanWord<ST>::unpack(bx[r * NT + tid], xv);
                 ChanWord<ST>::unpack(bc[r * NT + tid], cv);
+                if (p.logc) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) cv[v] = expf(cv[v]);
+                }
 #pragma unroll
                 for (int v = 0; v < V; ++v) val[v] = fmaf(val[v], cv[v], xv[v]);
                 bx[r * NT + tid] = ChanWord<ST>::pack(val);
                 if (BWD) {
                     float yv[V], dc[V];
                     ChanWord<ST>::unpack(by[r * NT + tid], yv);
+                    if (p.logc) {
+                        // gradient with respect to the logarithm: times the element's OWN coefficient, which
+                        // sits one row further along the scan in the shifted coefficient box
+                        const int ro = ASC ? r + 1 : r - 1;
+                        float co[V];
+                        if (ro >= 0 && ro < LC) {
+                            ChanWord<ST>::unpack(bc[ro * NT + tid], co);
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) co[v] = own_edge[v];
+                        }
+#pragma unroll
+                        for (int v = 0; v < V; ++v) yv[v] *= expf(co[v]);
+                    }
 #pragma unroll
                     for (int v = 0; v < V; ++v) dc[v] = val[v] * yv[v];
                     by[r * NT + tid] = ChanWord<ST>::pack(dc);

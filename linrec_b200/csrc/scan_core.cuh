@@ -163,6 +163,8 @@ struct ScanParams {
     int lazy;               // bulk-copy kernel: draw the next ticket only when the current tile is finished
     const PeerTable* px;    // sequence sharding: this rank's exchange buffer (records are pushed to all ranks)
     uint32_t px_epoch;      // epoch of this exchange; 0: no peer exchange in this launch (real epochs start at 1)
+    int logc;               // 1: `c` holds logarithms; the loaders apply exp, the backward pass returns the
+                            //    gradient with respect to the logarithm (d_c * c)
 };
 
 // Storage helpers are declared further down; the record emitter needs them, so it follows them.
@@ -189,6 +191,7 @@ struct Storage<float> {
     __device__ static __forceinline__ float to_float(float v) { return v; }
     __device__ static __forceinline__ float from_float(float v) { return v; }
     static constexpr uint32_t kOnePair = 0x3f800000u;   // the value 1 as a 32-bit word
+    static constexpr uint32_t kNegInfPair = 0xff800000u;   // -infinity (the logarithm of 0)
     __device__ static __forceinline__ float half_of_word(uint32_t w, bool) { return __uint_as_float(w); }
 };
 
@@ -217,6 +220,7 @@ struct Storage<__nv_bfloat16> {
     __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
     static constexpr uint32_t kOnePair = 0x3f803f80u;   // the value 1 in both halves of a 32-bit word
+    static constexpr uint32_t kNegInfPair = 0xff80ff80u;   // -infinity in both halves
     __device__ static __forceinline__ float half_of_word(uint32_t w, bool upper)
     {
         return __uint_as_float(upper ? (w & 0xffff0000u) : (w << 16));
@@ -250,6 +254,7 @@ struct Storage<__half> {
     __device__ static __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
     // the value 1 in both halves of a 32-bit word
     static constexpr uint32_t kOnePair = 0x3c003c00u;
+    static constexpr uint32_t kNegInfPair = 0xfc00fc00u;   // -infinity in both halves
     // a 2-byte element held in the low / high half of a 32-bit word, as float
     __device__ static __forceinline__ float half_of_word(uint32_t w, bool upper)
     {
@@ -441,15 +446,29 @@ struct Operands {
 // forced to 1 AFTER the backward shift: padding must be an identity element (x = 0, c = 1) or the
 // carry record of the row would pick up a stray factor (bulk copies fill with 0, and the shifted
 // coefficient of the first padding slot is the row's last real coefficient).
+// One coefficient read straight from the shared tile (the neighbour across a warp edge).
+template <typename ST>
+__device__ __forceinline__ float edge_coeff(const ST* b_c, int slot, bool logc)
+{
+    const float v = read_slot<ST>(b_c, slot);
+    return logc ? expf(v) : v;
+}
+
 template <typename ST, int E, int NT, bool BWD, bool ASC, bool PATCH>
 __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geometry& g,
                                               const ST* b_in0, const ST* b_c, const ST* b_y,
                                               float pred_c_outside, float succ_y_outside, int valid,
-                                              bool zero_first)
+                                              bool zero_first, bool logc = false)
 {
     load_run<ST, E>(b_in0, g.t, op.x);
     float craw[E];
     load_run<ST, E>(b_c, g.t, craw);
+    // Coefficients given as logarithms: everything read from the coefficient tile goes through exp
+    // (pred_c_outside is a coefficient already).
+    if (logc) {
+#pragma unroll
+        for (int j = 0; j < E; ++j) craw[j] = expf(craw[j]);
+    }
     const int a = g.t * E;          // first slot of the run inside the tile
     const int ra = g.m * E;         // ... and inside its row piece
     if (!BWD) {
@@ -467,7 +486,7 @@ __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geomet
         if (ASC) {   // predecessor = slot below, successor = slot above
             const float c_from_below = __shfl_up_sync(0xffffffffu, craw[E - 1], 1);
             const float y_from_above = __shfl_down_sync(0xffffffffu, yraw[0], 1);
-            const float c_pred = !lo_ok ? pred_c_outside : (g.lane > 0 ? c_from_below : read_slot<ST>(b_c, lo));
+            const float c_pred = !lo_ok ? pred_c_outside : (g.lane > 0 ? c_from_below : edge_coeff<ST>(b_c, lo, logc));
             const float y_succ = !hi_ok ? succ_y_outside : (g.lane < 31 ? y_from_above : read_slot<ST>(b_y, hi));
 #pragma unroll
             for (int j = 0; j < E; ++j) {
@@ -477,13 +496,21 @@ __device__ __forceinline__ void load_operands(Operands<E, BWD>& op, const Geomet
         } else {     // predecessor = slot above, successor = slot below
             const float c_from_above = __shfl_down_sync(0xffffffffu, craw[0], 1);
             const float y_from_below = __shfl_up_sync(0xffffffffu, yraw[E - 1], 1);
-            const float c_pred = !hi_ok ? pred_c_outside : (g.lane < 31 ? c_from_above : read_slot<ST>(b_c, hi));
+            const float c_pred = !hi_ok ? pred_c_outside : (g.lane < 31 ? c_from_above : edge_coeff<ST>(b_c, hi, logc));
             const float y_succ = !lo_ok ? succ_y_outside : (g.lane > 0 ? y_from_below : read_slot<ST>(b_y, lo));
 #pragma unroll
             for (int j = 0; j < E; ++j) {
                 op.c[j] = (j == E - 1) ? c_pred : craw[j + 1];
                 op.ysh[j] = (j == 0) ? y_succ : yraw[j - 1];
             }
+        }
+    }
+    if constexpr (BWD) {
+        // gradient with respect to the logarithm: d_c * c, folded into the shifted outputs that
+        // d_c = d_x * y_shifted is formed from
+        if (logc) {
+#pragma unroll
+            for (int j = 0; j < E; ++j) op.ysh[j] *= craw[j];
         }
     }
     // Slots past the end of the row are identity elements (x = 0 already, c = 1).

@@ -215,7 +215,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             // 4-byte copies from the 4-byte-aligned word that contains the element
             // (a coefficient that lies before an open shard start is 1; both halves for 2-byte storage)
             if (c_ok) ptx::cp_async_4(&halo[s][0], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(csrc) & ~(uintptr_t)3));
-            else halo[s][0] = !p.open_start ? 0u : Storage<ST>::kOnePair;
+            else halo[s][0] = !p.open_start ? (p.logc ? Storage<ST>::kNegInfPair : 0u) : (p.logc ? 0u : Storage<ST>::kOnePair);
             if (y_ok) ptx::cp_async_4(&halo[s][1], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ysrc) & ~(uintptr_t)3));
             else halo[s][1] = 0u;
             ptx::cp_async_mbar_arrive_noinc(&full[s]);
@@ -272,6 +272,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             // 2-byte storage: the element below the piece has an odd index (upper half of its word),
             // the element above it an even one (lower half)
             pred_c = Storage<ST>::half_of_word(wc, ASC);
+            if (p.logc) pred_c = expf(pred_c);   // boundary constants were stored as logarithms
             succ_y = Storage<ST>::half_of_word(wy, !ASC);
         }
         const bool zero_first =
@@ -280,7 +281,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1),
                                                  BWD ? in_buf(s, 2) : in_buf(s, 1), pred_c, succ_y,
-                                                 tc.valid, zero_first);
+                                                 tc.valid, zero_first, p.logc != 0);
         float o0[E], o1[BWD ? E : 1];
         bool alive = true;
         tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
@@ -388,14 +389,16 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
                 const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
                 const long long off = row * p.row_stride + col;
                 const int phys = ci ^ ((ci >> 3) & 7);
-                uint4 q0 = make_uint4(0u, 0u, 0u, 0u), qc = make_uint4(kOne, kOne, kOne, kOne), qy = make_uint4(0u, 0u, 0u, 0u);
+                const uint32_t one = p.logc ? 0u : kOne;                          // identity coefficient
+                const uint32_t zero = p.logc ? Storage<ST>::kNegInfPair : 0u;     // the coefficient 0
+                uint4 q0 = make_uint4(0u, 0u, 0u, 0u), qc = make_uint4(one, one, one, one), qy = make_uint4(0u, 0u, 0u, 0u);
                 if (ok) {
                     q0 = *reinterpret_cast<const uint4*>(gin0 + off);
                     qc = *reinterpret_cast<const uint4*>(gc + off);
                     if (BWD) qy = *reinterpret_cast<const uint4*>(gy + off);
                     if (!BWD && !p.open_start && col == first_col) {
-                        if (ASC) qc.x = sizeof(ST) == 4 ? 0u : (qc.x & 0xffff0000u);
-                        else     qc.w = sizeof(ST) == 4 ? 0u : (qc.w & 0x0000ffffu);
+                        if (ASC) qc.x = sizeof(ST) == 4 ? zero : ((qc.x & 0xffff0000u) | (zero & 0x0000ffffu));
+                        else     qc.w = sizeof(ST) == 4 ? zero : ((qc.w & 0x0000ffffu) | (zero & 0xffff0000u));
                     }
                 }
                 reinterpret_cast<uint4*>(buf_in0)[phys] = q0;
@@ -410,10 +413,10 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
                 const bool ok = (p.chain || j < p.rows_per_tile) && col < p.seqlen && row < p.numseq;
                 const long long off = row * p.row_stride + col;
                 write_slot<ST>(buf_in0, i, ok ? Storage<ST>::to_float(gin0[off]) : 0.0f);
-                float cv = ok ? Storage<ST>::to_float(gc[off]) : 1.0f;
+                float cv = ok ? Storage<ST>::to_float(gc[off]) : (p.logc ? 0.0f : 1.0f);
                 // the coefficient of a row's very first element has no effect (closed rows only); with
                 // padded rows that element need not be a thread's first slot, so it is cleared here
-                if (!BWD && !p.open_start && col == (ASC ? 0 : p.seqlen - 1)) cv = 0.0f;
+                if (!BWD && !p.open_start && col == (ASC ? 0 : p.seqlen - 1)) cv = p.logc ? -INFINITY : 0.0f;
                 write_slot<ST>(buf_c, i, cv);
                 if (BWD) write_slot<ST>(buf_y, i, ok ? Storage<ST>::to_float(gy[off]) : 0.0f);
             }
@@ -423,7 +426,12 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             const long long rb = tc.row * p.row_stride;
             if (tid == 0) {   // coefficient at the scan predecessor of the piece
                 const long long ci = ASC ? lo : hi;
-                halo[0] = (ci >= 0 && ci < p.seqlen) ? Storage<ST>::to_float(gc[rb + ci]) : (p.open_start ? 1.0f : 0.0f);
+                if (ci >= 0 && ci < p.seqlen) {
+                    const float v = Storage<ST>::to_float(gc[rb + ci]);
+                    halo[0] = p.logc ? expf(v) : v;
+                } else {
+                    halo[0] = p.open_start ? 1.0f : 0.0f;
+                }
             } else {          // output at the scan successor of the piece
                 const long long yi = ASC ? hi : lo;
                 halo[1] = (yi >= 0 && yi < p.seqlen) ? Storage<ST>::to_float(gy[rb + yi]) : 0.0f;
@@ -436,7 +444,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, true>(op, g, buf_in0, buf_c, buf_y,
                                                   (BWD && p.chain) ? halo[0] : (p.open_start ? 1.0f : 0.0f),
-                                                  (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first);
+                                                  (BWD && p.chain) ? halo[1] : 0.0f, tc.valid, zero_first, p.logc != 0);
         float o0[E], o1[BWD ? E : 1];
         uint4 probe = make_uint4(0u, 0u, 0u, 0u);   // no look-ahead here: the linking warp probes when it needs to
         tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, 0xffffffffu, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
@@ -577,7 +585,7 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
                     if (BWD) ptx::cp_async_16(reinterpret_cast<uint4*>(buf(s, 2)) + phys, gy + off);
                 } else {
                     *d0 = make_uint4(0u, 0u, 0u, 0u);
-                    *d1 = make_uint4(kOne, kOne, kOne, kOne);
+                    *d1 = p.logc ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(kOne, kOne, kOne, kOne);
                     if (BWD) reinterpret_cast<uint4*>(buf(s, 2))[phys] = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
@@ -590,7 +598,8 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
                 if (idx >= 0 && idx < p.seqlen)
                     ptx::cp_async_4(&halo[s][tid], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)3));
                 else
-                    halo[s][tid] = (tid == 0 && p.open_start) ? kOne : 0u;
+                    halo[s][tid] = tid == 1 ? 0u
+                                   : p.open_start ? (p.logc ? 0u : kOne) : (p.logc ? Storage<ST>::kNegInfPair : 0u);
             }
         }
         ptx::cp_async_commit();   // one group per call, empty or not: the wait below counts groups
@@ -624,12 +633,13 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
         float pred_c = p.open_start ? 1.0f : 0.0f, succ_y = 0.0f;
         if (with_halo) {
             pred_c = Storage<ST>::half_of_word(halo[s][0], ASC);
+            if (p.logc) pred_c = expf(pred_c);   // boundary constants were stored as logarithms
             succ_y = Storage<ST>::half_of_word(halo[s][1], !ASC);
         }
         const bool zero_first = !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, true>(op, g, buf(s, 0), buf(s, 1), BWD ? buf(s, 2) : buf(s, 1), pred_c, succ_y,
-                                                 tc.valid, zero_first);
+                                                 tc.valid, zero_first, p.logc != 0);
         if (!BWD && !p.open_start && !ASC && !p.chain) {
             // padded rows scanned downwards: the row's first element in scan order is its last real
             // element, which need not be the last slot of a thread's run
@@ -700,7 +710,9 @@ __global__ void linrec_seq_kernel(const ScanParams p, int reverse)
         for (long long n = 0; n < L; ++n) {
             const long long i = asc ? n : L - 1 - n;
             const float x = Storage<ST>::to_float(in0[i]);
-            v = (n == 0) ? x : fmaf(v, Storage<ST>::to_float(c[i]), x);
+            float ci = Storage<ST>::to_float(c[i]);
+            if (p.logc) ci = expf(ci);
+            v = (n == 0) ? x : fmaf(v, ci, x);
             out0[i] = Storage<ST>::from_float(v);
         }
     } else {
@@ -713,9 +725,12 @@ __global__ void linrec_seq_kernel(const ScanParams p, int reverse)
             const long long ip = asc ? i - 1 : i + 1;   // scan predecessor
             const long long is = asc ? i + 1 : i - 1;   // scan successor
             const float dy = Storage<ST>::to_float(in0[i]);
-            v = (n == 0) ? dy : fmaf(v, Storage<ST>::to_float(c[ip]), dy);
+            float cp = (n == 0) ? 0.0f : Storage<ST>::to_float(c[ip]);
+            if (p.logc && n > 0) cp = expf(cp);
+            v = (n == 0) ? dy : fmaf(v, cp, dy);
             out0[i] = Storage<ST>::from_float(v);
-            const float ys = (n == L - 1) ? 0.0f : Storage<ST>::to_float(y[is]);
+            float ys = (n == L - 1) ? 0.0f : Storage<ST>::to_float(y[is]);
+            if (p.logc) ys *= expf(Storage<ST>::to_float(c[i]));   // gradient with respect to the logarithm
             out1[i] = Storage<ST>::from_float(v * ys);
         }
     }

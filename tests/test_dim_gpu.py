@@ -310,3 +310,33 @@ def test_full_size_against_the_last_axis_kernels(dtype):
             del y2
         del y
     lb.check_status()
+
+
+@pytest.mark.parametrize("shape", [(3, 100, 36), (2, 1000, 4), (5, 33, 260), (2, 4099, 512), (300, 130, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_log_coefficients_fused(shape):
+    """Option logCoeffs along the middle axis: exp while loading, d_c * c out of the backward kernel
+    (the element's own coefficient comes from the neighbouring row of the shifted box, or from global
+    memory at the chunk edge)."""
+    lb, ops, linrec_general = _lb()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.3)
+    logc = torch.log(c)
+    c_eff = torch.exp(logc)
+    for rev in (False, True):
+        y_ref, dx_ref, dc_ref = _oracle_dim(x, c_eff, dy, 1, rev)
+        dl_ref = dc_ref * c_eff
+        for kw in ({}, {"kChunksPerJob": 1}, {"kChunksPerJob": 0}, {"kThreadsPerBlock": 128}):
+            y = ops.linrec_dim_fwd(x.to(dev), logc.to(dev), 1, rev, logCoeffs=1, **kw)
+            np.testing.assert_allclose(y.cpu().numpy(), y_ref.numpy(), rtol=RTOL, atol=ATOL)
+            dx, dl = ops.linrec_dim_bwd(dy.to(dev), logc.to(dev), y_ref.to(dev), 1, rev, logCoeffs=1, **kw)
+            np.testing.assert_allclose(dx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(dl.cpu().numpy(), dl_ref.numpy(), rtol=RTOL, atol=2 * ATOL)
+    # through the Python signature with autograd
+    xd, ld = x.to(dev).requires_grad_(True), logc.to(dev).requires_grad_(True)
+    y = linrec_general(xd, ld, logc=True, dim=1)
+    gx, gl = torch.autograd.grad(y, (xd, ld), dy.to(dev))
+    y_ref, dx_ref, dc_ref = _oracle_dim(x, c_eff, dy, 1, False)
+    np.testing.assert_allclose(gx.cpu().numpy(), dx_ref.numpy(), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(gl.cpu().numpy(), (dc_ref * c_eff).numpy(), rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()

@@ -321,6 +321,68 @@ def test_general_signature_logc_and_dim():
         np.testing.assert_allclose(gl.cpu().numpy(), rl.numpy(), rtol=RTOL, atol=2 * ATOL)
 
 
+@pytest.mark.parametrize("shape", [(5, 64), (40, 512), (3, 4096 * 5), (7, 100), (33, 1000), (3, 10000), (5, 333), (2, 2101),
+                                   (2, 8192 * 3 + 4096)], ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_log_coefficients_fused(shape, rev):
+    """Option logCoeffs: the kernels take log(c), apply exp while loading, and the backward kernels
+    return d_c * c.  Checked for every loader (bulk copies, cp.async, plain loads, sequential) against
+    the oracle run on c = exp(log c)."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.3, chi=1.0)
+    logc = torch.log(c)
+    c_eff = torch.exp(logc)                      # what the kernels see, up to the rounding of exp
+    y_ref = oracle.fwd_f32(x.numpy(), c_eff.numpy(), reverse=rev)
+    dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c_eff.numpy(), y_ref, reverse=rev)
+    dl_ref = dc_ref * c_eff.numpy()
+    xd, ld, dyd, yd = x.to(dev), logc.to(dev), dy.to(dev), torch.from_numpy(y_ref).to(dev)
+    fams = [("pipe", {}), ("ref", {}), ("pipe", {"memcode": 0})]
+    if shape[1] % 4 == 0:
+        fams.append(("pipe", {"memcode": 2}))
+    for fam, kw in fams:
+        y = getattr(lb._C, f"linrec_{fam}_fwd")(inputs=xd, coeffs=ld, reverse=rev, logCoeffs=1, **kw)
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+        dx, dl = getattr(lb._C, f"linrec_{fam}_bwd")(d_outputs=dyd, coeffs=ld, outputs=yd, reverse=rev, logCoeffs=1, **kw)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(dl.cpu().numpy(), dl_ref, rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()
+
+
+def test_log_coefficients_two_byte_and_first_element():
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    for dtype in (torch.bfloat16, torch.float16):
+        for shape in [(6, 256), (3, 4104), (2, 40000)]:
+            x, c, dy = _data(shape, clo=0.5, chi=1.0)
+            xd, ld = x.to(dev, dtype), torch.log(c).to(dev, dtype)
+            c_eff = torch.exp(ld.float()).cpu()
+            for rev in (False, True):
+                y = lb._C.linrec_pipe_fwd(inputs=xd, coeffs=ld, reverse=rev, logCoeffs=1)
+                ref = oracle.fwd_f32(xd.float().cpu().numpy(), c_eff.numpy(), reverse=rev)
+                np.testing.assert_allclose(y.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2)
+    # a non-finite logarithm at the first element of a row has no effect
+    x, c, dy = _data((4, 1000))
+    l2 = torch.log(c)
+    l2[:, 0] = float("inf")
+    y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=l2.to(dev), reverse=False, logCoeffs=1)
+    np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(x.numpy(), c.numpy()), rtol=RTOL, atol=ATOL)
+    lb.check_status()
+
+
+def test_log_coefficients_not_offered_for_sequence_sharding():
+    import ctypes
+    from linrec_b200 import _capi
+    dev = torch.device("cuda:0")
+    x = torch.ones(2, 256, device=dev)
+    rec = torch.zeros(2, 2, device=dev)
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device=dev)
+    opts, keep = _capi.make_opts({"logCoeffs": 1})
+    rc = _capi.lib.linrec_b200_fwd_carry(x.data_ptr(), x.data_ptr(), x.data_ptr(), rec.data_ptr(), 2, 256, 256, 0, 0, 0, 2,
+                                         opts, ws.data_ptr(), ws.numel(), None)
+    assert rc == _capi.ERR_NOT_IMPLEMENTED
+
+
 try:
     from hypothesis import given, settings, strategies as st, HealthCheck
     _HAVE_HYPOTHESIS = True
