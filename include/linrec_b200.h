@@ -63,7 +63,15 @@ extern "C" {
  * (linrec/impl/cuda/extension.cpp:20-31): parallel arrays of names and integer values.  Known
  * names are listed by linrec_b200_config_names(); an unknown name or a value without a compiled
  * variant gives LINREC_ERR_NOT_IMPLEMENTED (the reference raises NotImplementedError from
- * dispatch.h:70-71).  n_opts may be 0, in which case the regime selector chooses. */
+ * dispatch.h:70-71).  n_opts may be 0, in which case the regime selector chooses.
+ *
+ * Besides the variant selectors there is one option that changes what is computed:
+ *   logCoeffs = 1   the coefficient tensor holds logarithms (the `logc` argument of the reference's
+ *                   Python operator, linrec/impl/python/ops.py:8-14): the kernels use exp(c), and
+ *                   the backward entry points return the gradient with respect to the logarithm
+ *                   (d_c * exp(c)) in `dc`.  Accepted by linrec_b200_fwd/bwd (all kinds) and
+ *                   linrec_b200_fwd_dim/bwd_dim; the sequence-sharding entry points answer
+ *                   LINREC_ERR_NOT_IMPLEMENTED. */
 typedef struct linrec_opts {
     int n_opts;
     const char* const* names;
