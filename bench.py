@@ -80,6 +80,7 @@ class ClockSampler:
         self.nvml = None
         self.handle = None
         self.thread = None
+        self.t_start = 0.0
 
     def _sample(self):
         n = self.nvml
@@ -107,7 +108,10 @@ class ClockSampler:
 
     def _loop(self):
         while not self.done.is_set():
-            if self.active.is_set():
+            # not in the first period after start(): an NVML query can hold up this process's kernel
+            # launches for its 10-20 ms, and the host is still queueing the timed steps then (seen as
+            # one slow step right at the start of multi-GPU runs); later the queue is full
+            if self.active.is_set() and time.perf_counter() - self.t_start >= self.period:
                 try:
                     self.rows.append(self._sample())
                 except Exception:
@@ -115,6 +119,7 @@ class ClockSampler:
             time.sleep(self.period)
 
     def start(self):
+        self.t_start = time.perf_counter()
         self.active.set()
 
     def sample_now(self):
