@@ -32,7 +32,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -62,25 +61,21 @@ def _peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML from a thread while the timed region runs.
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs on the device.
 
-    NVML is initialised and the first sample is taken BEFORE the timed region: attaching a
-    monitoring client to the GPU (which is what starting `nvidia-smi` does) stalls kernel launches
-    for tens of milliseconds, which must not land inside the measurement.  Even an NVML query now and
-    then costs a step a few milliseconds (seen: one 11 ms step in 200 at a 20 ms period, none without
-    sampling), so the period is 100 ms: a few samples per timed region."""
+    NVML is initialised and a first query is made BEFORE the timed region: attaching a monitoring
+    client to the GPU (which is what starting `nvidia-smi` does) stalls kernel launches for tens of
+    milliseconds, which must not land inside the measurement.  The samples themselves are taken by the
+    benchmarking thread after it has queued the last launch of the region (see sample_while_busy),
+    every 100 ms until the device has finished."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, index: int, period_s: float = float(os.environ.get("LINREC_BENCH_CLOCK_PERIOD", "0.1"))):
         self.index, self.period, self.rows = index, period_s, []
-        self.active = threading.Event()
-        self.done = threading.Event()
         self.nvml = None
         self.handle = None
-        self.thread = None
-        self.t_start = 0.0
 
     def _sample(self):
         n = self.nvml
@@ -102,39 +97,30 @@ class ClockSampler:
             self._sample()
         except Exception:
             self.nvml = None
-            return
-        self.thread = threading.Thread(target=self._loop, daemon=True)
-        self.thread.start()
-
-    def _loop(self):
-        while not self.done.is_set():
-            # not in the first period after start(): an NVML query can hold up this process's kernel
-            # launches for its 10-20 ms, and the host is still queueing the timed steps then (seen as
-            # one slow step right at the start of multi-GPU runs); later the queue is full
-            if self.active.is_set() and time.perf_counter() - self.t_start >= self.period:
-                try:
-                    self.rows.append(self._sample())
-                except Exception:
-                    pass
-            time.sleep(self.period)
 
     def start(self):
-        self.t_start = time.perf_counter()
-        self.active.set()
+        self.rows = []
 
-    def sample_now(self):
-        """One sample from the calling thread.  Called right after the last launch of the timed region
-        has been queued: the host runs ahead of the device, so the GPU is still under that load and
-        no launch is delayed by the query.  Guarantees a sample for regions shorter than the period."""
-        if self.nvml is not None:
+    def sample_while_busy(self, finished):
+        """Samples from the CALLING thread until `finished()` is true; at least once.  Called right
+        after the last launch of the timed region has been queued: the host runs far ahead of the
+        device, so the GPU is under that load for the whole time and no launch can be held up by a
+        query (a sampling thread that woke up while the host was still queueing the timed steps cost
+        single steps several milliseconds)."""
+        if self.nvml is None:
+            return
+        while True:
             try:
                 self.rows.append(self._sample())
             except Exception:
                 pass
+            if finished():
+                return
+            time.sleep(self.period)
+            if finished():
+                return
 
     def stop(self):
-        self.active.clear()
-        self.done.set()
         if self.nvml is None or not self.rows:
             return None
         sm = [r[0] for r in self.rows]
@@ -257,7 +243,7 @@ def run_ours(args):
         ev[i][2].record()
     stop.record()
     if sampler:
-        sampler.sample_now()
+        sampler.sample_while_busy(stop.query)
     barrier()
     launches = C.launch_count() - launches0
     total_ms = start.elapsed_time(stop)
