@@ -101,7 +101,9 @@ LINREC_API int linrec_b200_bwd(int kind, const void* dy, const void* c, const vo
                                void* workspace, size_t workspace_bytes, void* stream);
 
 /* Device-side status word of the calls that used `workspace` since it was last read: synchronises
- * `stream`, reads the word, clears it, and returns LINREC_OK or LINREC_ERR_TIMEOUT.  The bounded waits inside the kernels
+ * `stream`, reads the word, clears it, and returns LINREC_OK or LINREC_ERR_TIMEOUT.  A NULL
+ * `workspace` stands for the built-in buffer of the current device (linrec_b200_fwd_static).
+ * The bounded waits inside the kernels
  * (look-back on a predecessor tile, arrival of a bulk copy) never trap and never spin forever;
  * when one gives up the kernel finishes with wrong numbers and sets this word.
  * No counterpart in the reference (its kernels contain no inter-CTA wait). */
@@ -132,7 +134,7 @@ LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
  *      gathered[(s*numseq + r)*rec + k]   (one all-gather; rec = 2 forward, 4 backward);
  *   3. *_fixup   folds the records of the shards that come earlier in scan order and adds
  *                carry * running product of the coefficients to this shard's results in place.  The
- *                walk along a row stops once the carried value has underflowed below the normal range.
+ *                walk along a row stops once the carried value has underflowed to exactly zero.
  * `reverse` is the flag of the forward pass in all four. */
 LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
@@ -191,7 +193,9 @@ LINREC_API int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void
  * scan (LINREC_KIND_PIPE, selector defaults, same arguments otherwise) but keeps its ticket counter,
  * status word and look-back descriptors in a buffer that is compiled into the library:
  * LINREC_STATIC_SCRATCH_BYTES (1 MiB) of device memory per GPU that loads the library, held until
- * the process exits.  It never calls cudaMalloc, cudaFree or any allocating routine.
+ * the process exits.  It calls no cudaMalloc, no cudaFree and no other allocating routine (the CUDA
+ * calls it makes are cudaGetDevice/cudaSetDevice on the current device, attribute and occupancy
+ * queries, cudaGetSymbolAddress, two 4-byte cudaMemsetAsync on `stream`, and the kernel launch).
  *
  * Limit: the scratch a problem needs must fit the built-in buffer.  Rows that fit one tile need
  * 256 bytes whatever their number; rows longer than a tile need 16 more bytes per tile.  A tile is
@@ -202,14 +206,29 @@ LINREC_API int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void
  *
  * The first call on each device looks up the buffer's device address (once per device, with that
  * device current); make that first call outside any stream capture.  All calls on a device share
- * the one buffer: each call re-initialises the words it needs at its start, the buffer otherwise
- * keeps what the previous call left, and two calls that overlap on the GPU (different streams,
- * different host threads) race on it -- serialise them, or use linrec_b200_fwd with separate
- * workspaces.  This function has no counterpart in the reference. */
+ * the one buffer, which keeps what the previous call left in it.  What has to start from zero is
+ * cleared by every call on `stream` before its kernel: the ticket counter and the count of finished
+ * CTAs (the kernels normally leave both at zero themselves, but a launch that failed, or two launches
+ * that raced, may not have).  The look-back descriptors need no clearing: each is tagged with the
+ * launch epoch kept in the buffer, which every launch advances, and a descriptor of another epoch
+ * reads as empty.  Two calls that overlap on the GPU (different streams, different host threads) race
+ * on the buffer -- serialise them, or use linrec_b200_fwd with separate workspaces.
+ *
+ * The bounded waits of a call through this entry point report to the status word inside the built-in
+ * buffer: read (and clear) it with linrec_b200_status(NULL, stream) on the same device.
+ * This function has no counterpart in the reference. */
 #define LINREC_STATIC_SCRATCH_BYTES (1u << 20)
 LINREC_API int linrec_b200_fwd_static(const void* x, const void* c, void* y,
                                       int64_t numseq, int64_t seqlen, int64_t row_stride,
                                       int reverse, int dtype, void* stream);
+
+/* The built-in buffer of the current device as a workspace for the other entry points: writes its
+ * device address and size (LINREC_STATIC_SCRATCH_BYTES).  For callers that cannot allocate but want
+ * what linrec_b200_fwd_static does not offer (options, the backward pass, the middle-axis scan);
+ * the same sharing rule applies -- one call at a time per device on this buffer -- and the caller
+ * checks the size against linrec_b200_workspace_size itself.  The first call on a device resolves the
+ * address (outside any stream capture).  No counterpart in the reference. */
+LINREC_API int linrec_b200_static_workspace(void** workspace, size_t* bytes);
 
 /* ---- scan along a dimension other than the last ------------------------------------------------------
  * The `dim` argument of the reference's Python operator (linrec/impl/python/ops.py:8-14,43-61); the

@@ -22,6 +22,7 @@ ERR_CUDA = -4
 ERR_TIMEOUT = -5
 ERR_TOO_LONG = -6
 ERR_UNALIGNED = -7
+ERR_SCRATCH_LIMIT = -8
 
 DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
 KIND_REF, KIND_TILE, KIND_PIPE = 0, 1, 2
@@ -85,6 +86,10 @@ def _load() -> ctypes.CDLL:
     lib.linrec_b200_fwd_dim.restype = i32
     lib.linrec_b200_bwd_dim.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, po, vp, sz, vp]
     lib.linrec_b200_bwd_dim.restype = i32
+    lib.linrec_b200_fwd_static.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, vp]
+    lib.linrec_b200_fwd_static.restype = i32
+    lib.linrec_b200_static_workspace.argtypes = [pp, ctypes.POINTER(sz)]
+    lib.linrec_b200_static_workspace.restype = i32
     lib.linrec_b200_launch_count.argtypes = []
     lib.linrec_b200_launch_count.restype = ctypes.c_uint64
     lib.linrec_b200_last_cuda_error.argtypes = []

@@ -61,6 +61,8 @@ struct Options {
     int LC = -1;                 // scan along the middle axis: sequence positions per chunk
     int K = -1;                  // scan along the middle axis: chunks per job (0 = whole column)
     int logc = 0;                // 1: the coefficient tensor holds logarithms
+    int fixed_first = 0;         // measurements only: chained rows also start from fixed round-robin tickets
+    int peer_wait_budget_ms = 30000;   // budget of a wait for ANOTHER RANK (its records, its acknowledgements)
 };
 
 int parse_options(const linrec_opts* o, Options& out)
@@ -85,6 +87,8 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "p2pPhase")) out.p2p_phase = v;
         else if (!strcmp(n, "lazyTickets")) out.lazy = v;
         else if (!strcmp(n, "l2Promotion")) out.l2_promotion = v;
+        else if (!strcmp(n, "fixedFirstTickets")) out.fixed_first = v != 0;
+        else if (!strcmp(n, "peerWaitBudgetMs")) out.peer_wait_budget_ms = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
     }
     return LINREC_OK;
@@ -249,10 +253,12 @@ int device_info(DeviceInfo& out)
     // Tensor maps are encoded through a driver entry point, which needs the device's primary context
     // to be current in the calling thread.  The runtime binds it lazily, and a thread that has only
     // made calls that do not need one (an autograd worker with warm caches) has none yet.
+    // cudaSetDevice on the device that is already selected does exactly that binding (it initialises
+    // the primary context if need be and makes it current) and allocates or frees nothing.
     thread_local int bound_device = -1;
     if (bound_device != dev) {
-        if (cudaFree(nullptr) != cudaSuccess) {
-            note_cuda_error("cudaFree(0)", "could not initialise the device context in this thread");
+        if (cudaSetDevice(dev) != cudaSuccess) {
+            note_cuda_error("cudaSetDevice", "could not bind the device context in this thread");
             cudaGetLastError();
             return LINREC_ERR_CUDA;
         }
@@ -586,6 +592,8 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     // the carry records and fix-up kernels of sequence sharding work on plain coefficients
     if (opt.logc && (carry_out || exchange || open_start)) return LINREC_ERR_NOT_IMPLEMENTED;
     p.wait_budget = (long long)opt.wait_budget_ms * (long long)dev.clock_khz;
+    p.peer_wait_budget = (long long)opt.peer_wait_budget_ms * (long long)dev.clock_khz;
+    p.fixed_first = opt.fixed_first;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     // the gradient scan runs against the direction of the forward pass
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
@@ -685,8 +693,8 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
 }
 
 int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
-                 const void* px, uint32_t px_epoch, uint32_t* status_word, int64_t numseq, int64_t seqlen,
-                 int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_)
+                 const void* px, uint32_t px_epoch, uint32_t* status_word, int peer_wait_budget_ms, int64_t numseq,
+                 int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_)
 {
     const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
     if (!carries && !px && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
@@ -709,7 +717,7 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     fp.px = static_cast<const linrec::PeerTable*>(px);
     fp.px_epoch = px ? px_epoch : 0u;
     fp.status = status_word;
-    fp.wait_budget = 2000LL * dev.clock_khz;
+    fp.wait_budget = (long long)peer_wait_budget_ms * (long long)dev.clock_khz;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     return dtype == LINREC_DTYPE_F32 ? launch_fixup_t<float>(bwd, asc, fp, stream, dev.sm_count)
            : dtype == LINREC_DTYPE_BF16 ? launch_fixup_t<__nv_bfloat16>(bwd, asc, fp, stream, dev.sm_count)
@@ -963,6 +971,39 @@ int launch_col(bool bwd, const void* in0, const void* c, const void* yin, void* 
 }
 }  // namespace
 
+// ---- built-in scratch buffer ------------------------------------------------------------------------
+// The buffer lives in the library's device image, so no call ever has to allocate.  In host code
+// the name below is only a handle for the runtime: the device address has to be asked for with
+// cudaGetSymbolAddress, once per device and with that device current, and it is that address --
+// never the host-side symbol -- that goes to the kernels.
+static __device__ __align__(256) unsigned char g_static_scratch[LINREC_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};   // device address of g_static_scratch, per device ordinal
+
+int static_scratch_address(void** out)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return LINREC_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return LINREC_ERR_CUDA;
+        }
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return LINREC_OK;
+}
+}  // namespace
+
+
 // =================================================================================================
 //  C ABI
 // =================================================================================================
@@ -1001,7 +1042,13 @@ int linrec_b200_bwd(int kind, const void* dy, const void* c, const void* y, void
 
 int linrec_b200_status(const void* workspace, void* stream)
 {
-    if (!workspace) return LINREC_ERR_INVALID_ARG;
+    if (!workspace) {
+        // the built-in buffer of the current device (linrec_b200_fwd_static)
+        void* scratch = nullptr;
+        const int rc = static_scratch_address(&scratch);
+        if (rc != LINREC_OK) return rc;
+        workspace = scratch;
+    }
     uint32_t words[2] = {0, 0};
     if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return LINREC_ERR_CUDA;
     if (cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return LINREC_ERR_CUDA;
@@ -1109,7 +1156,7 @@ int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
 int linrec_b200_fwd_fixup(void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
                           int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream)
 {
-    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, 0u, nullptr, numseq, seqlen, row_stride, reverse, dtype,
+    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype,
                         shard, nshards, stream);
 }
 
@@ -1130,7 +1177,7 @@ int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y, cons
                           int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
                           void* stream)
 {
-    return launch_fixup(true, dx, dc, c, y, records, nullptr, 0u, nullptr, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
+    return launch_fixup(true, dx, dc, c, y, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
                         stream);
 }
 
@@ -1176,8 +1223,8 @@ int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y, int64_t numse
         rc = launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, open, exchange, epoch, numseq, seqlen,
                          row_stride, reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1, numseq,
-                        seqlen, row_stride, reverse, dtype, shard, nshards, stream);
+    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
+                        opt.peer_wait_budget_ms, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
 
 int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* dx, void* dc, int64_t numseq,
@@ -1196,41 +1243,9 @@ int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* 
         rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, nullptr, 0, open, exchange, epoch, numseq, seqlen, row_stride,
                          reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(true, dx, dc, c, y, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1, numseq, seqlen,
-                        row_stride, reverse, dtype, shard, nshards, stream);
+    return launch_fixup(true, dx, dc, c, y, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
+                        opt.peer_wait_budget_ms, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
-
-// ---- forward scan on a built-in scratch buffer ----------------------------------------------------
-// The buffer lives in the library's device image, so no call ever has to allocate.  In host code
-// the name below is only a handle for the runtime: the device address has to be asked for with
-// cudaGetSymbolAddress, once per device and with that device current, and it is that address --
-// never the host-side symbol -- that goes to the kernels.
-static __device__ __align__(256) unsigned char g_static_scratch[LINREC_STATIC_SCRATCH_BYTES];
-
-namespace {
-constexpr int kMaxDevices = 64;
-std::mutex g_static_mutex;
-void* g_static_ptr[kMaxDevices] = {};   // device address of g_static_scratch, per device ordinal
-
-int static_scratch_address(void** out)
-{
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
-    if (dev < 0 || dev >= kMaxDevices) return LINREC_ERR_INVALID_ARG;
-    std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (!g_static_ptr[dev]) {
-        void* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (e != cudaSuccess || !p) {
-            cudaGetLastError();
-            return LINREC_ERR_CUDA;
-        }
-        g_static_ptr[dev] = p;
-    }
-    *out = g_static_ptr[dev];
-    return LINREC_OK;
-}
-}  // namespace
 
 int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq, int64_t seqlen,
                            int64_t row_stride, int reverse, int dtype, void* stream)
@@ -1251,10 +1266,30 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
     void* scratch = nullptr;
     rc = static_scratch_address(&scratch);
     if (rc != LINREC_OK) return rc;
-    // launch_scan rewrites the header words and zeroes the descriptors this call uses, so whatever
-    // an earlier call left in the buffer does not matter
+    // Everybody shares this buffer and nobody can re-zero it from outside, so what a launch needs at
+    // zero is cleared here, on the caller's stream, ahead of the kernel: header word 0 (ticket counter)
+    // and word 3 (CTAs finished).  Word 1 (the sticky status) and word 2 (the epoch) must survive:
+    // resetting the epoch would make the descriptors of earlier launches valid again.  Two 4-byte
+    // memsets, no allocation.
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t), st) != cudaSuccess ||
+        cudaMemsetAsync(static_cast<uint32_t*>(scratch) + 3, 0, sizeof(uint32_t), st) != cudaSuccess) {
+        note_cuda_error("cudaMemsetAsync", cudaGetErrorString(cudaGetLastError()));
+        return LINREC_ERR_CUDA;
+    }
     return launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, 0, nullptr, 0u, numseq, seqlen, row_stride,
                        reverse, dtype, nullptr, scratch, (size_t)LINREC_STATIC_SCRATCH_BYTES, stream);
+}
+
+int linrec_b200_static_workspace(void** workspace, size_t* bytes)
+{
+    if (!workspace || !bytes) return LINREC_ERR_INVALID_ARG;
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != LINREC_OK) return rc;
+    *workspace = scratch;
+    *bytes = (size_t)LINREC_STATIC_SCRATCH_BYTES;
+    return LINREC_OK;
 }
 
 uint64_t linrec_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -244,8 +244,12 @@ __global__ void __launch_bounds__(NT + 32) linrec_column_kernel(const __grid_con
             }
             if (drained) continue;   // only stores are left
             if (cur.q >= qend) {
-                // next job: the first ticket of a CTA is fixed, later ones come from the counter
-                cur.ticket = first ? p.first_ticket + blockIdx.x : p.first_ticket + gridDim.x + atomicAdd(p.header, 1u);
+                // next job: with one job per column nobody waits for anybody and the first ticket of a
+                // CTA is fixed; jobs that wait for their predecessor may only wait for a ticket that a
+                // running CTA holds, so there every ticket comes from the counter
+                const bool fixed = p.gens == 1;
+                cur.ticket = (first && fixed) ? p.first_ticket + blockIdx.x
+                                              : p.first_ticket + (fixed ? gridDim.x : 0u) + atomicAdd(p.header, 1u);
                 first = false;
                 if (cur.ticket >= njobs) {
                     drained = true;

@@ -153,7 +153,8 @@ struct ScanParams {
     int chunks_per_row;  // chain mode
     uint32_t* header;    // workspace header (ticket counter, status word)
     TileDesc* desc;      // chain mode: one descriptor per tile, zeroed before the launch
-    long long wait_budget;  // clock ticks any device-side wait may last
+    long long wait_budget;  // clock ticks a wait inside this GPU may last (bulk copy, look-back)
+    long long peer_wait_budget;   // clock ticks a wait for another rank may last (ranks start at different times)
     float* carry_out;    // optional: per row (P, Y) of the whole row, for sequence sharding
     int carry_stride;    // floats between the records of consecutive rows in carry_out
     int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
@@ -161,6 +162,7 @@ struct ScanParams {
     uint32_t first_ticket;  // diagnostics: added to every ticket (0 in normal use)
     int vec;                // any-alignment kernel: rows allow 16-byte global accesses
     int lazy;               // bulk-copy kernel: draw the next ticket only when the current tile is finished
+    int fixed_first;        // measurements only: chained rows also start from fixed round-robin tickets
     const PeerTable* px;    // sequence sharding: this rank's exchange buffer (records are pushed to all ranks)
     uint32_t px_epoch;      // epoch of this exchange; 0: no peer exchange in this launch (real epochs start at 1)
     int logc;               // 1: `c` holds logarithms; the loaders apply exp, the backward pass returns the

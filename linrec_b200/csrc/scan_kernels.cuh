@@ -181,7 +181,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
                                  : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
 
-    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
@@ -226,10 +226,15 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         if (BWD) ptx::tma_load_3d(in_buf(s, 2), &tm_y, &full[s], 0, c1, c2);
     };
 
-    // Tickets.  The first S+1 tickets of every CTA are fixed round-robin (ticket = round*grid + CTA), so
-    // that neighbouring tickets start on different CTAs at the same time; drawing them from the counter
-    // would hand each CTA S+1 CONSECUTIVE tickets, and with few rows those are consecutive pieces of
-    // one row that would wait for each other across CTAs.  All later tickets come from the counter.
+    // Tickets.  Rows that fit a tile never wait for another tile, so there the first S+1 tickets of a
+    // CTA are fixed round-robin (ticket = round*grid + CTA): no trip to the counter before the first
+    // copy starts.  Chained rows WAIT for their predecessors' descriptors, and a wait may only ever be
+    // for a ticket that a running CTA holds: a fixed ticket can belong to a CTA that is not resident yet
+    // (another kernel shares the GPU) and would then be waited for until the budget runs out.  So in
+    // chain mode every ticket, the first ones included, comes from the counter: a ticket exists only
+    // once a running CTA has drawn it, CTAs work through theirs in increasing order, and the oldest
+    // unfinished ticket is therefore always being worked on.  (`fixed_first` restores the fixed start
+    // for measurements.)  All later tickets come from the counter in both modes.
     //
     // "Lazy" mode (one ring slot; chosen when a handful of very long rows is all there is): a CTA holds
     // ONE ticket at a time and draws the next only when its tile is finished.  Holding tickets ahead is
@@ -238,15 +243,16 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     // it; with one ticket per CTA the oldest unfinished tiles are always the ones being worked on.
     const uint32_t grid = gridDim.x;
     const bool lazy = (S == 1) && p.lazy;
-    const uint32_t dyn_base = p.first_ticket + (lazy ? 1u : (uint32_t)(S + 1)) * grid;
+    const bool fixed = !p.chain || p.fixed_first;
+    const uint32_t dyn_base = p.first_ticket + (fixed ? (lazy ? 1u : (uint32_t)(S + 1)) * grid : 0u);
     uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket held one step ahead
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
-            const uint32_t tk = p.first_ticket + (uint32_t)s * grid + blockIdx.x;
+            const uint32_t tk = fixed ? p.first_ticket + (uint32_t)s * grid + blockIdx.x : dyn_base + atomicAdd(p.header, 1u);
             tile_of_stage[s] = tk;
             if (tk < ntiles) issue(s, tk);
         }
-        next_ticket = p.first_ticket + (uint32_t)S * grid + blockIdx.x;
+        if (!lazy) next_ticket = fixed ? p.first_ticket + (uint32_t)S * grid + blockIdx.x : dyn_base + atomicAdd(p.header, 1u);
     }
     __syncthreads();
 
@@ -275,8 +281,12 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             if (p.logc) pred_c = expf(pred_c);   // boundary constants were stored as logarithms
             succ_y = Storage<ST>::half_of_word(wy, !ASC);
         }
+        // The thread whose run holds the row's first element in scan order.  Scanning downwards, that
+        // element is the last one INSIDE the row: in a ragged last piece it sits at slot valid-1, not at
+        // the end of the tile (whole 128-byte lines make `valid` a multiple of E, so it is the last slot
+        // of thread valid/E - 1).
         const bool zero_first =
-            !p.open_start && (p.chain ? (tc.q == 0 && g.s == 0) : (g.k == 0));
+            !p.open_start && (p.chain ? (tc.q == 0 && (ASC ? g.t == 0 : g.t == tc.valid / E - 1)) : (g.k == 0));
 
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1),
@@ -360,13 +370,17 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     ST* gout0 = reinterpret_cast<ST*>(p.out0);
     ST* gout1 = reinterpret_cast<ST*>(p.out1);
     const int spr = p.chain ? T : p.slots_per_row;
-    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
 
     bool first_round = true;
     for (;;) {
-        // first ticket fixed (one per CTA), later ones from the counter
-        if (tid == 0)
-            ticket_s = first_round ? p.first_ticket + blockIdx.x : p.first_ticket + gridDim.x + atomicAdd(p.header, 1u);
+        // rows that fit a tile: first ticket fixed (one per CTA), later ones from the counter; chained
+        // rows wait for each other, so there every ticket is drawn (see linrec_tma_kernel)
+        if (tid == 0) {
+            const bool fixed = !p.chain || p.fixed_first;
+            ticket_s = (first_round && fixed) ? p.first_ticket + blockIdx.x
+                                              : p.first_ticket + (fixed ? gridDim.x : 0u) + atomicAdd(p.header, 1u);
+        }
         first_round = false;
         __syncthreads();   // also: everybody has finished storing the previous tile
         const uint32_t tk = ticket_s;
@@ -539,7 +553,7 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
     const int spr = p.chain ? T : p.slots_per_row;
     const int cpr = spr / PC;
     const bool with_halo = BWD && p.chain;
-    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.wait_budget, p.header + 1, tid);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
 
     // The chunks a thread copies are the same in every tile: chunk ci = tid + k*NT of the tile.  Its
     // place relative to the tile's first element is worked out once (there is an integer division in
@@ -605,16 +619,20 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
         ptx::cp_async_commit();   // one group per call, empty or not: the wait below counts groups
     };
 
-    // Tickets as in the bulk-copy kernel: the first S+1 of a CTA are fixed round-robin, later ones come
-    // from the counter.  "Lazy" mode (a handful of very long rows): one ticket at a time in ring slot 0,
-    // the next one drawn only when the tile has been scanned.
+    // Tickets as in the bulk-copy kernel: rows that fit a tile start from fixed round-robin tickets,
+    // chained rows draw every ticket from the counter.  "Lazy" mode (a handful of very long rows): one
+    // ticket at a time in ring slot 0, the next one drawn only when the tile has been scanned.
     const uint32_t grid = gridDim.x;
     const bool lazy = p.lazy != 0;
-    const uint32_t dyn_base = p.first_ticket + (lazy ? 1u : (uint32_t)(S + 1)) * grid;
-    uint32_t next_ticket = p.first_ticket + (uint32_t)S * grid + blockIdx.x;   // used by thread 0
-    if (tid == 0)
+    const bool fixed = !p.chain || p.fixed_first;
+    const uint32_t dyn_base = p.first_ticket + (fixed ? (lazy ? 1u : (uint32_t)(S + 1)) * grid : 0u);
+    uint32_t next_ticket = 0;   // used by thread 0
+    if (tid == 0) {
         for (int s = 0; s < S; ++s)
-            tile_of_stage[s] = (lazy && s > 0) ? 0xffffffffu : p.first_ticket + (uint32_t)s * grid + blockIdx.x;
+            tile_of_stage[s] = (lazy && s > 0) ? 0xffffffffu
+                               : fixed ? p.first_ticket + (uint32_t)s * grid + blockIdx.x : dyn_base + atomicAdd(p.header, 1u);
+        if (!lazy) next_ticket = fixed ? p.first_ticket + (uint32_t)S * grid + blockIdx.x : dyn_base + atomicAdd(p.header, 1u);
+    }
     __syncthreads();
     for (int s = 0; s < S; ++s) issue(s, tile_of_stage[s]);
 

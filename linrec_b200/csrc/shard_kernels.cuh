@@ -10,8 +10,8 @@
 //   3. the records of all shards are all-gathered (NCCL) into local memory;
 //   4. a fix-up kernel folds the records of the shards that come earlier in scan order into the
 //      carry v that enters this shard, and adds v * (running product of the coefficients) to the
-//      shard's results.  The walk along a row stops as soon as the running value has become
-//      subnormal: from there on no correction can change a result that is itself above 2^-102.
+//      shard's results.  The walk along a row stops as soon as the running value is exactly zero
+//      (underflow of carry * product): from there on every correction is zero.
 //
 // Carry records are fp32: forward 2 floats per row (P, Y); backward 4 floats (P, Y, c_edge, y_edge).
 #pragma once
@@ -59,11 +59,11 @@ __global__ void linrec_exchange_init_kernel(PeerTable* dst, const PeerTableArg a
 template <bool ASC>
 __device__ __forceinline__ int shard_at(int n, int nshards) { return ASC ? n : nshards - 1 - n; }
 
-// The walk along a row goes on while the carried value is a normal number (or not finite).  Once it
-// is subnormal (< 1.18e-38) every further correction is smaller still, and adding it to a result
-// changes that result only if the result itself is below 2^-102 -- the walk stops there, about 15 %
-// earlier than at exact zero for slowly decaying coefficients.
-__device__ __forceinline__ bool fixup_carry_alive(float v) { return !(fabsf(v) < 1.17549435e-38f); }
+// The walk along a row goes on until the carried value is exactly zero: from there on every correction
+// is zero whatever the coefficients that follow are.  (Stopping earlier, once the value is subnormal,
+// would be safe only for |c| <= 1 from there on -- a later stretch of |c| > 1 lets the correction grow
+// back -- and the operator does not restrict its coefficients.)  NaN keeps walking.
+__device__ __forceinline__ bool fixup_carry_alive(float v) { return !(v == 0.0f); }
 
 // Eight consecutive elements of a row as floats, memory order.  VEC: 16-byte loads (the caller has
 // checked alignment), else element loads.  `m0` may address elements outside [0, seqlen) only when

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import torch
 
-from .ops import _C, dim_eligible, dim_worthwhile, linrec_dim_bwd, linrec_dim_fwd, linrec_pipe
+from .ops import _C, _empty_like_rows, dim_eligible, dim_worthwhile, linrec_dim_bwd, linrec_dim_fwd, linrec_pipe
 
 __all__ = ["linrec_general"]
 
@@ -57,7 +57,7 @@ class _LinrecLogcFn(torch.autograd.Function):
     def backward(ctx, d_outputs):
         logcoeffs, outputs = ctx.saved_tensors
         if d_outputs.stride() != outputs.stride():
-            d_outputs = torch.empty_like(outputs).copy_(d_outputs)
+            d_outputs = _empty_like_rows(outputs).copy_(d_outputs)
         d_inputs, d_log = _C.linrec_pipe_bwd(d_outputs=d_outputs, coeffs=logcoeffs, outputs=outputs,
                                              reverse=ctx.reverse, logCoeffs=1)
         return d_inputs, d_log, None
@@ -77,7 +77,7 @@ def linrec_general(inputs: torch.Tensor, coeffs: torch.Tensor, logc: bool = Fals
         y = _LinrecLogcFn.apply(x, c, reverse) if logc else linrec_pipe(x, c, reverse)
         return y.transpose(d, last)
     if coeffs.stride() != inputs.stride():
-        coeffs = torch.empty_like(inputs).copy_(coeffs)
+        coeffs = _empty_like_rows(inputs).copy_(coeffs)
     if logc:
         return _LinrecLogcFn.apply(inputs, coeffs, reverse)
     return linrec_pipe(inputs, coeffs, reverse)

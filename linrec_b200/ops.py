@@ -96,6 +96,16 @@ def _row_layout(t: torch.Tensor):
     return n, L, row_stride
 
 
+def _empty_like_rows(t: torch.Tensor) -> torch.Tensor:
+    """A result tensor with the LAYOUT of `t`.  `torch.empty_like` keeps the strides of dense tensors
+    only; for rows that are padded (row stride larger than the row) it returns a contiguous tensor,
+    and a kernel that is handed one row stride for all its tensors would then write outside it.  Rows
+    at one uniform stride keep their strides here; anything else gets a contiguous result."""
+    if t.numel() and _row_layout(t) is not None:
+        return torch.empty_strided(t.size(), t.stride(), dtype=t.dtype, device=t.device)
+    return torch.empty(t.size(), dtype=t.dtype, device=t.device)
+
+
 def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
     """One forward or backward call.  `outs` (optional) are caller-provided result tensors with the
     layout of the inputs; without them the results are allocated like the inputs."""
@@ -103,7 +113,7 @@ def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
     ref = ins[0]
     n_out = 2 if bwd else 1
     if outs is None:
-        outs = [torch.empty_like(ref) for _ in range(n_out)]
+        outs = [_empty_like_rows(ref) for _ in range(n_out)]
     else:
         outs = list(outs)
         if len(outs) != n_out:
@@ -264,7 +274,7 @@ def fake_fwd(inputs: torch.Tensor, coeffs: torch.Tensor, reverse: bool = False) 
     assert inputs.device == coeffs.device
     assert inputs.dtype == coeffs.dtype
     assert inputs.stride(-1) == 1
-    return torch.empty_like(inputs)
+    return _empty_like_rows(inputs)
 
 
 def fake_bwd(d_outputs: torch.Tensor, coeffs: torch.Tensor, outputs: torch.Tensor,
@@ -274,7 +284,7 @@ def fake_bwd(d_outputs: torch.Tensor, coeffs: torch.Tensor, outputs: torch.Tenso
     assert d_outputs.device == coeffs.device == outputs.device
     assert d_outputs.dtype == coeffs.dtype == outputs.dtype
     assert d_outputs.stride(-1) == 1
-    return torch.empty_like(d_outputs), torch.empty_like(coeffs)
+    return _empty_like_rows(d_outputs), _empty_like_rows(coeffs)
 
 
 def _register(family: str):
@@ -298,7 +308,7 @@ def _register(family: str):
         # gradient to the layout of the saved tensors (the reference only fixes stride(-1) and
         # then fails its equal-strides check, linrec/impl/cuda/ops.py:55).
         if d_outputs.stride() != coeffs.stride():
-            d_outputs = torch.empty_like(coeffs).copy_(d_outputs)
+            d_outputs = _empty_like_rows(coeffs).copy_(d_outputs)
         d_inputs, d_coeffs = bwd(d_outputs=d_outputs, coeffs=coeffs, outputs=outputs, reverse=ctx.reverse)
         return d_inputs, d_coeffs, None
 

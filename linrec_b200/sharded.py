@@ -10,7 +10,7 @@ sequence sharding  every rank holds the columns [rank*L, (rank+1)*L) of ALL rows
                    all-gathered once (NCCL over NVLink; 8 or 16 bytes per row and rank), and a fused
                    fix-up kernel folds the records of the earlier shards and adds
                    `carry * running product of c` to the local result, stopping along each row as
-                   soon as that correction has underflowed below the normal range (it could no longer change a result).
+                   soon as that correction has underflowed to exactly zero (no later element can be changed by it).
 
 `linrec_seq_sharded(x_shard, c_shard, reverse=False, group=None)` is differentiable; its backward
 does the same three steps with the gradient scan.
@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 from . import _capi
-from .ops import _DTYPES, _check_same, _row_layout, _workspace, linrec_pipe
+from .ops import _DTYPES, _check_same, _empty_like_rows, _row_layout, _workspace, linrec_pipe
 
 __all__ = ["linrec_channel_sharded", "linrec_seq_sharded", "seq_sharded_fwd", "seq_sharded_bwd", "PeerExchange"]
 
@@ -36,10 +36,14 @@ class CudaShardKernels:
 
     @staticmethod
     def _prep(*ts):
+        """Inputs brought to ONE row layout (numseq, seqlen, row_stride).  Every tensor of a call,
+        results included, is addressed with that one row stride, so results are allocated with
+        `_empty_like_rows` (the layout of the inputs): for padded rows a plain `empty_like` returns a
+        contiguous tensor, which the kernels would overrun."""
         _check_same(*ts)
         ts = [t if _row_layout(t) is not None else t.contiguous() for t in ts]
         lay = _row_layout(ts[0])
-        if any(_row_layout(t) != lay for t in ts):
+        if any(_row_layout(t) != lay or t.stride() != ts[0].stride() for t in ts):
             ts = [t.contiguous() for t in ts]
             lay = _row_layout(ts[0])
         return ts, lay
@@ -54,7 +58,7 @@ class CudaShardKernels:
 
     def fwd_carry(self, x, c, reverse, shard, nshards):
         (x, c), (numseq, seqlen, stride) = self._prep(x, c)
-        y = torch.empty_like(x)
+        y = _empty_like_rows(x)
         rec = torch.empty((numseq, 2), dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
             stream, dtype, ws = self._launch_env(x, numseq, seqlen)
@@ -74,7 +78,7 @@ class CudaShardKernels:
 
     def bwd_carry(self, dy, c, y, reverse, shard, nshards):
         (dy, c, y), (numseq, seqlen, stride) = self._prep(dy, c, y)
-        dx, dc = torch.empty_like(dy), torch.empty_like(dy)
+        dx, dc = _empty_like_rows(dy), _empty_like_rows(dy)
         rec = torch.empty((numseq, 4), dtype=torch.float32, device=dy.device)
         with torch.cuda.device(dy.device):
             stream, dtype, ws = self._launch_env(dy, numseq, seqlen)
@@ -127,10 +131,41 @@ class PeerExchange:
         handle.barrier()                   # every rank's buffer is initialised before anyone pushes into it
         self.buffer = buf
         self._keep = handle
+        self._pending = None               # (event, pinned copy of the status word, workspace, stream) of the last call
+        self._pinned = None
 
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch
+
+    # A wait for another rank that ran out of its budget (option peerWaitBudgetMs, 30 s by default)
+    # leaves wrong numbers and a bit in the status word of the workspace.  Reading that word means
+    # waiting for the device, which the hot path must not do; so every call queues a copy of the word
+    # into pinned memory behind its kernels, and the NEXT call looks at that copy if it has arrived.
+    def _watch(self, ws, stream_obj):
+        if self._pinned is None:
+            self._pinned = torch.zeros(2, dtype=torch.int32, pin_memory=True)
+        host = self._pinned[self.epoch & 1:(self.epoch & 1) + 1]    # the word is sticky, so losing an older copy loses nothing
+        host.copy_(ws[4:8].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(stream_obj)
+        self._pending = (ev, host, ws, stream_obj)
+
+    def poll(self, wait: bool = False) -> None:
+        """Raise if an earlier call on this exchange gave up waiting for another rank.  Without `wait`
+        only a result that has already arrived is looked at (no synchronisation)."""
+        if self._pending is None:
+            return
+        ev, host, ws, stream_obj = self._pending
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        self._pending = None
+        if int(host.item()) != 0:
+            with torch.cuda.device(ws.device):
+                rc = _capi.lib.linrec_b200_status(ws.data_ptr(), stream_obj.cuda_stream)   # reads and clears the word
+            _capi.raise_for(rc if rc != 0 else _capi.ERR_TIMEOUT, "linrec_b200 peer exchange")
 
     def _env(self, ref, numseq, seqlen):
         stream = torch.cuda.current_stream(ref.device).cuda_stream
@@ -142,21 +177,24 @@ class PeerExchange:
         (x, c), (numseq, seqlen, stride) = CudaShardKernels._prep(x, c)
         if numseq > self.max_rows:
             raise RuntimeError("linrec: more rows than the peer exchange was created for")
-        y = torch.empty_like(x)
+        self.poll()
+        y = _empty_like_rows(x)
         o, keep = _capi.make_opts(opts or {})
         with torch.cuda.device(x.device):
             stream, dtype, ws = self._env(x, numseq, seqlen)
             rc = _capi.lib.linrec_b200_fwd_seq_p2p(x.data_ptr(), c.data_ptr(), y.data_ptr(), numseq, seqlen, stride,
                                                    int(bool(reverse)), dtype, self.rank, self.world,
                                                    self.buffer.data_ptr(), self.next_epoch(), o, ws.data_ptr(), ws.numel(), stream)
-        _capi.raise_for(rc, "linrec_b200_fwd_seq_p2p")
+            _capi.raise_for(rc, "linrec_b200_fwd_seq_p2p")
+            self._watch(ws, torch.cuda.current_stream(x.device))
         return y
 
     def bwd(self, dy, c, y, reverse, opts=None):
         (dy, c, y), (numseq, seqlen, stride) = CudaShardKernels._prep(dy, c, y)
         if numseq > self.max_rows:
             raise RuntimeError("linrec: more rows than the peer exchange was created for")
-        dx, dc = torch.empty_like(dy), torch.empty_like(dy)
+        self.poll()
+        dx, dc = _empty_like_rows(dy), _empty_like_rows(dy)
         o, keep = _capi.make_opts(opts or {})
         with torch.cuda.device(dy.device):
             stream, dtype, ws = self._env(dy, numseq, seqlen)
@@ -164,7 +202,8 @@ class PeerExchange:
                                                    numseq, seqlen, stride, int(bool(reverse)), dtype, self.rank, self.world,
                                                    self.buffer.data_ptr(), self.next_epoch(), o, ws.data_ptr(),
                                                    ws.numel(), stream)
-        _capi.raise_for(rc, "linrec_b200_bwd_seq_p2p")
+            _capi.raise_for(rc, "linrec_b200_bwd_seq_p2p")
+            self._watch(ws, torch.cuda.current_stream(dy.device))
         return dx, dc
 
 
@@ -218,7 +257,7 @@ class _SeqShardedFn(torch.autograd.Function):
     def backward(ctx, dy):
         c, y = ctx.saved_tensors
         if dy.stride() != c.stride():
-            dy = torch.empty_like(c).copy_(dy)
+            dy = _empty_like_rows(c).copy_(dy)
         dx, dc = seq_sharded_bwd(dy, c, y, ctx.reverse, ctx.group, exchange=ctx.exchange)
         return dx, dc, None, None, None
 

@@ -259,6 +259,30 @@ def test_permuted_batch_dims():
     np.testing.assert_allclose(y.cpu().numpy(), ref, rtol=RTOL, atol=ATOL)
 
 
+def test_autograd_through_padded_rows():
+    """Rows with a stride larger than their length, through autograd: outputs and gradients keep the
+    layout of the inputs (the reference's backward fails its equal-strides check in this situation,
+    linrec/impl/cuda/ops.py:55 with linrec_pipe.cu:98), and nothing is written into the padding."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    rows, L, stride = 6, 1000, 1024
+    x, c, dy = _data((rows, L), clo=0.5)
+    for rev in (False, True):
+        bx = torch.full((rows, stride), -777.0, device=dev)
+        bc = torch.full((rows, stride), -777.0, device=dev)
+        bx[:, :L], bc[:, :L] = x.to(dev), c.to(dev)
+        xd, cd = bx[:, :L].requires_grad_(True), bc[:, :L].requires_grad_(True)
+        y = lb.linrec(xd, cd, reverse=rev)
+        assert y.stride() == (stride, 1)
+        gx, gc = torch.autograd.grad(y, (xd, cd), dy.to(dev))          # a contiguous incoming gradient
+        y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+        dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+        np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
+    lb.check_status()
+
+
 def test_guard_bands_untouched():
     """Outputs are written into the middle of a sentinel-filled allocation through the C ABI; the
     bytes before and after every row block must keep the sentinel (no out-of-row writes)."""
@@ -535,16 +559,57 @@ def test_attrs_and_configs():
     assert b["numRegs"] > 0 and b["residentBlocksPerSM"] >= 1
 
 
-def test_inf_in_first_coefficient_is_ignored():
-    """c at the scan start has no effect, even when it is not finite (linrec_ref.cuh:63)."""
+@pytest.mark.parametrize("bad", [float("inf"), float("nan")], ids=["inf", "nan"])
+@pytest.mark.parametrize("L", [8192 + 32, 3 * 8192 + 64, 2 * 2048 + 64, 5000, 5001, 512, 100], ids=lambda v: f"L{v}")
+@pytest.mark.parametrize("rev", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_nonfinite_first_coefficient_is_ignored(dtype, rev, L, bad):
+    """c at the scan start has no effect, even when it is not finite (linrec_ref.cuh:63): the first
+    output is x itself.  Lengths cover the bulk-copy kernel with a ragged last piece (the scan start
+    of a reversed scan then lies inside the tile, not at its end), the 16-byte cp.async kernel
+    (5000), the plain-load kernel (5001) and rows that share a tile (512, 100)."""
     lb = _ops()
     dev = torch.device("cuda:0")
-    x, c, _ = _data((3, 5000))
-    c[:, 0] = float("inf")
-    y = lb.linrec(x.to(dev), c.to(dev))
+    x, c, dy = _data((3, L), clo=0.5)
+    x, c, dy = x.to(dtype), c.to(dtype), dy.to(dtype)
+    first = L - 1 if rev else 0
+    c[:, first] = bad
+    rtol = RTOL if dtype == torch.float32 else 2.0 ** -7
+    y = lb.linrec(x.to(dev), c.to(dev), reverse=rev)
     c2 = c.clone()
-    c2[:, 0] = 0.0
-    np.testing.assert_allclose(y.cpu().numpy(), oracle.fwd_f32(x.numpy(), c2.numpy()), rtol=RTOL, atol=ATOL)
+    c2[:, first] = 0.0
+    y_ref = oracle.fwd_f32(x.float().numpy(), c2.float().numpy(), reverse=rev)
+    np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=rtol, atol=ATOL)
+    # the backward pass never reads that coefficient either (its shifted coefficients start one later)
+    yd = torch.from_numpy(y_ref).to(dtype).to(dev)
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yd, reverse=rev)
+    dx_ref, dc_ref = oracle.bwd_f32(dy.float().numpy(), c2.float().numpy(), yd.float().cpu().numpy(), reverse=rev)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=rtol, atol=ATOL)
+    np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref, rtol=rtol, atol=2 * ATOL)
+    lb.check_status()
+
+
+@pytest.mark.parametrize("L", [3 * 8192 + 64, 5000, 5001], ids=lambda v: f"L{v}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_nonfinite_first_coefficient_on_the_shard_that_holds_the_scan_start(rev, L):
+    """The carry-emitting forward of sequence sharding: on the shard that holds the scan start the
+    first coefficient is ignored as in the unsharded operator (the other shards use theirs)."""
+    from linrec_b200.sharded import CudaShardKernels
+    dev = torch.device("cuda:0")
+    x, c, _ = _data((4, L), clo=0.5)
+    first = L - 1 if rev else 0
+    c[:, first] = float("inf")
+    nshards = 3
+    shard = nshards - 1 if rev else 0
+    y, rec = CudaShardKernels().fwd_carry(x.to(dev), c.to(dev), rev, shard, nshards)
+    c2 = c.clone()
+    c2[:, first] = 0.0
+    y_ref = oracle.fwd_f32(x.numpy(), c2.numpy(), reverse=rev)
+    np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+    last = 0 if rev else L - 1
+    np.testing.assert_allclose(rec[:, 1].cpu().numpy(), y_ref[:, last], rtol=RTOL, atol=ATOL)
+    assert float(rec[:, 0].abs().max()) == 0.0     # the product over the shard contains the ignored factor as 0
+    _ops().check_status()
 
 
 def test_call_from_a_fresh_host_thread():

@@ -143,3 +143,30 @@ def test_channel_sharding_is_the_plain_operator():
     import inspect
     assert "linrec_pipe(inputs, coeffs, reverse)" in inspect.getsource(sharded.linrec_channel_sharded)
     assert linrec_b200.linrec is linrec_b200.linrec_pipe
+
+
+def test_results_follow_the_row_layout_of_padded_inputs(monkeypatch):
+    """Every tensor of a sharded call is addressed with ONE row stride.  Inputs whose rows are padded
+    (row stride larger than the row) keep their layout, so the results must be allocated with that
+    layout too; a contiguous result would be overrun by a kernel that steps from row to row with the
+    inputs' stride.  Checked on CPU tensors with the CUDA-only precondition switched off."""
+    from linrec_b200 import ops, sharded
+    monkeypatch.setattr(sharded, "_check_same", lambda *ts: None)
+    base = torch.zeros(5, 300)
+    x, c = base[:, :256], torch.ones(5, 300)[:, :256]
+    assert x.stride() == (300, 1) and torch.empty_like(x).stride() == (256, 1)   # what went wrong before
+    (xp, cp), (numseq, seqlen, stride) = sharded.CudaShardKernels._prep(x, c)
+    assert (numseq, seqlen, stride) == (5, 256, 300)
+    for t in (xp, cp, ops._empty_like_rows(xp)):
+        assert ops._row_layout(t) == (5, 256, 300)
+    # batch dimensions in front of padded rows
+    x3 = torch.zeros(2, 3, 40)[:, :, :32]
+    out = ops._empty_like_rows(x3)
+    assert out.stride() == x3.stride() and ops._row_layout(out) == (6, 32, 40)
+    # no uniform row stride (a permuted batch): inputs are made contiguous, and so is the result
+    xp = torch.zeros(4, 6, 8).permute(1, 0, 2)
+    (a, b), lay = sharded.CudaShardKernels._prep(xp, xp.clone(memory_format=torch.preserve_format))
+    assert lay == (24, 8, 8) and a.is_contiguous() and ops._empty_like_rows(a).is_contiguous()
+    # inputs with different (individually valid) strides end up with one layout
+    (a, b), lay = sharded.CudaShardKernels._prep(x, torch.zeros(5, 256))
+    assert lay == (5, 256, 256) and a.stride() == b.stride()

@@ -142,6 +142,74 @@ def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
         np.testing.assert_allclose(cat(dcs), dc_ref, rtol=RTOL, atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
 
 
+@pytest.mark.parametrize("rev", [False, True])
+def test_padded_rows_stay_inside_their_allocation(rev):
+    """Inputs whose rows are padded (row stride 300, row length 256): the sharded entry points must
+    allocate their results with the same layout and leave the padding and everything around it alone.
+    The padding of the inputs is poisoned with NaN, so a kernel that read it would show."""
+    from linrec_b200.sharded import CudaShardKernels
+    k = CudaShardKernels()
+    dev = torch.device("cuda:0")
+    rows, L, stride, G = 5, 2 * 256, 300, 2
+    x, c, dy = _data((rows, L), 0.5, seed=21)
+    Ls = L // G
+
+    def padded(t):
+        buf = torch.full((rows, stride), float("nan"), device=dev)
+        buf[:, :Ls] = t.to(dev)
+        return buf[:, :Ls]
+
+    xs, cs, dys = ([padded(t[:, s * Ls:(s + 1) * Ls]) for s in range(G)] for t in (x, c, dy))
+    ys, recs = zip(*[k.fwd_carry(xs[s], cs[s], rev, s, G) for s in range(G)])
+    for y in ys:
+        assert y.stride() == (stride, 1) and y.untyped_storage().nbytes() >= ((rows - 1) * stride + Ls) * 4
+    gathered = torch.stack(recs).contiguous()
+    for s in range(G):
+        k.fwd_fixup(ys[s], cs[s], gathered, rev, s, G)
+    y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+    np.testing.assert_allclose(torch.cat([t.cpu() for t in ys], dim=1).numpy(), y_ref, rtol=RTOL, atol=ATOL)
+    yg = [padded(torch.from_numpy(y_ref[:, s * Ls:(s + 1) * Ls])) for s in range(G)]
+    outs = [k.bwd_carry(dys[s], cs[s], yg[s], rev, s, G) for s in range(G)]
+    gathered = torch.stack([o[2] for o in outs]).contiguous()
+    for s in range(G):
+        assert outs[s][0].stride() == (stride, 1) and outs[s][1].stride() == (stride, 1)
+        k.bwd_fixup(outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
+    dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+    np.testing.assert_allclose(torch.cat([o[0].cpu() for o in outs], dim=1).numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(torch.cat([o[1].cpu() for o in outs], dim=1).numpy(), dc_ref, rtol=RTOL,
+                               atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+    import linrec_b200
+    linrec_b200.check_status()
+
+
+def test_wait_for_a_peer_gives_up_with_status():
+    """The fix-up phase of the peer-store path is run for shard 1 without anybody ever pushing shard
+    0's records: its bounded waits (option peerWaitBudgetMs, 20 ms here) must run out by themselves,
+    set the status word of the workspace and leave the context usable."""
+    import ctypes
+    from linrec_b200 import _capi
+    dev = torch.device("cuda:0")
+    rows, Ls, G = 3, 4096, 2
+    nbytes = _capi.lib.linrec_b200_exchange_size(rows, G)
+    bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(G)]
+    ptrs = (ctypes.c_void_p * G)(*[b.data_ptr() for b in bufs])
+    stream = torch.cuda.current_stream().cuda_stream
+    for s in range(G):
+        assert _capi.lib.linrec_b200_exchange_init(bufs[s].data_ptr(), ptrs, s, G, rows, stream) == 0
+    ws = torch.zeros(_capi.lib.linrec_b200_workspace_size(rows, Ls, 0), dtype=torch.uint8, device=dev)
+    x = torch.ones(rows, Ls, device=dev)
+    y = torch.zeros_like(x)
+    o, keep = _capi.make_opts({"p2pPhase": 2, "peerWaitBudgetMs": 20})
+    rc = _capi.lib.linrec_b200_fwd_seq_p2p(x.data_ptr(), x.data_ptr(), y.data_ptr(), rows, Ls, Ls, 0, 0, 1, G,
+                                           bufs[1].data_ptr(), 1, o, ws.data_ptr(), ws.numel(), stream)
+    assert rc == 0, _capi.strerror(rc)
+    assert _capi.lib.linrec_b200_status(ws.data_ptr(), stream) == _capi.ERR_TIMEOUT
+    assert _capi.lib.linrec_b200_status(ws.data_ptr(), stream) == 0
+    import linrec_b200
+    assert torch.isfinite(linrec_b200.linrec(x, x * 0.5)).all()
+    linrec_b200.check_status()
+
+
 def _nccl_worker(rank, world, port, tmp):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -152,10 +220,11 @@ def _nccl_worker(rank, world, port, tmp):
     try:
         import linrec_b200
         from linrec_b200.sharded import PeerExchange, linrec_seq_sharded
-        rows, L = 12, world * 3 * 4096
+        rows, L = 1024, world * 3 * 4096
         exchange = PeerExchange(rows)
         Ls = L // world
         x, c, dy = _data((rows, L), 0.9, seed=77)
+        c[rows // 2:] = 0.999 + 0.001 * c[rows // 2:]        # half of the rows decay slowly: carries cross whole shards
         sl = slice(rank * Ls, (rank + 1) * Ls)
         for rev in (False, True):
             xf, cf = x.to(dev).requires_grad_(True), c.to(dev).requires_grad_(True)
@@ -165,18 +234,28 @@ def _nccl_worker(rank, world, port, tmp):
             cs = c[:, sl].contiguous().to(dev).requires_grad_(True)
             ys = linrec_seq_sharded(xs, cs, reverse=rev)
             gx, gc = torch.autograd.grad(ys, (xs, cs), dy[:, sl].contiguous().to(dev))
-            torch.testing.assert_close(ys, y_full[:, sl], rtol=RTOL, atol=ATOL)
-            torch.testing.assert_close(gx, gx_full[:, sl], rtol=RTOL, atol=ATOL)
-            torch.testing.assert_close(gc, gc_full[:, sl], rtol=RTOL, atol=4 * ATOL)
+            h = rows // 2
+            # slowly decaying rows reach |y| ~ 30: two valid fp32 evaluation orders differ by a few ulp of
+            # that near zero crossings, so their absolute tolerance is scaled by the size of the values
+            ymax = max(1.0, float(y_full[h:].abs().max()))
+            gmax = max(1.0, float(gx_full[h:].abs().max()))
+
+            def close(got, want, scale=1.0):
+                torch.testing.assert_close(got[:h], want[:h], rtol=RTOL, atol=4 * ATOL)
+                torch.testing.assert_close(got[h:], want[h:], rtol=RTOL, atol=ATOL * scale)
+
+            close(ys, y_full[:, sl], ymax)
+            close(gx, gx_full[:, sl], gmax)
+            close(gc, gc_full[:, sl], 4 * ymax * gmax)
             # the same through peer stores instead of the all-gather (several exchanges in a row)
             for _ in range(3):
                 xs2 = xs.detach().clone().requires_grad_(True)
                 cs2 = cs.detach().clone().requires_grad_(True)
                 ys2 = linrec_seq_sharded(xs2, cs2, reverse=rev, exchange=exchange)
                 gx2, gc2 = torch.autograd.grad(ys2, (xs2, cs2), dy[:, sl].contiguous().to(dev))
-                torch.testing.assert_close(ys2, y_full[:, sl], rtol=RTOL, atol=ATOL)
-                torch.testing.assert_close(gx2, gx_full[:, sl], rtol=RTOL, atol=ATOL)
-                torch.testing.assert_close(gc2, gc_full[:, sl], rtol=RTOL, atol=4 * ATOL)
+                # same kernels, same records: bit-identical to the all-gather path
+                assert torch.equal(ys2, ys) and torch.equal(gx2, gx) and torch.equal(gc2, gc)
+        exchange.poll(wait=True)
         linrec_b200.check_status()
         open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
     finally:
@@ -184,7 +263,7 @@ def _nccl_worker(rank, world, port, tmp):
 
 
 def test_real_ranks_over_nccl(tmp_path):
-    world = min(torch.cuda.device_count(), 4)
+    world = torch.cuda.device_count()
     if world < 2:
         pytest.skip("needs at least two GPUs")
     import torch.multiprocessing as mp
