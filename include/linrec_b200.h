@@ -43,10 +43,13 @@ extern "C" {
 #define LINREC_ERR_UNALIGNED       (-7)  /* bulk-copy path forced on pointers/strides it cannot take */
 #define LINREC_ERR_SCRATCH_LIMIT   (-8)  /* problem needs more scratch than the built-in buffer has  */
 
-/* ---- element storage types (arithmetic is always fp32) -------------------------------------- */
+/* ---- element storage types (arithmetic is fp32, except for LINREC_DTYPE_F64) ----------------- */
 #define LINREC_DTYPE_F32   0
 #define LINREC_DTYPE_BF16  1
 #define LINREC_DTYPE_F16   2
+#define LINREC_DTYPE_F64   3   /* fp64 storage AND arithmetic; LINREC_KIND_REF only (the type dispatch the
+                                  reference leaves open, linrec/impl/cuda/linrec_pipe.cu:22); other kinds
+                                  and the sharding entry points answer LINREC_ERR_NOT_IMPLEMENTED */
 
 /* ---- which family of kernels a call may use --------------------------------------------------
  * The reference exposes three operator families with one signature

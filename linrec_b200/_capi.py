@@ -24,7 +24,7 @@ ERR_TOO_LONG = -6
 ERR_UNALIGNED = -7
 ERR_SCRATCH_LIMIT = -8
 
-DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
+DTYPE_F32, DTYPE_BF16, DTYPE_F16, DTYPE_F64 = 0, 1, 2, 3
 KIND_REF, KIND_TILE, KIND_PIPE = 0, 1, 2
 
 

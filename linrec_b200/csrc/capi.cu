@@ -548,11 +548,12 @@ size_t workspace_need(const Plan& pl)
 
 int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seqlen, int64_t row_stride, int dtype)
 {
-    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16 && dtype != LINREC_DTYPE_F16) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (dtype != LINREC_DTYPE_F32 && dtype != LINREC_DTYPE_BF16 && dtype != LINREC_DTYPE_F16 && dtype != LINREC_DTYPE_F64)
+        return LINREC_ERR_NOT_IMPLEMENTED;
     if (numseq < 0 || seqlen < 0) return LINREC_ERR_INVALID_ARG;
     if (numseq == 0 || seqlen == 0) return LINREC_OK;
     if (row_stride < seqlen) return LINREC_ERR_INVALID_ARG;
-    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    const int sz = dtype == LINREC_DTYPE_F64 ? 8 : dtype == LINREC_DTYPE_F32 ? 4 : 2;
     for (int i = 0; i < nptrs; ++i) {
         if (!ptrs[i]) return LINREC_ERR_INVALID_ARG;
         if (reinterpret_cast<uintptr_t>(ptrs[i]) % sz != 0) return LINREC_ERR_INVALID_ARG;
@@ -598,11 +599,16 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     // the gradient scan runs against the direction of the forward pass
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
 
+    // double precision: the sequential operator only (fp64 storage and arithmetic)
+    if (dtype == LINREC_DTYPE_F64 && (kind != LINREC_KIND_REF || carry_out || exchange || open_start)) return LINREC_ERR_NOT_IMPLEMENTED;
     if (kind == LINREC_KIND_REF) {
         if (carry_out) return LINREC_ERR_NOT_IMPLEMENTED;
-        const int threads = 128;
+        const int threads = dtype == LINREC_DTYPE_F64 ? 32 : 128;   // fp64 is the checker: spread few rows over many SMs
         const unsigned blocks = (unsigned)ceil_div(numseq, threads);
-        if (di == 0) {
+        if (dtype == LINREC_DTYPE_F64) {
+            if (bwd) linrec::linrec_seq_f64_kernel<true><<<blocks, threads, 0, stream>>>(p, reverse);
+            else     linrec::linrec_seq_f64_kernel<false><<<blocks, threads, 0, stream>>>(p, reverse);
+        } else if (di == 0) {
             if (bwd) linrec::linrec_seq_kernel<float, true><<<blocks, threads, 0, stream>>>(p, reverse);
             else     linrec::linrec_seq_kernel<float, false><<<blocks, threads, 0, stream>>>(p, reverse);
         } else if (di == 1) {
@@ -698,6 +704,7 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
 {
     const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
     if (!carries && !px && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
+    if (dtype == LINREC_DTYPE_F64) return LINREC_ERR_NOT_IMPLEMENTED;
     int rc = check_common(ptrs, 2, numseq, seqlen, row_stride, dtype);
     if (rc != LINREC_OK) return rc;
     if (bwd && (!out1 || !yin) && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
@@ -1251,6 +1258,7 @@ int linrec_b200_fwd_static(const void* x, const void* c, void* y, int64_t numseq
                            int64_t row_stride, int reverse, int dtype, void* stream)
 {
     const void* ptrs[3] = {x, c, y};
+    if (dtype == LINREC_DTYPE_F64) return LINREC_ERR_NOT_IMPLEMENTED;
     int rc = check_common(ptrs, 3, numseq, seqlen, row_stride, dtype);
     if (rc != LINREC_OK) return rc;
     if (numseq == 0 || seqlen == 0) return LINREC_OK;

@@ -755,5 +755,48 @@ __global__ void linrec_seq_kernel(const ScanParams p, int reverse)
 }
 
 
+// The same walk in double precision: fp64 storage AND arithmetic (the type dispatch the reference
+// leaves as a TODO, linrec/impl/cuda/linrec_pipe.cu:22).  Besides being an operator in its own right
+// it is the GPU-side "exact" evaluation that fp32 results are judged against where two valid fp32
+// evaluation orders already differ by more than the nominal tolerance.
+template <bool BWD>
+__global__ void linrec_seq_f64_kernel(const ScanParams p, int reverse)
+{
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= p.numseq) return;
+    const long long L = p.seqlen;
+    const long long rb = r * p.row_stride;
+    const double* in0 = reinterpret_cast<const double*>(p.in0) + rb;
+    const double* c = reinterpret_cast<const double*>(p.c) + rb;
+    double* out0 = reinterpret_cast<double*>(p.out0) + rb;
+    if (!BWD) {
+        const bool asc = !reverse;
+        double v = 0.0;
+        for (long long n = 0; n < L; ++n) {
+            const long long i = asc ? n : L - 1 - n;
+            double ci = c[i];
+            if (p.logc) ci = exp(ci);
+            v = (n == 0) ? in0[i] : fma(v, ci, in0[i]);
+            out0[i] = v;
+        }
+    } else {
+        const double* y = reinterpret_cast<const double*>(p.yin) + rb;
+        double* out1 = reinterpret_cast<double*>(p.out1) + rb;
+        const bool asc = reverse != 0;   // the gradient scan runs against the forward direction
+        double v = 0.0;
+        for (long long n = 0; n < L; ++n) {
+            const long long i = asc ? n : L - 1 - n;
+            const long long ip = asc ? i - 1 : i + 1;   // scan predecessor
+            const long long is = asc ? i + 1 : i - 1;   // scan successor
+            double cp = (n == 0) ? 0.0 : c[ip];
+            if (p.logc && n > 0) cp = exp(cp);
+            v = (n == 0) ? in0[i] : fma(v, cp, in0[i]);
+            out0[i] = v;
+            double ys = (n == L - 1) ? 0.0 : y[is];
+            if (p.logc) ys *= exp(c[i]);
+            out1[i] = v * ys;
+        }
+    }
+}
 
 }  // namespace linrec

@@ -24,7 +24,8 @@ from . import _capi
 
 __all__ = ["linrec_ref", "linrec_tile", "linrec_pipe"]
 
-_DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16, torch.float16: _capi.DTYPE_F16}
+_DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16, torch.float16: _capi.DTYPE_F16,
+           torch.float64: _capi.DTYPE_F64}   # float64: the sequential family (linrec_ref) only
 _CHECK_EVERY_CALL = os.environ.get("LINREC_B200_CHECK", "0") not in ("0", "")
 
 # ---- workspace cache: one scratch buffer per (device, stream) --------------------------------------
@@ -71,7 +72,7 @@ def _check_same(*ts: torch.Tensor) -> None:
     if not all(t.is_cuda for t in ts):
         raise RuntimeError("linrec: tensors must be CUDA tensors (there is no CPU implementation)")
     if a.dtype not in _DTYPES:
-        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16, float16)")
+        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16, float16; float64 for linrec_ref)")
     if a.dim() == 0:
         raise RuntimeError("linrec: need at least one dimension")
     if a.numel() > 0 and a.stride(-1) != 1:

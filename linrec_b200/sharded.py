@@ -56,9 +56,20 @@ class CudaShardKernels:
         ws = _workspace(ref.device, stream, need)
         return stream, dtype, ws
 
-    def fwd_carry(self, x, c, reverse, shard, nshards):
+    @staticmethod
+    def _results(ref, out, n):
+        """`n` result tensors with the layout of `ref`: the caller's (`out`) if they have it, else new ones."""
+        if out is None:
+            return [_empty_like_rows(ref) for _ in range(n)]
+        out = list(out) if isinstance(out, (tuple, list)) else [out]
+        if len(out) != n or any(o.shape != ref.shape or o.stride() != ref.stride() or o.dtype != ref.dtype or
+                                o.device != ref.device for o in out):
+            raise RuntimeError("linrec: result tensors must have the shape, strides, dtype and device of the inputs")
+        return out
+
+    def fwd_carry(self, x, c, reverse, shard, nshards, out=None):
         (x, c), (numseq, seqlen, stride) = self._prep(x, c)
-        y = _empty_like_rows(x)
+        (y,) = self._results(x, out, 1)
         rec = torch.empty((numseq, 2), dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
             stream, dtype, ws = self._launch_env(x, numseq, seqlen)
@@ -76,9 +87,9 @@ class CudaShardKernels:
                                                  int(bool(reverse)), _DTYPES[y.dtype], shard, nshards, stream)
         _capi.raise_for(rc, "linrec_b200_fwd_fixup")
 
-    def bwd_carry(self, dy, c, y, reverse, shard, nshards):
+    def bwd_carry(self, dy, c, y, reverse, shard, nshards, out=None):
         (dy, c, y), (numseq, seqlen, stride) = self._prep(dy, c, y)
-        dx, dc = _empty_like_rows(dy), _empty_like_rows(dy)
+        dx, dc = self._results(dy, out, 2)
         rec = torch.empty((numseq, 4), dtype=torch.float32, device=dy.device)
         with torch.cuda.device(dy.device):
             stream, dtype, ws = self._launch_env(dy, numseq, seqlen)
@@ -173,12 +184,12 @@ class PeerExchange:
         ws = _workspace(ref.device, stream, _capi.lib.linrec_b200_workspace_size(numseq, seqlen, dtype))
         return stream, dtype, ws
 
-    def fwd(self, x, c, reverse, opts=None):
+    def fwd(self, x, c, reverse, opts=None, out=None):
         (x, c), (numseq, seqlen, stride) = CudaShardKernels._prep(x, c)
         if numseq > self.max_rows:
             raise RuntimeError("linrec: more rows than the peer exchange was created for")
         self.poll()
-        y = _empty_like_rows(x)
+        (y,) = CudaShardKernels._results(x, out, 1)
         o, keep = _capi.make_opts(opts or {})
         with torch.cuda.device(x.device):
             stream, dtype, ws = self._env(x, numseq, seqlen)
@@ -189,12 +200,12 @@ class PeerExchange:
             self._watch(ws, torch.cuda.current_stream(x.device))
         return y
 
-    def bwd(self, dy, c, y, reverse, opts=None):
+    def bwd(self, dy, c, y, reverse, opts=None, out=None):
         (dy, c, y), (numseq, seqlen, stride) = CudaShardKernels._prep(dy, c, y)
         if numseq > self.max_rows:
             raise RuntimeError("linrec: more rows than the peer exchange was created for")
         self.poll()
-        dx, dc = _empty_like_rows(dy), _empty_like_rows(dy)
+        dx, dc = CudaShardKernels._results(dy, out, 2)
         o, keep = _capi.make_opts(opts or {})
         with torch.cuda.device(dy.device):
             stream, dtype, ws = self._env(dy, numseq, seqlen)
@@ -216,15 +227,17 @@ def _gather(records: torch.Tensor, group) -> torch.Tensor:
     return out.view((world, rows) + tuple(records.shape[1:]))
 
 
-def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None, exchange=None):
+def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None, exchange=None,
+                    out=None):
     """Forward scan of a row that is split over the ranks of `group` (this rank holds shard `rank`).
     With `exchange` (a PeerExchange) the records travel by peer stores inside the kernels; without it
-    by one all-gather."""
+    by one all-gather.  `out` may hold a preallocated result with the layout of `x`."""
+    kw = {} if out is None else {"out": out}
     if exchange is not None:
-        return exchange.fwd(x, c, reverse)
+        return exchange.fwd(x, c, reverse, **kw)
     k = kernels or _CUDA_KERNELS
     shard, nshards = dist.get_rank(group), dist.get_world_size(group)
-    y, rec = k.fwd_carry(x, c, reverse, shard, nshards)
+    y, rec = k.fwd_carry(x, c, reverse, shard, nshards, **kw)
     if nshards > 1:
         gathered = _gather(rec, group)
         k.fwd_fixup(y, c if c.stride() == y.stride() else c.contiguous(), gathered, reverse, shard, nshards)
@@ -232,13 +245,15 @@ def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, gro
 
 
 def seq_sharded_bwd(dy: torch.Tensor, c: torch.Tensor, y: torch.Tensor, reverse: bool = False, group=None,
-                    kernels=None, exchange=None):
-    """Backward of `seq_sharded_fwd`: (dx, dc) of this rank's shard; `y` is the forward output shard."""
+                    kernels=None, exchange=None, out=None):
+    """Backward of `seq_sharded_fwd`: (dx, dc) of this rank's shard; `y` is the forward output shard.
+    `out` may hold two preallocated results with the layout of `dy`."""
+    kw = {} if out is None else {"out": out}
     if exchange is not None:
-        return exchange.bwd(dy, c, y, reverse)
+        return exchange.bwd(dy, c, y, reverse, **kw)
     k = kernels or _CUDA_KERNELS
     shard, nshards = dist.get_rank(group), dist.get_world_size(group)
-    dx, dc, rec, c2, y2 = k.bwd_carry(dy, c, y, reverse, shard, nshards)
+    dx, dc, rec, c2, y2 = k.bwd_carry(dy, c, y, reverse, shard, nshards, **kw)
     if nshards > 1:
         gathered = _gather(rec, group)
         k.bwd_fixup(dx, dc, c2, y2, gathered, reverse, shard, nshards)

@@ -642,6 +642,33 @@ def test_call_from_a_fresh_host_thread():
     assert out["ok"]
 
 
+# ---- double precision: the sequential family ----------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1, 1), (5, 17), (64, 512), (3, 20000)], ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_float64_sequential_operator(shape, rev):
+    """fp64 storage and arithmetic through `linrec_ref` (the dtype dispatch the reference leaves as a
+    TODO, linrec_pipe.cu:22), against the fp64 oracle at rtol 1e-10; the tiled families refuse fp64."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.9)
+    y = lb._C.linrec_ref_fwd(inputs=x.double().to(dev), coeffs=c.double().to(dev), reverse=rev)
+    assert y.dtype == torch.float64
+    y_ref = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
+    np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=1e-10, atol=1e-12)
+    dx, dc = lb._C.linrec_ref_bwd(d_outputs=dy.double().to(dev), coeffs=c.double().to(dev), outputs=y, reverse=rev)
+    dx_ref, dc_ref = oracle.bwd_f64(dy.numpy(), c.numpy(), y.cpu().numpy(), reverse=rev)
+    np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=1e-10, atol=1e-12)
+    # autograd through the sequential family
+    xd = x.double().to(dev).requires_grad_(True)
+    cd = c.double().to(dev).requires_grad_(True)
+    gx, gc = torch.autograd.grad(lb.linrec_ref(xd, cd, reverse=rev), (xd, cd), dy.double().to(dev))
+    np.testing.assert_allclose(gx.cpu().numpy(), dx_ref, rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=1e-10, atol=1e-12)
+    with pytest.raises(NotImplementedError):
+        lb._C.linrec_pipe_fwd(inputs=x.double().to(dev), coeffs=c.double().to(dev), reverse=rev)
+
+
 # ---- bounded waits -----------------------------------------------------------------------------------
 def test_lookback_wait_gives_up_with_status():
     """Tickets are started past the first piece of every row, so the pieces that run wait for a
