@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(PKG, "liblinrec_b200.so")
 EXE_PATH = os.path.join(PKG, "_build", "linrec_cli")
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xfatbin=-compress-all", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 
 
 def _nvcc() -> str:
@@ -68,14 +68,51 @@ def _all_deps():
     return deps
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
+def _translation_units():
+    """capi.cu (host logic, the small kernels) and the variants_*.cu files the kernel variants are spread
+    over so that they compile side by side."""
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)
+                  if f.endswith(".cu") and (f == "capi.cu" or f.startswith("variants_")))
+
+
+def build_library(force: bool = False, verbose: bool = False, jobs: int | None = None) -> str:
     if not force and not _stale(LIB_PATH, _all_deps()):
         return LIB_PATH
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-shared", "-I", INCLUDE, "-o", LIB_PATH,
-           *_sources("capi.cu")]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    subprocess.run(cmd, check=True)
+    nvcc = _nvcc()
+    objdir = os.path.join(PKG, "_build", "obj")
+    os.makedirs(objdir, exist_ok=True)
+    units = _translation_units()
+    jobs = jobs or max(1, min(len(units), os.cpu_count() or 1))
+    objs, running, failed = [], [], []
+
+    def reap(block_until_below: int):
+        while len(running) > block_until_below:
+            proc, src, log = running.pop(0)
+            rc = proc.wait()
+            log.close()
+            if verbose or rc != 0:
+                with open(log.name) as f:
+                    sys.stderr.write(f.read())
+            if rc != 0:
+                failed.append(src)
+
+    for src in units:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", INCLUDE, "-c", "-o", obj, src]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        log = open(obj + ".log", "w")
+        running.append((subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT), src, log))
+        reap(jobs - 1)
+    reap(0)
+    if failed:
+        raise RuntimeError("nvcc failed on " + ", ".join(os.path.basename(f) for f in failed))
+    subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", LIB_PATH, *objs], check=True)
+    for obj in objs:            # the objects are not reused (staleness is judged for the library as a whole)
+        for f in (obj, obj + ".log"):
+            if os.path.exists(f):
+                os.remove(f)
     _stamp(LIB_PATH, _all_deps())
     return LIB_PATH
 

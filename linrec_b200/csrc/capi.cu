@@ -16,9 +16,8 @@
 #include <vector>
 
 #include "../../include/linrec_b200.h"
-#include "scan_kernels.cuh"
+#include "variants.h"
 #include "shard_kernels.cuh"
-#include "column_kernels.cuh"
 
 namespace {
 
@@ -48,7 +47,8 @@ const char* const kConfigNames[] = {"kElemsPerThread", "kThreadsPerBlock", "kSta
 constexpr int kNumConfigNames = 5;
 // memcode: 0 = plain coalesced loads/stores staged through shared memory (any alignment),
 //          1 = tiled bulk-tensor copies (TMA) through an mbarrier ring (rows of whole 128-byte lines),
-//          2 = 16-byte cp.async through a two-slot ring (16-byte aligned rows of whole 16-byte chunks).
+//          2 = 16-byte cp.async through a two-slot ring (16-byte aligned rows of whole 16-byte chunks),
+//          3 = 4-byte cp.async through a two-slot ring (4-byte aligned rows of whole 4-byte words).
 
 struct Options {
     int E = -1, NT = -1, S = -1, OB = -1, memcode = -1;
@@ -61,6 +61,7 @@ struct Options {
     int LC = -1;                 // scan along the middle axis: sequence positions per chunk
     int K = -1;                  // scan along the middle axis: chunks per job (0 = whole column)
     int logc = 0;                // 1: the coefficient tensor holds logarithms
+    int super_chunks = -1;       // few very long rows: -1 = selector decides, 0/1 = off, N (a power of two) = cut every row into N
     int fixed_first = 0;         // measurements only: chained rows also start from fixed round-robin tickets
     int peer_wait_budget_ms = 30000;   // budget of a wait for ANOTHER RANK (its records, its acknowledgements)
 };
@@ -88,119 +89,24 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "lazyTickets")) out.lazy = v;
         else if (!strcmp(n, "l2Promotion")) out.l2_promotion = v;
         else if (!strcmp(n, "fixedFirstTickets")) out.fixed_first = v != 0;
+        else if (!strcmp(n, "superChunks")) out.super_chunks = v;
         else if (!strcmp(n, "peerWaitBudgetMs")) out.peer_wait_budget_ms = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
     }
     return LINREC_OK;
 }
 
-// ---- compiled variants ---------------------------------------------------------------------------
-using TmaFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                       const CUtensorMap, const ScanParams);
-using GenericFn = void (*)(const ScanParams);
-
-struct TmaVariant {
-    int E, NT, S, OB;
-    size_t smem[3][2];      // [dtype][bwd]
-    TmaFn fn[3][2][2];      // [dtype][bwd][asc]
-};
-
-template <int E, int NT, int S, int OB>
-TmaVariant make_tma_variant()
-{
-    using namespace linrec;
-    TmaVariant v{};
-    v.E = E; v.NT = NT; v.S = S; v.OB = OB;
-    v.smem[0][0] = TmaLayout<float, E, NT, S, OB, false>::kDynSmem;
-    v.smem[0][1] = TmaLayout<float, E, NT, S, OB, true>::kDynSmem;
-    v.smem[1][0] = TmaLayout<__nv_bfloat16, E, NT, S, OB, false>::kDynSmem;
-    v.smem[1][1] = TmaLayout<__nv_bfloat16, E, NT, S, OB, true>::kDynSmem;
-    v.fn[0][0][0] = linrec_tma_kernel<float, E, NT, S, OB, false, false>;
-    v.fn[0][0][1] = linrec_tma_kernel<float, E, NT, S, OB, false, true>;
-    v.fn[0][1][0] = linrec_tma_kernel<float, E, NT, S, OB, true, false>;
-    v.fn[0][1][1] = linrec_tma_kernel<float, E, NT, S, OB, true, true>;
-    v.fn[1][0][0] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, false, false>;
-    v.fn[1][0][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, false, true>;
-    v.fn[1][1][0] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, false>;
-    v.fn[1][1][1] = linrec_tma_kernel<__nv_bfloat16, E, NT, S, OB, true, true>;
-    v.smem[2][0] = TmaLayout<__half, E, NT, S, OB, false>::kDynSmem;
-    v.smem[2][1] = TmaLayout<__half, E, NT, S, OB, true>::kDynSmem;
-    v.fn[2][0][0] = linrec_tma_kernel<__half, E, NT, S, OB, false, false>;
-    v.fn[2][0][1] = linrec_tma_kernel<__half, E, NT, S, OB, false, true>;
-    v.fn[2][1][0] = linrec_tma_kernel<__half, E, NT, S, OB, true, false>;
-    v.fn[2][1][1] = linrec_tma_kernel<__half, E, NT, S, OB, true, true>;
-    return v;
-}
-
-struct GenericVariant {
-    int E, NT, S;
-    size_t smem[3][2];      // [dtype][bwd]: dynamic shared memory (0 for the plain-load kernel)
-    GenericFn fn[3][2][2];  // [dtype][bwd][asc]
-};
-
-template <int E, int NT>
-GenericVariant make_generic_variant()
-{
-    using namespace linrec;
-    GenericVariant v{};
-    v.E = E; v.NT = NT; v.S = 1;
-    v.fn[0][0][0] = linrec_generic_kernel<float, E, NT, false, false>;
-    v.fn[0][0][1] = linrec_generic_kernel<float, E, NT, false, true>;
-    v.fn[0][1][0] = linrec_generic_kernel<float, E, NT, true, false>;
-    v.fn[0][1][1] = linrec_generic_kernel<float, E, NT, true, true>;
-    v.fn[1][0][0] = linrec_generic_kernel<__nv_bfloat16, E, NT, false, false>;
-    v.fn[1][0][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, false, true>;
-    v.fn[1][1][0] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, false>;
-    v.fn[1][1][1] = linrec_generic_kernel<__nv_bfloat16, E, NT, true, true>;
-    v.fn[2][0][0] = linrec_generic_kernel<__half, E, NT, false, false>;
-    v.fn[2][0][1] = linrec_generic_kernel<__half, E, NT, false, true>;
-    v.fn[2][1][0] = linrec_generic_kernel<__half, E, NT, true, false>;
-    v.fn[2][1][1] = linrec_generic_kernel<__half, E, NT, true, true>;
-    return v;
-}
-
-template <int E, int NT, int S>
-GenericVariant make_async_variant()
-{
-    using namespace linrec;
-    GenericVariant v{};
-    v.E = E; v.NT = NT; v.S = S;
-    v.smem[0][0] = AsyncLayout<float, E, NT, S, false>::kDynSmem;
-    v.smem[0][1] = AsyncLayout<float, E, NT, S, true>::kDynSmem;
-    v.smem[1][0] = AsyncLayout<__nv_bfloat16, E, NT, S, false>::kDynSmem;
-    v.smem[1][1] = AsyncLayout<__nv_bfloat16, E, NT, S, true>::kDynSmem;
-    v.smem[2][0] = AsyncLayout<__half, E, NT, S, false>::kDynSmem;
-    v.smem[2][1] = AsyncLayout<__half, E, NT, S, true>::kDynSmem;
-    v.fn[0][0][0] = linrec_async_kernel<float, E, NT, S, false, false>;
-    v.fn[0][0][1] = linrec_async_kernel<float, E, NT, S, false, true>;
-    v.fn[0][1][0] = linrec_async_kernel<float, E, NT, S, true, false>;
-    v.fn[0][1][1] = linrec_async_kernel<float, E, NT, S, true, true>;
-    v.fn[1][0][0] = linrec_async_kernel<__nv_bfloat16, E, NT, S, false, false>;
-    v.fn[1][0][1] = linrec_async_kernel<__nv_bfloat16, E, NT, S, false, true>;
-    v.fn[1][1][0] = linrec_async_kernel<__nv_bfloat16, E, NT, S, true, false>;
-    v.fn[1][1][1] = linrec_async_kernel<__nv_bfloat16, E, NT, S, true, true>;
-    v.fn[2][0][0] = linrec_async_kernel<__half, E, NT, S, false, false>;
-    v.fn[2][0][1] = linrec_async_kernel<__half, E, NT, S, false, true>;
-    v.fn[2][1][0] = linrec_async_kernel<__half, E, NT, S, true, false>;
-    v.fn[2][1][1] = linrec_async_kernel<__half, E, NT, S, true, true>;
-    return v;
-}
+using namespace linrec_variants;
 
 const std::vector<TmaVariant>& tma_variants()
 {
-    static const std::vector<TmaVariant> v = {
-        make_tma_variant<16, 256, 2, 1>(),
-        make_tma_variant<16, 256, 3, 1>(),
-        make_tma_variant<16, 128, 3, 1>(),
-        make_tma_variant<16, 128, 2, 1>(),
-        make_tma_variant<16, 512, 2, 1>(),
-        make_tma_variant<16, 512, 1, 1>(),
-        make_tma_variant<16, 256, 1, 1>(),
-        make_tma_variant<16, 128, 1, 1>(),
-        make_tma_variant<32, 128, 2, 1>(),
-        make_tma_variant<32, 128, 3, 1>(),
-        make_tma_variant<32, 256, 2, 1>(),
-    };
+    static const std::vector<TmaVariant> v = [] {
+        std::vector<TmaVariant> t;
+        add_tma_variants_0(t);
+        add_tma_variants_1(t);
+        add_tma_variants_2(t);
+        return t;
+    }();
     return v;
 }
 
@@ -216,13 +122,22 @@ const std::vector<GenericVariant>& generic_variants()
 // 16-byte cp.async loader, two ring slots: aligned rows whose length is not a multiple of 128 bytes
 const std::vector<GenericVariant>& async_variants()
 {
-    static const std::vector<GenericVariant> v = {
-        make_async_variant<16, 128, 2>(),
-        make_async_variant<16, 128, 3>(),
-        make_async_variant<32, 128, 2>(),
-        make_async_variant<16, 256, 2>(),
-        make_async_variant<16, 512, 2>(),
-    };
+    static const std::vector<GenericVariant> v = [] {
+        std::vector<GenericVariant> t;
+        add_async_variants(t);
+        return t;
+    }();
+    return v;
+}
+
+// 4-byte cp.async loader: rows of whole 4-byte words at 4-byte aligned addresses (any fp32 row)
+const std::vector<GenericVariant>& word_variants()
+{
+    static const std::vector<GenericVariant> v = [] {
+        std::vector<GenericVariant> t;
+        add_word_variants(t);
+        return t;
+    }();
     return v;
 }
 
@@ -264,6 +179,13 @@ int device_info(DeviceInfo& out)
         }
         bound_device = dev;
     }
+    // the calling thread's own copy first: no lock on the path every launch takes
+    thread_local int known_device = -1;
+    thread_local DeviceInfo known;
+    if (known_device == dev) {
+        out = known;
+        return LINREC_OK;
+    }
     std::lock_guard<std::mutex> lock(g_mutex);
     auto it = g_devices.find(dev);
     if (it == g_devices.end()) {
@@ -274,6 +196,8 @@ int device_info(DeviceInfo& out)
         it = g_devices.emplace(dev, d).first;
     }
     out = it->second;
+    known = it->second;
+    known_device = dev;
     return LINREC_OK;
 }
 
@@ -283,8 +207,20 @@ int occupancy(const void* fn, int threads, size_t smem, int& out)
 {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return LINREC_ERR_CUDA;
-    std::lock_guard<std::mutex> lock(g_mutex);
     const KernelKey key{fn, dev};
+    // the calling thread's last few answers first: no lock on the path every launch takes
+    struct Recent {
+        KernelKey key;
+        int n;
+    };
+    thread_local Recent recent[8] = {};
+    thread_local int recent_next = 0;
+    for (const Recent& r : recent)
+        if (r.n > 0 && r.key == key) {
+            out = r.n;
+            return LINREC_OK;
+        }
+    std::lock_guard<std::mutex> lock(g_mutex);
     auto it = g_occupancy.find(key);
     if (it == g_occupancy.end()) {
         if (smem > 48 * 1024) {
@@ -306,6 +242,10 @@ int occupancy(const void* fn, int threads, size_t smem, int& out)
         it = g_occupancy.emplace(key, n).first;
     }
     out = it->second;
+    if (out > 0) {
+        recent[recent_next] = Recent{key, out};
+        recent_next = (recent_next + 1) % 8;
+    }
     return out > 0 ? LINREC_OK : LINREC_ERR_CUDA;
 }
 
@@ -361,16 +301,57 @@ int make_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64
     return LINREC_OK;
 }
 
+// Encoding a tensor map costs about a microsecond and a launch needs five; a training loop calls with
+// the same buffers and shapes over and over.  Each host thread therefore keeps the last few maps it
+// encoded (no lock; a map depends on nothing but the arguments that make up the key).
+struct MapKey {
+    const void* ptr;
+    int64_t numseq, seqlen, row_stride;
+    int dtype, box_lines, box_rows, l2;
+    bool operator==(const MapKey& o) const
+    {
+        return ptr == o.ptr && numseq == o.numseq && seqlen == o.seqlen && row_stride == o.row_stride && dtype == o.dtype &&
+               box_lines == o.box_lines && box_rows == o.box_rows && l2 == o.l2;
+    }
+};
+int cached_map(CUtensorMap* map, const void* ptr, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride,
+               int box_lines, int box_rows, int l2_promotion)
+{
+    constexpr int kSlots = 16;
+    struct Slot {
+        MapKey key;
+        CUtensorMap map;
+        bool used;
+    };
+    thread_local Slot slots[kSlots] = {};
+    thread_local int next = 0;
+    const MapKey key{ptr, numseq, seqlen, row_stride, dtype, box_lines, box_rows, l2_promotion};
+    for (int i = 0; i < kSlots; ++i)
+        if (slots[i].used && slots[i].key == key) {
+            *map = slots[i].map;
+            return LINREC_OK;
+        }
+    const int rc = make_map(map, ptr, dtype, numseq, seqlen, row_stride, box_lines, box_rows, l2_promotion);
+    if (rc != LINREC_OK) return rc;
+    Slot& s = slots[next];
+    next = (next + 1) % kSlots;
+    s.key = key;
+    s.map = *map;
+    s.used = true;
+    return LINREC_OK;
+}
+
 // ---- planning ------------------------------------------------------------------------------------
 struct Plan {
     bool tma = false;
-    bool async_copy = false;
+    bool async_copy = false;   // cp.async ring, 16-byte (memcode 2) or 4-byte (memcode 3) chunks
     const TmaVariant* tv = nullptr;
     const GenericVariant* gv = nullptr;
     int E = 0, NT = 0, T = 0;
     int chain = 0, slots_per_row = 0, rows_per_tile = 1, chunks_per_row = 1;
     long long ntiles = 0;
     bool lazy_default = false;
+    int memcode = 0;
 };
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -395,6 +376,16 @@ bool vec_eligible(int dtype, int64_t seqlen, int64_t row_stride, const void* con
     if ((row_stride * sz) % 16 != 0 || (seqlen * sz) % 16 != 0) return false;
     for (int i = 0; i < nptrs; ++i)
         if (reinterpret_cast<uintptr_t>(ptrs[i]) % 16 != 0) return false;
+    return true;
+}
+
+// 4-byte asynchronous copies: rows of whole 4-byte words at 4-byte aligned addresses
+bool word_eligible(int dtype, int64_t seqlen, int64_t row_stride, const void* const* ptrs, int nptrs)
+{
+    const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+    if ((row_stride * sz) % 4 != 0 || (seqlen * sz) % 4 != 0) return false;
+    for (int i = 0; i < nptrs; ++i)
+        if (reinterpret_cast<uintptr_t>(ptrs[i]) % 4 != 0) return false;
     return true;
 }
 
@@ -429,13 +420,16 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
 {
     const bool can_tma = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, nptrs);
     const bool can_vec = vec_eligible(dtype, seqlen, row_stride, ptrs, nptrs);
+    const bool can_word = word_eligible(dtype, seqlen, row_stride, ptrs, nptrs);
     int memcode = opt.memcode;
-    if (memcode < 0) memcode = can_tma ? 1 : (can_vec ? 2 : 0);
-    if (memcode < 0 || memcode > 2) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (memcode < 0) memcode = can_tma ? 1 : (can_vec ? 2 : (can_word ? 3 : 0));
+    if (memcode < 0 || memcode > 3) return LINREC_ERR_NOT_IMPLEMENTED;
     if (memcode == 1 && !can_tma) return LINREC_ERR_UNALIGNED;
     if (memcode == 2 && !can_vec) return LINREC_ERR_UNALIGNED;
+    if (memcode == 3 && !can_word) return LINREC_ERR_UNALIGNED;
     pl.tma = memcode == 1;
-    pl.async_copy = memcode == 2;
+    pl.async_copy = memcode == 2 || memcode == 3;
+    pl.memcode = memcode;
     const int di = dtype == LINREC_DTYPE_F32 ? 0 : (dtype == LINREC_DTYPE_BF16 ? 1 : 2);
     if (pl.tma) {
         // Defaults of the selector (measured on B200, see the sweep of the standalone harness):
@@ -465,15 +459,21 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             } else {
                 // 2-byte storage moves half the bytes per element, so instruction issue starts to
                 // matter: 32 elements per thread halve the shuffle and barrier cost per element
-                if (short_rows) { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
-                else if (!bwd)  { E = 32; NT = 256; S = 2; OB = 1; }
-                else            { E = 32; NT = 128; S = 2; OB = 1; }
+                // Few long rows: with two or more CTAs per SM there are more tiles being worked on than
+                // there are rows, so a tile's predecessor is usually still in flight and the look-back
+                // waits; one CTA per SM with a 16384-element tile (the bytes of an 8192-element fp32
+                // tile) keeps the predecessor a whole round back.
+                if (short_rows)     { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
+                else if (few_rows)  { E = 32; NT = 512; S = bwd ? 1 : 2; OB = 1; }
+                else if (!bwd)      { E = 32; NT = 256; S = 2; OB = 1; }
+                else                { E = 32; NT = 128; S = 2; OB = 1; }
             }
         }
         const TmaVariant* best = nullptr;
         for (const TmaVariant& v : tma_variants()) {
             if (!((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S) && (OB < 0 || v.OB == OB))) continue;
             if (v.smem[di][bwd] > (size_t)max_smem) continue;
+            if ((size_t)v.E * v.NT * (di == 0 ? 4 : 2) > 256 * 128) continue;   // a copy box holds at most 256 lines of 128 bytes
             if (!pinned && kind == LINREC_KIND_TILE) {
                 // smallest tile that holds the row; among equals the deeper ring
                 if (v.E * v.NT < seqlen) continue;
@@ -502,12 +502,13 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             const bool handful = seqlen > 8192 && numseq < 32;
             pl.lazy_default = handful;
             S = 2;
-            if (handful)       { E = 16; NT = 512; }
-            else if (few_rows) { E = 32; NT = 128; }
+            if (handful)            { E = 16; NT = 512; }
+            else if (memcode == 3)  { E = 16; NT = 128; }   // word copies: the small tile won every sweep
+            else if (few_rows)      { E = 32; NT = 128; }
             else if (di == 0 && seqlen <= 4096) { E = 16; NT = 256; }   // 4-byte rows that fit the 4096-element tile
-            else               { E = 16; NT = 128; }
+            else                    { E = 16; NT = 128; }
         }
-        for (const GenericVariant& v : async_variants()) {
+        for (const GenericVariant& v : (memcode == 2 ? async_variants() : word_variants())) {
             if (!((E < 0 || v.E == E) && (NT < 0 || v.NT == NT) && (S < 0 || v.S == S))) continue;
             if (v.smem[di][bwd] > (size_t)max_smem) continue;
             if (!pinned && kind == LINREC_KIND_TILE) {
@@ -561,11 +562,11 @@ int check_common(const void* const* ptrs, int nptrs, int64_t numseq, int64_t seq
     return LINREC_OK;
 }
 
-// The one launcher behind forward, backward and the carry-emitting forward.
-int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
-                float* carry_out, int carry_stride, int open_start, const void* exchange, uint32_t px_epoch, int64_t numseq, int64_t seqlen, int64_t row_stride,
-                int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
-                void* stream_)
+// The one launcher behind forward, backward and the carry-emitting forward: ONE kernel launch.
+int launch_scan_direct(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
+                       float* carry_out, int carry_stride, int open_start, const void* exchange, uint32_t px_epoch, int64_t numseq, int64_t seqlen, int64_t row_stride,
+                       int reverse, int dtype, const linrec_opts* opts, void* workspace, size_t workspace_bytes,
+                       void* stream_, int super_chunks = 0)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const void* ptrs[5] = {in0, c, out0, bwd ? yin : in0, bwd ? out1 : out0};
@@ -587,6 +588,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     p.carry_out = carry_out;
     p.carry_stride = carry_stride;
     p.open_start = open_start;
+    p.super_chunks = super_chunks;
     p.px = static_cast<const linrec::PeerTable*>(exchange);
     p.px_epoch = exchange ? px_epoch : 0u;
     p.logc = opt.logc;
@@ -657,7 +659,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
         const int box_rows = pl.chain ? 1 : pl.rows_per_tile;
         const void* src[5] = {in0, c, bwd ? yin : c, out0, bwd ? out1 : out0};
         for (int i = 0; i < 5; ++i) {
-            rc = make_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows, opt.l2_promotion);
+            rc = cached_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows, opt.l2_promotion);
             if (rc != LINREC_OK) return rc;
         }
         pl.tv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
@@ -700,7 +702,8 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
 
 int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
                  const void* px, uint32_t px_epoch, uint32_t* status_word, int peer_wait_budget_ms, int64_t numseq,
-                 int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_)
+                 int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_,
+                 int super_chunks = 0)
 {
     const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
     if (!carries && !px && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
@@ -713,7 +716,7 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
     // nothing enters the shard that holds the scan start; with a peer exchange the kernel still runs
     // because it is the one that acknowledges the epoch to the other ranks
-    if (holds_scan_start(asc, shard, nshards) && !bwd && !px) return LINREC_OK;
+    if (holds_scan_start(asc, shard, nshards) && !bwd && !px && super_chunks <= 1) return LINREC_OK;
     DeviceInfo dev;
     rc = device_info(dev);
     if (rc != LINREC_OK) return rc;
@@ -721,6 +724,7 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     fp.out0 = out0; fp.out1 = out1; fp.c = c; fp.yin = yin; fp.carries = carries;
     fp.numseq = numseq; fp.seqlen = seqlen; fp.row_stride = row_stride;
     fp.shard = shard; fp.nshards = nshards; fp.rec = bwd ? 4 : 2;
+    fp.super_chunks = super_chunks;
     fp.px = static_cast<const linrec::PeerTable*>(px);
     fp.px_epoch = px ? px_epoch : 0u;
     fp.status = status_word;
@@ -733,54 +737,87 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
 }  // namespace
 
 
+// ---- few, very long rows: super-chunks ------------------------------------------------------------------
+// With fewer rows than CTAs, consecutive tiles of one row are in flight together and every tile waits
+// for its predecessor: the chain of look-backs, not the memory system, sets the pace (about 3 TB/s).
+// There every real row is cut into V consecutive super-chunks that are scanned as independent rows
+// (all but the first one "open", exactly like the shards of a sequence that is split over GPUs), each
+// leaving a record (P, Y[, edge elements]); a second, short kernel folds the records of the earlier
+// super-chunks of the same row and adds carry * running product to the head of each super-chunk, as far
+// as that carry lives (for decaying coefficients a few thousand elements at most; only coefficients
+// that do not decay at all make it a full second pass).  The records live at the end of the workspace.
+namespace {
+constexpr int64_t kSuperChunkMaxRows = 128;       // regime: fewer rows than this ...
+constexpr int64_t kSuperChunkMinRow = 1 << 17;    // ... each at least this long
+constexpr int64_t kSuperChunkMinLen = 1 << 15;    // a super-chunk is at least this long
+constexpr int64_t kSuperChunkTargetRows = 1024;   // cut until there are about this many independent rows
+constexpr size_t kSuperChunkRecordBytes = 2 * kSuperChunkTargetRows * 16 + 256;
+
+int pick_super_chunks(int kind, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride, const void* const* ptrs,
+                      int nptrs, const Options& opt, bool plain)
+{
+    if (opt.super_chunks == 0 || opt.super_chunks == 1) return 1;
+    // fp32 only: the fix-up adds its correction to a result that has already been rounded to the
+    // storage type, and for 2-byte storage that second rounding shows where the correction cancels
+    // most of the local value
+    if (!plain || kind != LINREC_KIND_PIPE || opt.logc || dtype != LINREC_DTYPE_F32) return 1;
+    if (opt.memcode >= 0 && opt.memcode != 1) return 1;
+    if (numseq <= 0 || seqlen <= 0 || (row_stride != seqlen && numseq != 1)) return 1;
+    int64_t V = 1;
+    if (opt.super_chunks > 1) {
+        V = opt.super_chunks;
+        if (V & (V - 1)) return 1;                 // powers of two only
+        if (numseq * V > 2 * kSuperChunkTargetRows) return 1;
+    } else {
+        if (numseq >= kSuperChunkMaxRows || seqlen < kSuperChunkMinRow) return 1;
+        while (numseq * V < kSuperChunkTargetRows) V <<= 1;
+    }
+    const int64_t line = 128 / (dtype == LINREC_DTYPE_F32 ? 4 : 2);
+    while (V > 1 && (seqlen % V != 0 || seqlen / V < kSuperChunkMinLen || (seqlen / V) % line != 0)) V >>= 1;
+    if (V < 2) return 1;
+    if (!tma_eligible(dtype, numseq * V, seqlen / V, seqlen / V, ptrs, nptrs)) return 1;
+    return (int)V;
+}
+
+int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* yin, void* out0, void* out1,
+                float* carry_out, int carry_stride, int open_start, const void* exchange, uint32_t px_epoch, int64_t numseq,
+                int64_t seqlen, int64_t row_stride, int reverse, int dtype, const linrec_opts* opts, void* workspace,
+                size_t workspace_bytes, void* stream)
+{
+    Options opt;
+    if (parse_options(opts, opt) == LINREC_OK && numseq > 0 && seqlen > 0 && in0 && c && out0 && workspace) {
+        const void* ptrs[5] = {in0, c, out0, bwd ? yin : in0, bwd ? out1 : out0};
+        const bool plain = !carry_out && !exchange && !open_start;
+        const int V = (!bwd || (yin && out1)) ? pick_super_chunks(kind, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, plain) : 1;
+        const size_t rec_bytes = (size_t)round_up(numseq * V * 16, 256);
+        if (V > 1 && workspace_bytes > rec_bytes + linrec::kHeaderBytes) {
+            const size_t main_bytes = (workspace_bytes - rec_bytes) & ~(size_t)255;
+            float* records = reinterpret_cast<float*>(static_cast<char*>(workspace) + main_bytes);
+            const int64_t ns = numseq * V, len = seqlen / V;
+            const int rc = launch_scan_direct(kind, bwd, in0, c, yin, out0, out1, records, bwd ? 4 : 2, 0, nullptr, 0u, ns, len,
+                                              len, reverse, dtype, opts, workspace, main_bytes, stream, V);
+            if (rc == LINREC_OK)
+                return launch_fixup(bwd, out0, out1, c, yin, records, nullptr, 0u, nullptr, 0, ns, len, len, reverse, dtype, 0,
+                                    V, stream, V);
+            if (rc != LINREC_ERR_WORKSPACE) return rc;
+            // the workspace holds the plain scan but not the records as well: scan the rows as they are
+        }
+    }
+    return launch_scan_direct(kind, bwd, in0, c, yin, out0, out1, carry_out, carry_stride, open_start, exchange, px_epoch,
+                              numseq, seqlen, row_stride, reverse, dtype, opts, workspace, workspace_bytes, stream);
+}
+}  // namespace
+
 // ---- scan along the middle axis of (nb, seqlen, nchan) -------------------------------------------------
 namespace {
-using ColFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                       const CUtensorMap, const linrec::ColParams);
-struct ColVariant {
-    int NT, LC, S;
-    size_t smem[3][2];     // [dtype][bwd]
-    ColFn fn[3][2][2];     // [dtype][bwd][asc]; null where the variant does not exist for the type
-};
-
-template <typename ST, int NT, int LC, int S>
-void fill_col_variant(ColVariant& v, int di)
-{
-    using namespace linrec;
-    if constexpr (NT * (4 / (int)sizeof(ST)) <= 256) {
-        v.smem[di][0] = ColLayout<ST, NT, LC, S, false>::kDynSmem;
-        v.smem[di][1] = ColLayout<ST, NT, LC, S, true>::kDynSmem;
-        v.fn[di][0][0] = linrec_column_kernel<ST, NT, LC, S, false, false>;
-        v.fn[di][0][1] = linrec_column_kernel<ST, NT, LC, S, false, true>;
-        v.fn[di][1][0] = linrec_column_kernel<ST, NT, LC, S, true, false>;
-        v.fn[di][1][1] = linrec_column_kernel<ST, NT, LC, S, true, true>;
-    }
-}
-
-template <int NT, int LC, int S>
-ColVariant make_col_variant()
-{
-    ColVariant v{};
-    v.NT = NT; v.LC = LC; v.S = S;
-    fill_col_variant<float, NT, LC, S>(v, 0);
-    fill_col_variant<__nv_bfloat16, NT, LC, S>(v, 1);
-    fill_col_variant<__half, NT, LC, S>(v, 2);
-    return v;
-}
-
 const std::vector<ColVariant>& col_variants()
 {
-    static const std::vector<ColVariant> v = {
-        make_col_variant<128, 32, 3>(),
-        make_col_variant<128, 32, 2>(),
-        make_col_variant<128, 32, 4>(),
-        make_col_variant<64, 64, 3>(),
-        make_col_variant<64, 64, 2>(),
-        make_col_variant<32, 64, 3>(),
-        make_col_variant<32, 64, 2>(),
-        make_col_variant<32, 128, 2>(),
-        make_col_variant<256, 32, 2>(),
-    };
+    static const std::vector<ColVariant> v = [] {
+        std::vector<ColVariant> t;
+        add_col_variants_0(t);
+        add_col_variants_1(t);
+        return t;
+    }();
     return v;
 }
 
@@ -1026,7 +1063,10 @@ size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype)
         for (const TmaVariant& v : tma_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         for (const GenericVariant& v : generic_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         for (const GenericVariant& v : async_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
+        for (const GenericVariant& v : word_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         if (seqlen > tmin) n += (size_t)numseq * (size_t)ceil_div(seqlen, tmin) * sizeof(TileDesc);
+        // few very long rows may be cut into super-chunks: their records and a few more descriptors
+        if (numseq < kSuperChunkMaxRows && seqlen >= kSuperChunkMinRow) n += 2 * kSuperChunkRecordBytes;
     }
     return (size_t)round_up((int64_t)n, 256);
 }
@@ -1101,7 +1141,7 @@ int linrec_b200_attrs(int kind, int fwd, int dtype, const linrec_opts* opts, con
             dyn = pl.tv->smem[di][bwd];
         } else {
             fn = reinterpret_cast<const void*>(pl.gv->fn[di][bwd][1]);
-            E = pl.gv->E; NT = pl.gv->NT; S = pl.gv->S; OB = 0; memcode = pl.async_copy ? 2 : 0;
+            E = pl.gv->E; NT = pl.gv->NT; S = pl.gv->S; OB = 0; memcode = pl.memcode;
             dyn = pl.gv->smem[di][bwd];
         }
     }
@@ -1146,6 +1186,7 @@ int linrec_b200_config_list(int* values, int cap_rows)
     for (const TmaVariant& v : tma_variants()) put(v.E, v.NT, v.S, v.OB, 1);
     for (const GenericVariant& v : generic_variants()) put(v.E, v.NT, 1, 0, 0);
     for (const GenericVariant& v : async_variants()) put(v.E, v.NT, v.S, 0, 2);
+    for (const GenericVariant& v : word_variants()) put(v.E, v.NT, v.S, 0, 3);
     return row;
 }
 

@@ -159,6 +159,9 @@ struct ScanParams {
     int carry_stride;    // floats between the records of consecutive rows in carry_out
     int open_start;      // 1: the rows continue an earlier shard: the first coefficient counts, and a
                          //    coefficient that lies before the shard is taken as 1 (folded in later)
+    int super_chunks;    // > 1 (a power of two; bulk-copy kernel, chained rows only): every real row was cut
+                         //    into this many consecutive "rows" that are scanned independently; all but
+                         //    the one that holds the real row's scan start are open (see open_start)
     uint32_t first_ticket;  // diagnostics: added to every ticket (0 in normal use)
     int vec;                // any-alignment kernel: rows allow 16-byte global accesses
     int lazy;               // bulk-copy kernel: draw the next ticket only when the current tile is finished
@@ -168,6 +171,15 @@ struct ScanParams {
     int logc;               // 1: `c` holds logarithms; the loaders apply exp, the backward pass returns the
                             //    gradient with respect to the logarithm (d_c * c)
 };
+
+// Does `row` continue an earlier piece of its sequence (another GPU's shard, or the preceding
+// super-chunk of the same real row)?
+template <bool ASC>
+__device__ __forceinline__ bool row_is_open(const ScanParams& p, long long row)
+{
+    if (p.super_chunks > 1) return ((int)row & (p.super_chunks - 1)) != (ASC ? 0 : p.super_chunks - 1);
+    return p.open_start != 0;
+}
 
 // Storage helpers are declared further down; the record emitter needs them, so it follows them.
 
@@ -311,7 +323,7 @@ __device__ __forceinline__ void emit_record(const ScanParams& p, long long row, 
 
 // Before a launch pushes records of epoch e it makes sure that every rank has acknowledged epoch
 // e-2, whose slots it is about to overwrite (lanes 0..nranks-1 of the calling warp check one rank each).
-__device__ __noinline__ void wait_for_slot_release(const PeerTable* px, uint32_t px_epoch, long long budget,
+static __device__ __noinline__ void wait_for_slot_release(const PeerTable* px, uint32_t px_epoch, long long budget,
                                                    uint32_t* status, int lane)
 {
     if (lane < px->nranks) {
@@ -640,9 +652,12 @@ __device__ __forceinline__ Pair desc_pair(const uint4& v) { return Pair{__uint_a
 
 // Phase 2b, chain mode, run by ONE warp: decoupled look-back over the predecessor tiles of the
 // same row.  Tile (row r, scan piece q) has ticket q*numseq + r, so its predecessor is `numseq`
-// tickets back.  Returns (on every lane) the exclusive prefix of this tile.  Each poll is bounded
-// by p.wait_budget clock ticks; on expiry the status word is flagged and the missing predecessor
-// is treated as an inclusive identity so that the walk terminates.
+// tickets back.  Returns (on every lane) the exclusive prefix of this tile.  One step of the walk
+// looks at 32 predecessors, one per lane (nearest = lane 0), and folds them up to the nearest one
+// that holds an inclusive value.  (Requesting the descriptors of several windows per round trip was
+// measured and did not pay: where the walk is long, the tiles it waits for are still being scanned.)
+// Each poll is bounded by p.wait_budget clock ticks; on expiry the status word is flagged and the
+// missing predecessor is treated as an inclusive identity so that the walk terminates.
 __device__ __forceinline__ Pair lookback(const ScanParams& p, uint32_t epoch, long long ticket, int q, int lane)
 {
     Pair acc = pair_identity();

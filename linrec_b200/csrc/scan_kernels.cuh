@@ -14,6 +14,8 @@
 //
 // Replaces linrec/impl/cuda/linrec_pipe.cuh:8-143 and linrec/impl/cuda/linrec_tile.cuh:158-249.
 #pragma once
+#include <type_traits>
+
 #include "scan_core.cuh"
 
 namespace linrec {
@@ -174,6 +176,11 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
 
     const Geometry g = make_geometry<E, NT, ASC>(p);
     const int tid = g.t;
+    // The thread that issues every bulk copy, draws the tickets and owns the bulk-store groups.  It
+    // sits in the warp that comes FIRST in scan order, because the warp that comes last links the tile
+    // to its row (publishes, looks back, fetches the next descriptor): one warp doing both would do
+    // them one after the other.
+    constexpr int boss = ASC ? 0 : NT - 32;
     const uint32_t ntiles = (uint32_t)p.ntiles;
     const uint32_t epoch = read_epoch(p.header);
     const bool with_halo = BWD && p.chain;
@@ -182,7 +189,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
                                  : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
 
     if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
-    if (tid == 0) {
+    if (tid == boss) {
 #pragma unroll
         for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
         abort_flag = 0;
@@ -197,7 +204,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     }
     __syncthreads();
 
-    // Thread 0 only: start the copies of ticket `tk` into ring slot `s`.
+    // Issuing thread only: start the copies of ticket `tk` into ring slot `s`.
     auto issue = [&](int s, uint32_t tk) {
         const TileCoord tc = decode_ticket<T, ASC>(p, tk);
         const int c1 = tc.piece * LINES;
@@ -215,7 +222,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             // 4-byte copies from the 4-byte-aligned word that contains the element
             // (a coefficient that lies before an open shard start is 1; both halves for 2-byte storage)
             if (c_ok) ptx::cp_async_4(&halo[s][0], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(csrc) & ~(uintptr_t)3));
-            else halo[s][0] = !p.open_start ? (p.logc ? Storage<ST>::kNegInfPair : 0u) : (p.logc ? 0u : Storage<ST>::kOnePair);
+            else halo[s][0] = !row_is_open<ASC>(p, tc.row) ? (p.logc ? Storage<ST>::kNegInfPair : 0u) : (p.logc ? 0u : Storage<ST>::kOnePair);
             if (y_ok) ptx::cp_async_4(&halo[s][1], reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(ysrc) & ~(uintptr_t)3));
             else halo[s][1] = 0u;
             ptx::cp_async_mbar_arrive_noinc(&full[s]);
@@ -245,8 +252,8 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     const bool lazy = (S == 1) && p.lazy;
     const bool fixed = !p.chain || p.fixed_first;
     const uint32_t dyn_base = p.first_ticket + (fixed ? (lazy ? 1u : (uint32_t)(S + 1)) * grid : 0u);
-    uint32_t next_ticket = 0;   // meaningful in thread 0 only: ticket held one step ahead
-    if (tid == 0) {
+    uint32_t next_ticket = 0;   // meaningful in the issuing thread only: ticket held one step ahead
+    if (tid == boss) {
         for (int s = 0; s < S; ++s) {
             const uint32_t tk = fixed ? p.first_ticket + (uint32_t)s * grid + blockIdx.x : dyn_base + atomicAdd(p.header, 1u);
             tile_of_stage[s] = tk;
@@ -271,7 +278,8 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             abort_flag = 1;
         }
 
-        float pred_c = p.open_start ? 1.0f : 0.0f, succ_y = 0.0f;
+        const bool open = row_is_open<ASC>(p, tc.row);   // (super-chunks only exist in chain mode: one row per tile)
+        float pred_c = open ? 1.0f : 0.0f, succ_y = 0.0f;
         if (with_halo) {
             // the halo word holds the element in its low or high half for 2-byte storage
             const uint32_t wc = halo[s][0], wy = halo[s][1];
@@ -286,7 +294,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         // the end of the tile (whole 128-byte lines make `valid` a multiple of E, so it is the last slot
         // of thread valid/E - 1).
         const bool zero_first =
-            !p.open_start && (p.chain ? (tc.q == 0 && (ASC ? g.t == 0 : g.t == tc.valid / E - 1)) : (g.k == 0));
+            !open && (p.chain ? (tc.q == 0 && (ASC ? g.t == 0 : g.t == tc.valid / E - 1)) : (g.k == 0));
 
         Operands<E, BWD> op;
         load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1),
@@ -296,13 +304,13 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         bool alive = true;
         tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
             // the output buffer about to be reused must have been drained by its bulk store
-            if (tid == 0) ptx::tma_wait_group_read<OB - 1>();
+            if (tid == boss) ptx::tma_wait_group_read<OB - 1>();
             __syncthreads();
             if (abort_flag) {
                 alive = false;
                 return false;
             }
-            if (tid == 0 && !lazy) {   // ring slot s is free again: refill it with the ticket drawn earlier
+            if (tid == boss && !lazy) {   // ring slot s is free again: refill it with the ticket drawn earlier
                 tile_of_stage[s] = next_ticket;
                 if (next_ticket < ntiles) issue(s, next_ticket);
                 next_ticket = dyn_base + atomicAdd(p.header, 1u);
@@ -316,7 +324,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         if constexpr (BWD) store_run<ST, E>(out_buf(ob, 1), g.t, o1);
         ptx::fence_proxy_async_smem();
         __syncthreads();
-        if (tid == 0) {
+        if (tid == boss) {
             const int c1 = tc.piece * LINES;
             const int c2 = (int)tc.row;
             ptx::tma_store_3d(&tm_out0, out_buf(ob, 0), 0, c1, c2);
@@ -331,7 +339,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         if (lazy) __syncthreads();   // the new ticket must be visible before the next round reads it
     }
 
-    if (tid == 0) {
+    if (tid == boss) {
         if (abort_flag) {
             // best effort: let copies already in flight land before the CTA gives its memory back
             for (uint32_t j = 1; j < (uint32_t)S; ++j) {
@@ -504,13 +512,16 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
 }
 
 // =================================================================================================
-//  Asynchronous-copy kernel: 16-byte aligned rows that the bulk-copy kernel cannot take
+//  Asynchronous-copy kernel: rows that the bulk-copy kernel cannot take
 // =================================================================================================
-// Rows that are 16-byte aligned and a whole number of 16-byte chunks long, but not a multiple of 128
-// bytes (L = 1000, 10000, ...): every thread copies its share of a tile with 16-byte cp.async
+// Rows that are not whole 128-byte lines: every thread copies its share of a tile with cp.async
 // straight into the swizzled layout through a ring of S tiles (the copies of the next S-1 tiles are
-// in flight while tile i is scanned); padding chunks are written as identities.  Results go back through the same
-// shared tile and leave with 16-byte stores.  Same tile algebra and look-back as the other kernels.
+// in flight while tile i is scanned); padding chunks are written as identities.  Results go back
+// through the same shared tile.  Same tile algebra and look-back as the other kernels.
+//   CB = 16  rows 16-byte aligned and a whole number of 16-byte chunks long (L = 1000, 10000, ...);
+//   CB = 4   rows 4-byte aligned and a whole number of 4-byte words long: every fp32 row whatever its
+//            length or offset (L = 1001, views that start at an odd element), even-length rows of
+//            2-byte elements.  One word per lane: a warp still moves whole 128-byte lines.
 template <typename ST, int E, int NT, int S, bool BWD>
 struct AsyncLayout {
     static constexpr int T = E * NT;
@@ -525,13 +536,15 @@ struct AsyncLayout {
     static constexpr int kMinBlocks = kFitSmem < 1 ? 1 : (kFitSmem < kByThreads ? kFitSmem : kByThreads);
 };
 
-template <typename ST, int E, int NT, int S, bool BWD, bool ASC>
+template <typename ST, int E, int NT, int S, int CB, bool BWD, bool ASC>
 __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlocks)) linrec_async_kernel(const ScanParams p)
 {
     using L = AsyncLayout<ST, E, NT, S, BWD>;
+    static_assert(CB == 16 || CB == 4, "chunks are 16 or 4 bytes");
     constexpr int T = L::T, NW = NT / 32, NIN = L::NIN;
-    constexpr int PC = Storage<ST>::kPerChunk;
+    constexpr int PC = CB / (int)sizeof(ST);          // elements per chunk
     constexpr uint32_t kOne = Storage<ST>::kOnePair;
+    using Chunk = typename std::conditional<CB == 16, uint4, uint32_t>::type;
     extern __shared__ uint8_t dyn_smem[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~(uintptr_t)1023);
     auto buf = [&](int s, int a) { return reinterpret_cast<ST*>(base + (size_t)(s * NIN + a) * L::kTileBytes); };
@@ -556,24 +569,52 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
     if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
 
     // The chunks a thread copies are the same in every tile: chunk ci = tid + k*NT of the tile.  Its
-    // place relative to the tile's first element is worked out once (there is an integer division in
-    // it); per tile only the base offset and one comparison remain.
+    // place relative to the tile's first element has an integer division in it.  With few chunks per
+    // thread it is worked out once and kept in registers (per tile only the base offset and one
+    // comparison remain); with many (4-byte chunks) it is recomputed per tile with a multiply-high in
+    // place of the division (exact: chunk indices and chunks per row stay below 2^14).
     constexpr int CPT = T / PC / NT;   // chunks per thread and array
-    long long rel[CPT];                // element offset from the tile's first element
-    int key[CPT];                      // chain: column inside the tile; else row inside the tile
-#pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        const int ci = tid + k * NT;
+    constexpr bool kTable = CPT <= 4;
+    long long rel[kTable ? CPT : 1];   // element offset from the tile's first element
+    int key[kTable ? CPT : 1];         // chain: column inside the tile; else row inside the tile
+    const uint32_t cpr_magic = (uint32_t)((0x100000000ull + (uint32_t)cpr - 1u) / (uint32_t)cpr);   // ceil(2^32 / cpr)
+    auto locate = [&](int k, long long& r, int& ky) {
+        int ci = tid + k * NT;
+        // (without the table the values are meant to be recomputed where they are used; the empty
+        //  volatile statement keeps the compiler from hoisting all of them out of the tile loop, which
+        //  would cost three registers per chunk)
+        if constexpr (!kTable) asm volatile("" : "+r"(ci));
         if (p.chain) {
-            key[k] = ci * PC;
-            rel[k] = (long long)ci * PC;
+            ky = ci * PC;
+            r = (long long)ci * PC;
         } else {
-            const int j = ci / cpr;
+            const int j = (int)__umulhi((uint32_t)ci, cpr_magic);
             const int col = (ci - j * cpr) * PC;
-            key[k] = (j < p.rows_per_tile && col < p.seqlen) ? j : 0x7fffffff;
-            rel[k] = (long long)j * p.row_stride + col;
+            ky = (j < p.rows_per_tile && col < p.seqlen) ? j : 0x7fffffff;
+            r = (long long)j * p.row_stride + col;
         }
+    };
+    if constexpr (kTable) {
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) locate(k, rel[k], key[k]);
     }
+    auto place = [&](int k, long long& r, int& ky) {
+        if constexpr (kTable) {
+            r = rel[k];
+            ky = key[k];
+        } else {
+            locate(k, r, ky);
+        }
+    };
+    // byte offset of chunk ci inside a swizzled tile buffer
+    auto chunk_offset = [](int ci) -> uint32_t {
+        const uint32_t b = (uint32_t)ci * (uint32_t)CB;
+        const uint32_t c16 = b >> 4;
+        return ((c16 ^ ((c16 >> 3) & 7u)) << 4) | (b & 15u);
+    };
+    auto chunk_at = [&](int s_, int a, int ci) -> Chunk* {
+        return reinterpret_cast<Chunk*>(reinterpret_cast<char*>(buf(s_, a)) + chunk_offset(ci));
+    };
     // tile -> (offset of its first element, bound that key[] has to stay under)
     auto tile_base = [&](const TileCoord& tc, int& lim) -> long long {
         const long long rows_left = p.numseq - tc.row;
@@ -589,18 +630,32 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
                 const int ci = tid + k * NT;
-                const long long off = tb + rel[k];
-                const int phys = ci ^ ((ci >> 3) & 7);
-                uint4* d0 = reinterpret_cast<uint4*>(buf(s, 0)) + phys;
-                uint4* d1 = reinterpret_cast<uint4*>(buf(s, 1)) + phys;
-                if (key[k] < lim) {
-                    ptx::cp_async_16(d0, gin0 + off);
-                    ptx::cp_async_16(d1, gc + off);
-                    if (BWD) ptx::cp_async_16(reinterpret_cast<uint4*>(buf(s, 2)) + phys, gy + off);
+                long long r;
+                int ky;
+                place(k, r, ky);
+                const long long off = tb + r;
+                Chunk* d0 = chunk_at(s, 0, ci);
+                Chunk* d1 = chunk_at(s, 1, ci);
+                if (ky < lim) {
+                    if constexpr (CB == 16) {
+                        ptx::cp_async_16(d0, gin0 + off);
+                        ptx::cp_async_16(d1, gc + off);
+                        if (BWD) ptx::cp_async_16(chunk_at(s, 2, ci), gy + off);
+                    } else {
+                        ptx::cp_async_4(d0, gin0 + off);
+                        ptx::cp_async_4(d1, gc + off);
+                        if (BWD) ptx::cp_async_4(chunk_at(s, 2, ci), gy + off);
+                    }
                 } else {
-                    *d0 = make_uint4(0u, 0u, 0u, 0u);
-                    *d1 = p.logc ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(kOne, kOne, kOne, kOne);
-                    if (BWD) reinterpret_cast<uint4*>(buf(s, 2))[phys] = make_uint4(0u, 0u, 0u, 0u);
+                    if constexpr (CB == 16) {
+                        *d0 = make_uint4(0u, 0u, 0u, 0u);
+                        *d1 = p.logc ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(kOne, kOne, kOne, kOne);
+                        if (BWD) *chunk_at(s, 2, ci) = make_uint4(0u, 0u, 0u, 0u);
+                    } else {
+                        *d0 = 0u;
+                        *d1 = p.logc ? 0u : kOne;
+                        if (BWD) *chunk_at(s, 2, ci) = 0u;
+                    }
                 }
             }
             if (with_halo && tid < 2) {
@@ -693,12 +748,14 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
             const long long tb = tile_base(tc, lim);
 #pragma unroll
             for (int k = 0; k < CPT; ++k) {
-                if (key[k] < lim) {
+                long long r;
+                int ky;
+                place(k, r, ky);
+                if (ky < lim) {
                     const int ci = tid + k * NT;
-                    const long long off = tb + rel[k];
-                    const int phys = ci ^ ((ci >> 3) & 7);
-                    *reinterpret_cast<uint4*>(gout0 + off) = reinterpret_cast<const uint4*>(buf(s, 0))[phys];
-                    if (BWD) *reinterpret_cast<uint4*>(gout1 + off) = reinterpret_cast<const uint4*>(buf(s, 2))[phys];
+                    const long long off = tb + r;
+                    *reinterpret_cast<Chunk*>(gout0 + off) = *chunk_at(s, 0, ci);
+                    if (BWD) *reinterpret_cast<Chunk*>(gout1 + off) = *chunk_at(s, 2, ci);
                 }
             }
         }

@@ -30,6 +30,9 @@ struct FixupParams {
     int rec;             // floats per record: 2 forward, 4 backward
     const PeerTable* px; // with px_epoch != 0: the records arrive in this rank's exchange buffer (16-byte
     uint32_t px_epoch;   // records, one flag per row and sender) instead of `carries`
+    int super_chunks;    // > 1: the "shards" are consecutive rows of ONE tensor (a real row cut into this many
+                         //      pieces, a power of two): row r is shard r % super_chunks of real row
+                         //      r / super_chunks, and the records are indexed by row
     long long wait_budget;   // clock ticks a wait for a peer's record may last
     uint32_t* status;    // status word that receives kStatusPeerTimeout
 };
@@ -43,6 +46,7 @@ __device__ __forceinline__ const float* fixup_record(const FixupParams& p, int s
         if (!wait_epoch_reached(px_flag(t, t.me, par, s, row), p.px_epoch, p.wait_budget)) atomicOr(p.status, kStatusPeerTimeout);
         return reinterpret_cast<const float*>(px_record(t, t.me, par, s, row));
     }
+    if (p.super_chunks > 1) return p.carries + ((row & ~(long long)(p.super_chunks - 1)) + s) * p.rec;
     return p.carries + ((long long)s * p.numseq + row) * p.rec;
 }
 
@@ -123,24 +127,27 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
     __shared__ float wprod[2][NW];
     __shared__ float v_in_s;
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
-    const int my_pos = ASC ? p.shard : p.nshards - 1 - p.shard;   // my rank among the shards in scan order
     const long long L = p.seqlen;
 
     for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
+        const int shard = p.super_chunks > 1 ? (int)(row & (p.super_chunks - 1)) : p.shard;
+        const int my_pos = ASC ? shard : p.nshards - 1 - shard;   // my rank among the shards in scan order
         // ---- carry that enters this shard ---------------------------------------------------------
+        // v = sum over the earlier shards n of Y_n * (product of everything between shard n and this one),
+        // gathered from the nearest shard backwards: the multiplier only shrinks for decaying
+        // coefficients, and once it is exactly zero no earlier shard can contribute (with many shards
+        // per row -- super-chunks -- the walk usually ends after one record).  Backward pass: between
+        // two shards lies the coefficient at the earlier one's scan-last element (record word 2),
+        // which the local scans treated as 1.
         if (tid == 0) {
-            float v = 0.0f;
-            int prev = -1;
-            float prev_edge = 1.0f;   // c at the scan-last element of the shard folded last
-            for (int n = 0; n < my_pos; ++n) {
-                const int s = shard_at<ASC>(n, p.nshards);
-                const volatile float* rec = fixup_record(p, s, row);
-                if (BWD && prev >= 0) v *= prev_edge;
-                v = fmaf(v, rec[0], rec[1]);
-                if (BWD) prev_edge = rec[2];
-                prev = s;
+            float v = 0.0f, m = 1.0f;
+            for (int n = my_pos - 1; n >= 0; --n) {
+                const volatile float* rec = fixup_record(p, shard_at<ASC>(n, p.nshards), row);
+                if (BWD) m *= rec[2];
+                v = fmaf(rec[1], m, v);
+                m *= rec[0];
+                if (m == 0.0f) break;
             }
-            if (BWD && prev >= 0) v *= prev_edge;
             v_in_s = v;
         }
         __syncthreads();

@@ -1,0 +1,16 @@
+// cp.async kernel variants with 16-byte chunks.
+// One of the translation units the kernel variants are spread over (see variants.h).
+#include "variants.h"
+
+namespace linrec_variants {
+
+void add_async_variants(std::vector<GenericVariant>& v)
+{
+    v.push_back(make_async_variant<16, 128, 2, 16>());
+    v.push_back(make_async_variant<16, 128, 3, 16>());
+    v.push_back(make_async_variant<32, 128, 2, 16>());
+    v.push_back(make_async_variant<16, 256, 2, 16>());
+    v.push_back(make_async_variant<16, 512, 2, 16>());
+}
+
+}  // namespace linrec_variants

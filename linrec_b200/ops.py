@@ -12,6 +12,8 @@ they were; element counts are 64-bit.
 """
 from __future__ import annotations
 
+import contextlib
+import functools
 import os
 import threading
 from types import SimpleNamespace
@@ -42,6 +44,18 @@ def _workspace(device: torch.device, stream_ptr: int, nbytes: int) -> torch.Tens
             ws = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
             _workspaces[key] = ws
         return ws
+
+
+@functools.lru_cache(maxsize=256)
+def _workspace_size(numseq: int, seqlen: int, dtype: int) -> int:
+    return int(_capi.lib.linrec_b200_workspace_size(numseq, seqlen, dtype))
+
+
+def _on_device(device: torch.device):
+    """Context that makes `device` current; free when it already is (the usual case)."""
+    if torch.cuda.current_device() == device.index:
+        return contextlib.nullcontext()
+    return torch.cuda.device(device)
 
 
 def check_status(device=None) -> None:
@@ -107,34 +121,49 @@ def _empty_like_rows(t: torch.Tensor) -> torch.Tensor:
     return torch.empty(t.size(), dtype=t.dtype, device=t.device)
 
 
+# Signature (shape, strides, dtype, device) of tensors that passed every check before -> their row
+# layout.  A training loop calls with the same signatures over and over; for them the preconditions
+# reduce to "all tensors of the call have the signature of the first, and that one is known".
+_known_layouts: dict = {}
+
+
 def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
     """One forward or backward call.  `outs` (optional) are caller-provided result tensors with the
     layout of the inputs; without them the results are allocated like the inputs."""
-    _check_same(*ins)
     ref = ins[0]
     n_out = 2 if bwd else 1
-    if outs is None:
-        outs = [_empty_like_rows(ref) for _ in range(n_out)]
+    sig = (ref.shape, ref.stride(), ref.dtype, ref.device)
+    layout = _known_layouts.get(sig)
+    if layout is not None and all((t.shape, t.stride(), t.dtype, t.device) == sig for t in ins[1:]) and (
+            outs is None or (len(outs) == n_out and all((t.shape, t.stride(), t.dtype, t.device) == sig for t in outs))):
+        if outs is None:
+            outs = [torch.empty_strided(sig[0], sig[1], dtype=sig[2], device=sig[3]) for _ in range(n_out)]
+        work_ins, work_outs = ins, outs
     else:
-        outs = list(outs)
-        if len(outs) != n_out:
-            raise RuntimeError("linrec: wrong number of result tensors")
-        _check_same(ref, *outs)
-    if ref.numel() == 0:
-        return outs
-    layout = _row_layout(ref)
-    work_ins, work_outs = list(ins), outs
-    if layout is None or any(o.stride() != ref.stride() for o in outs):
-        work_ins = [t.contiguous() for t in ins]
-        work_outs = [torch.empty_like(work_ins[0]) for _ in range(n_out)]
-        layout = _row_layout(work_ins[0])
+        _check_same(*ins)
+        if outs is None:
+            outs = [_empty_like_rows(ref) for _ in range(n_out)]
+        else:
+            outs = list(outs)
+            if len(outs) != n_out:
+                raise RuntimeError("linrec: wrong number of result tensors")
+            _check_same(ref, *outs)
+        if ref.numel() == 0:
+            return outs
+        layout = _row_layout(ref)
+        work_ins, work_outs = list(ins), outs
+        if layout is None or any(o.stride() != ref.stride() for o in outs):
+            work_ins = [t.contiguous() for t in ins]
+            work_outs = [torch.empty_like(work_ins[0]) for _ in range(n_out)]
+            layout = _row_layout(work_ins[0])
+        elif len(_known_layouts) < 4096:
+            _known_layouts[sig] = layout        # every tensor of this call has the signature of `ref`
     numseq, seqlen, row_stride = layout
     dtype = _DTYPES[ref.dtype]
     opts, keep = _capi.make_opts(kwargs)
-    with torch.cuda.device(ref.device):
+    with _on_device(ref.device):
         stream = torch.cuda.current_stream(ref.device).cuda_stream
-        need = _capi.lib.linrec_b200_workspace_size(numseq, seqlen, dtype)
-        ws = _workspace(ref.device, stream, need)
+        ws = _workspace(ref.device, stream, _workspace_size(numseq, seqlen, dtype))
         if not bwd:
             rc = _capi.lib.linrec_b200_fwd(kind, work_ins[0].data_ptr(), work_ins[1].data_ptr(),
                                            work_outs[0].data_ptr(), numseq, seqlen, row_stride,

@@ -145,11 +145,11 @@ def test_bf16_storage(shape, rev, dtype):
 
 
 def test_tile_family_refuses_rows_longer_than_a_tile():
-    """The tile family keeps a whole row in one tile: 8192 elements when rows can be copied in
-    16-byte chunks, 2048 for the plain-load kernel."""
+    """The tile family keeps a whole row in one tile; the largest tile holds 8192 fp32 elements
+    whichever loader the row's length and alignment select."""
     lb = _ops()
     dev = torch.device("cuda:0")
-    for L, fits in [(2049, False), (2100, True), (8192 + 4, False), (8192 - 4, True)]:
+    for L, fits in [(2049, True), (2100, True), (8192 + 4, False), (8192 - 4, True), (8191, True), (8193, False)]:
         x, c, _ = _data((2, L))
         if fits:
             y = lb._C.linrec_tile_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=False)
@@ -208,6 +208,65 @@ def test_async_copy_kernel_refuses_unaligned_rows():
         lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=False, memcode=2)
 
 
+# ---- rows of whole 4-byte words: the 4-byte cp.async kernel -------------------------------------------
+@pytest.mark.parametrize("shape", [(7, 101), (300, 37), (33, 1001), (5, 2101), (3, 10001), (2, 50003), (1, 3), (9, 1),
+                                   (2, 3 * 8192 + 1), (40, 4097)], ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_word_copy_kernel(shape, rev):
+    """fp32 rows of any length (here: odd lengths, which no 16-byte path can take) go through 4-byte
+    cp.async copies (memcode 3, the default for them); every variant of that loader, the lazy-ticket
+    mode and the plain-load kernel (memcode 0) must agree with the oracle."""
+    lb = _ops()
+    x, c, dy = _data(shape, clo=0.3)
+    attrs = lb._C.linrec_pipe_attrs(fwd=True, memcode=3)
+    assert attrs["memcode"] == 3 and attrs["kStages"] == 2
+    for kw in ({}, {"memcode": 3, "kThreadsPerBlock": 128}, {"memcode": 3, "kThreadsPerBlock": 256},
+               {"memcode": 3, "kThreadsPerBlock": 512}, {"memcode": 3, "kThreadsPerBlock": 512, "lazyTickets": 1},
+               {"memcode": 0}):
+        _check_fwd_bwd(x, c, dy, rev, **kw)
+
+
+def test_word_copy_kernel_views_and_two_byte_rows():
+    """Views that start at an odd element and rows with padding between them (fp32), and even-length
+    rows of 2-byte elements at 4-byte aligned addresses; a 2-byte row that starts at an odd element
+    has no 4-byte path and falls to the plain-load kernel."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(17)
+    for (rows, L, stride, off) in [(5, 255, 255, 1), (5, 1001, 1003, 3), (3, 9001, 9002, 1), (4, 20001, 20001, 0)]:
+        big_x = torch.randn(rows * stride + off + 8, generator=g)
+        big_c = torch.rand(rows * stride + off + 8, generator=g)
+        big_dy = torch.randn(rows * stride + off + 8, generator=g)
+        view = lambda t: torch.as_strided(t, (rows, L), (stride, 1), off)
+        xh, ch, dyh = (view(t).contiguous() for t in (big_x, big_c, big_dy))
+        for rev in (False, True):
+            xv, cv, dyv = (view(t.to(dev)) for t in (big_x, big_c, big_dy))
+            y = lb._C.linrec_pipe_fwd(inputs=xv, coeffs=cv, reverse=rev, memcode=3)
+            y_ref = oracle.fwd_f32(xh.numpy(), ch.numpy(), reverse=rev)
+            np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=RTOL, atol=ATOL)
+            dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dyv, coeffs=cv, outputs=y, reverse=rev, memcode=3)
+            dx_ref, dc_ref = oracle.bwd_f32(dyh.numpy(), ch.numpy(), y.cpu().numpy(), reverse=rev)
+            np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=RTOL, atol=ATOL)
+            np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=RTOL, atol=2 * ATOL)
+    for dtype in (torch.bfloat16, torch.float16):
+        rtol = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9
+        for shape in [(9, 202), (4, 4102), (2, 20006)]:
+            x, c, dy = (t.to(dtype) for t in _data(shape, clo=0.5))
+            for rev in (False, True):
+                y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev, memcode=3)
+                y_ref = oracle.fwd_f32(x.float().numpy(), c.float().numpy(), reverse=rev)
+                np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=rtol, atol=ATOL)
+                dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=y, reverse=rev, memcode=3)
+                dx_ref, dc_ref = oracle.bwd_f32(dy.float().numpy(), c.float().numpy(), y.float().cpu().numpy(), reverse=rev)
+                np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=rtol, atol=ATOL)
+                np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref, rtol=rtol, atol=2 * ATOL)
+        odd = torch.zeros(2 * 101 + 1, dtype=dtype, device=dev)[1:].view(2, 101)
+        with pytest.raises(RuntimeError):
+            lb._C.linrec_pipe_fwd(inputs=odd, coeffs=odd, reverse=False, memcode=3)
+        assert lb.linrec(odd, odd).shape == (2, 101)
+    lb.check_status()
+
+
 # ---- every compiled variant ------------------------------------------------------------------------
 def _variants():
     lb = _ops()
@@ -222,7 +281,7 @@ def test_all_variants(shape, rev):
     assert len(configs) >= 4
     for cfg in configs:
         E, NT, S, OB, memcode = cfg
-        if memcode == 1 and E * NT * 4 * (3 * S + 2 * OB) + 1024 > 227 * 1024:
+        if memcode == 1 and (E * NT * 4 * (3 * S + 2 * OB) + 1024 > 227 * 1024 or E * NT * 4 > 256 * 128):
             # the backward pass of this variant needs more shared memory than an SM has
             with pytest.raises(NotImplementedError):
                 _check_fwd_bwd(x, c, dy, rev, **dict(zip(names, cfg)))
@@ -444,9 +503,10 @@ def test_handful_of_very_long_rows(rev):
     """Few rows, many tiles each: the selector's one-ticket-at-a-time mode (every tile looks back at
     tiles that are in flight at the same moment)."""
     x, c, dy = _data((3, 40 * 8192 + 4096), clo=0.9)
-    _check_fwd_bwd(x, c, dy, rev)
-    _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=128, kStages=1, lazyTickets=1)
-    _check_fwd_bwd(x, c, dy, rev, kElemsPerThread=16, kThreadsPerBlock=256, kStages=1, lazyTickets=0)
+    _check_fwd_bwd(x, c, dy, rev)                      # default: super-chunks (see test_super_chunks)
+    _check_fwd_bwd(x, c, dy, rev, superChunks=0)       # the rows as they are: one ticket at a time
+    _check_fwd_bwd(x, c, dy, rev, superChunks=0, kElemsPerThread=16, kThreadsPerBlock=128, kStages=1, lazyTickets=1)
+    _check_fwd_bwd(x, c, dy, rev, superChunks=0, kElemsPerThread=16, kThreadsPerBlock=256, kStages=1, lazyTickets=0)
     # the same regime for rows that are not whole 128-byte lines (cp.async kernel)
     x, c, dy = _data((3, 40 * 8192 + 4100), clo=0.9)
     _check_fwd_bwd(x, c, dy, rev)
@@ -454,6 +514,60 @@ def test_handful_of_very_long_rows(rev):
     _check_fwd_bwd(x, c, dy, rev, memcode=2, kThreadsPerBlock=512, lazyTickets=0)
     x, c, dy = _data((150, 3 * 8192 + 8), clo=0.9)   # few rows: the 4096-element tile
     _check_fwd_bwd(x, c, dy, rev)
+
+
+@pytest.mark.parametrize("rev", [False, True])
+@pytest.mark.parametrize("rows,L,clo,chi", [(3, 1 << 18, 0.0, 1.0), (1, 1 << 20, 0.9, 1.0), (5, 3 << 17, 0.999, 1.0),
+                                            (2, 1 << 18, 1.0, 1.0), (7, 1 << 17, 0.5, 1.5)],
+                         ids=["fast_decay", "one_row", "slow_decay", "no_decay", "growing_stretches"])
+def test_super_chunks(rows, L, clo, chi, rev):
+    """Few very long rows are cut into super-chunks that are scanned independently and then corrected
+    by a fix-up kernel (two launches).  Checked against the oracle for coefficients that decay fast,
+    slowly (the correction crosses whole super-chunks), not at all (c = 1: a plain prefix sum, the
+    fix-up is a full second pass) and for c in (0.5, 1.5), where stretches of |c| > 1 let a
+    correction grow back; the result must also agree with the single-launch scan of the same rows."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data((rows, L), clo=clo, chi=chi, seed=SEED + rows)
+    if clo == chi:
+        c = torch.full_like(c, clo)
+        x, dy = x * 1e-2, dy * 1e-2
+    before = lb._C.launch_count()
+    y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
+    assert lb._C.launch_count() - before == 2, "expected the super-chunk path (scan + fix-up)"
+    y1 = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev, superChunks=0)
+    y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
+    y64 = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
+    scale = max(1.0, float(np.abs(y64).max()))
+    # judged like every slowly decaying case: against the fp64 evaluation, relative to the sequential
+    # fp32 oracle's own error (two valid fp32 orders differ by more than the nominal tolerance there)
+    err_seq = float(np.abs(y_ref - y64).max())
+    for got in (y, y1):
+        assert float(np.abs(got.cpu().numpy() - y64).max()) <= 2 * err_seq + ATOL * scale
+    yd = torch.from_numpy(y_ref).to(dev)
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yd, reverse=rev)
+    dx1, dc1 = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yd, reverse=rev, superChunks=0)
+    dx64, dc64 = oracle.bwd_f64(dy.numpy(), c.numpy(), y_ref.astype(np.float64), reverse=rev)
+    dx32, dc32 = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+    gscale = max(1.0, float(np.abs(dx64).max()))
+    for gx, gc in ((dx, dc), (dx1, dc1)):
+        assert float(np.abs(gx.cpu().numpy() - dx64).max()) <= 2 * float(np.abs(dx32 - dx64).max()) + ATOL * gscale
+        assert float(np.abs(gc.cpu().numpy() - dc64).max()) <= 2 * float(np.abs(dc32 - dc64).max()) + 2 * ATOL * gscale * scale
+    if chi <= 1.0 and clo < 1.0:
+        np.testing.assert_allclose(y.cpu().numpy(), y1.cpu().numpy(), rtol=RTOL, atol=ATOL * scale)
+    # explicit cut counts, bf16 storage
+    for V in (2, 8):
+        yv = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev, superChunks=V)
+        assert float(np.abs(yv.cpu().numpy() - y64).max()) <= 2 * err_seq + ATOL * scale
+    # 2-byte storage keeps the single-launch scan (a second rounding of the corrected values would show)
+    before = lb._C.launch_count()
+    xb, cb = x.bfloat16(), c.bfloat16()
+    yb = lb._C.linrec_pipe_fwd(inputs=xb.to(dev), coeffs=cb.to(dev), reverse=rev)
+    assert lb._C.launch_count() - before == 1
+    if clo < 0.99:
+        yb_ref = oracle.fwd_f32(xb.float().numpy(), cb.float().numpy(), reverse=rev)
+        np.testing.assert_allclose(yb.float().cpu().numpy(), yb_ref, rtol=2.0 ** -7, atol=ATOL)
+    lb.check_status()
 
 
 def test_cuda_graph_capture_and_replay():
