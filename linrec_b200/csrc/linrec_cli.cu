@@ -4,7 +4,10 @@
 //
 //   linrec_cli --numseq 512 --seqlen 65536 [--reverse] [--bwd] [--dtype f32|bf16|f16]
 //              [--clo 0 --chi 1] [--stride N] [--iters 20 --warmup 3] [--flush]
-//              [--opt name=value ...] [--sweep] [--no-verify] [--kind pipe|tile|ref]
+//              [--opt name=value ...] [--sweep] [--no-verify] [--kind pipe|tile|ref] [--dump PREFIX]
+//
+// --dump writes the operands and the results of the last measured configuration as raw arrays, so that
+// a checker outside this program (the CPU oracle of the test-suite) can judge them.
 //
 // Prints one JSON object per measured configuration.
 #include <cuda_bf16.h>
@@ -106,6 +109,7 @@ struct Args {
     float clo = 0.0f, chi = 1.0f;
     std::vector<std::string> opt_names;
     std::vector<int> opt_values;
+    std::string dump;     // not empty: write operands and results to <dump>.{in0,c,y,out0,out1}.bin (raw storage type)
 };
 
 static void usage()
@@ -113,7 +117,7 @@ static void usage()
     fprintf(stderr,
             "usage: linrec_cli [--numseq N] [--seqlen L] [--stride S | --chan D] [--reverse] [--bwd] [--dtype f32|bf16|f16]\n"
             "                  [--clo a --chi b] [--iters K --warmup W] [--flush] [--opt name=value ...]\n"
-            "                  [--sweep] [--no-verify] [--kind pipe|tile|ref]\n");
+            "                  [--sweep] [--no-verify] [--kind pipe|tile|ref] [--dump PREFIX]\n");
 }
 
 struct Result {
@@ -339,6 +343,26 @@ static int run(const Args& a)
         printf("}\n");
         fflush(stdout);
     }
+    if (!a.dump.empty()) {
+        CK(cudaDeviceSynchronize());
+        std::vector<T> host(total);
+        auto put = [&](const char* what, const T* dev) {
+            if (!dev) return;
+            CK(cudaMemcpy(host.data(), dev, total * sizeof(T), cudaMemcpyDeviceToHost));
+            const std::string path = a.dump + "." + what + ".bin";
+            FILE* f = fopen(path.c_str(), "wb");
+            if (!f || fwrite(host.data(), sizeof(T), total, f) != total) {
+                fprintf(stderr, "cannot write %s\n", path.c_str());
+                worst = worst ? worst : 6;
+            }
+            if (f) fclose(f);
+        };
+        put("in0", in0);
+        put("c", c);
+        put("y", yfw);
+        put("out0", out0);
+        put("out1", out1);
+    }
     cudaFree(in0); cudaFree(c); cudaFree(out0); cudaFree(ref0); cudaFree(ws); cudaFree(d_max); cudaFree(d_bad);
     if (yfw) cudaFree(yfw);
     if (out1) cudaFree(out1);
@@ -370,6 +394,7 @@ int main(int argc, char** argv)
         else if (s == "--flush") a.flush = 1;
         else if (s == "--sweep") a.sweep = 1;
         else if (s == "--no-verify") a.verify = 0;
+        else if (s == "--dump") a.dump = next();
         else if (s == "--kind") {
             std::string k = next();
             a.kind = k == "ref" ? LINREC_KIND_REF : k == "tile" ? LINREC_KIND_TILE : LINREC_KIND_PIPE;

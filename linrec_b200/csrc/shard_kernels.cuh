@@ -112,7 +112,7 @@ template <bool BWD>
 struct FixupStep {
     float c[8];              // forward: c of the element; backward: c of the scan predecessor
     float o0[8];             // current y (forward) / dx (backward)
-    float o1[BWD ? 8 : 1];   // backward: current dc
+    float o1[BWD ? 8 : 1];   // backward: dc (recomputed from the corrected dx, never read)
     float ys[BWD ? 8 : 1];   // backward: y of the scan successor
     long long m0;            // memory index of element 0
 };
@@ -172,7 +172,6 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             } else {
                 float yr[8];
                 load8<ST, VEC>(y, st.m0, L, 0.0f, yr);
-                load8<ST, VEC>(o1, st.m0, L, 0.0f, st.o1);
                 // neighbours just outside the 8 elements (0 / 1 beyond the shard: the edge factors are
                 // folded into the carry and the scan-last dc is finished after the walk)
                 const long long below = st.m0 - 1, above = st.m0 + V;
@@ -234,7 +233,9 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
                     const int j = ASC ? jj : 7 - jj;
                     const float z = zin * pr[jj];
                     cur.o0[j] += z;
-                    if constexpr (BWD) cur.o1[j] = fmaf(z, cur.ys[j], cur.o1[j]);
+                    // dc is dx * y at the scan successor by definition: formed again from the corrected dx
+                    // (exactly what the scan kernel computes; the stored dc need not be read)
+                    if constexpr (BWD) cur.o1[j] = cur.o0[j] * cur.ys[j];
                 }
                 store8<ST, VEC>(o0, cur.m0, L, cur.o0);
                 if constexpr (BWD) store8<ST, VEC>(o1, cur.m0, L, cur.o1);
