@@ -568,52 +568,67 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
     const bool with_halo = BWD && p.chain;
     if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
 
-    // The chunks a thread copies are the same in every tile: chunk ci = tid + k*NT of the tile.  Its
-    // place relative to the tile's first element has an integer division in it.  With few chunks per
-    // thread it is worked out once and kept in registers (per tile only the base offset and one
-    // comparison remain); with many (4-byte chunks) it is recomputed per tile with a multiply-high in
-    // place of the division (exact: chunk indices and chunks per row stay below 2^14).
+    // The chunks a thread copies are the same in every tile: chunk ci = tid + k*NT of the tile,
+    // k = 0 .. CPT-1.  Where chunk ci lies -- its byte offset in the swizzled shared tile, its element
+    // offset from the tile's first element, and the row of the tile it belongs to -- is found without
+    // a division or a table: the thread keeps the place of its chunk 0 and steps from chunk to chunk.
+    //   shared memory: the swizzle exchanges 16-byte chunks inside a 128-byte line by the line number
+    //                  modulo 8; going from chunk ci to ci + NT moves a whole number of lines, and the
+    //                  line number modulo 8 repeats with period one or two in k, so the offset of
+    //                  chunk k is k*NT*CB plus one of two per-thread constants;
+    //   global memory: chained rows: consecutive; rows that share a tile: (row, column) advance by
+    //                  (NT / cpr, NT % cpr) chunks with at most one wrap into the next row.
     constexpr int CPT = T / PC / NT;   // chunks per thread and array
-    constexpr bool kTable = CPT <= 4;
-    long long rel[kTable ? CPT : 1];   // element offset from the tile's first element
-    int key[kTable ? CPT : 1];         // chain: column inside the tile; else row inside the tile
-    const uint32_t cpr_magic = (uint32_t)((0x100000000ull + (uint32_t)cpr - 1u) / (uint32_t)cpr);   // ceil(2^32 / cpr)
-    auto locate = [&](int k, long long& r, int& ky) {
-        int ci = tid + k * NT;
-        // (without the table the values are meant to be recomputed where they are used; the empty
-        //  volatile statement keeps the compiler from hoisting all of them out of the tile loop, which
-        //  would cost three registers per chunk)
-        if constexpr (!kTable) asm volatile("" : "+r"(ci));
-        if (p.chain) {
-            ky = ci * PC;
-            r = (long long)ci * PC;
-        } else {
-            const int j = (int)__umulhi((uint32_t)ci, cpr_magic);
-            const int col = (ci - j * cpr) * PC;
-            ky = (j < p.rows_per_tile && col < p.seqlen) ? j : 0x7fffffff;
-            r = (long long)j * p.row_stride + col;
-        }
-    };
-    if constexpr (kTable) {
-#pragma unroll
-        for (int k = 0; k < CPT; ++k) locate(k, rel[k], key[k]);
-    }
-    auto place = [&](int k, long long& r, int& ky) {
-        if constexpr (kTable) {
-            r = rel[k];
-            ky = key[k];
-        } else {
-            locate(k, r, ky);
-        }
-    };
-    // byte offset of chunk ci inside a swizzled tile buffer
-    auto chunk_offset = [](int ci) -> uint32_t {
+    auto chunk_offset = [](int ci) -> uint32_t {   // byte offset of chunk ci inside a swizzled tile buffer
         const uint32_t b = (uint32_t)ci * (uint32_t)CB;
         const uint32_t c16 = b >> 4;
         return ((c16 ^ ((c16 >> 3) & 7u)) << 4) | (b & 15u);
     };
-    auto chunk_at = [&](int s_, int a, int ci) -> Chunk* {
-        return reinterpret_cast<Chunk*>(reinterpret_cast<char*>(buf(s_, a)) + chunk_offset(ci));
+    static_assert((NT * CB) % 1024 == 0 || (2 * NT * CB) % 1024 == 0, "the swizzle pattern must repeat within two steps");
+    const uint32_t soff_even = chunk_offset(tid);
+    const uint32_t soff_odd = chunk_offset(tid + NT) - (uint32_t)(NT * CB);
+    int j0 = 0, col0 = tid, step_rows = 0, step_cols = 0;
+    long long rel0 = (long long)tid * PC, step_rel = 0;
+    if (!p.chain) {
+        j0 = tid / cpr;
+        col0 = tid - j0 * cpr;
+        rel0 = (long long)j0 * p.row_stride + (long long)col0 * PC;
+        step_rows = NT / cpr;
+        step_cols = NT - step_rows * cpr;
+        step_rel = (long long)step_rows * p.row_stride + (long long)step_cols * PC;
+    }
+    const long long wrap_rel = p.row_stride - (long long)cpr * PC;   // what a wrap into the next row adds
+    // f(shared byte offset, element offset from the tile's first element, key); the chunk is inside the
+    // tile's data iff key < lim (chain: key = column inside the tile; else key = row inside the tile)
+    auto for_chunks = [&](auto&& f) {
+        if (p.chain) {
+#pragma unroll
+            for (int k = 0; k < CPT; ++k)
+                f((uint32_t)(k * NT * CB) + ((k & 1) ? soff_odd : soff_even), rel0 + (long long)k * NT * PC, (tid + k * NT) * PC);
+        } else {
+            int j = j0, col = col0;
+            long long rel = rel0;
+            // (the walk is the same for every tile; the empty volatile statement keeps the compiler from
+            //  computing all CPT places once and holding them in registers across the tile loop, which
+            //  measured slower even with four chunks per thread: the registers are worth more)
+            asm volatile("" : "+r"(j), "+r"(col), "+l"(rel));
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                f((uint32_t)(k * NT * CB) + ((k & 1) ? soff_odd : soff_even), rel,
+                  (j < p.rows_per_tile && col * PC < p.seqlen) ? j : 0x7fffffff);
+                j += step_rows;
+                col += step_cols;
+                rel += step_rel;
+                if (col >= cpr) {
+                    col -= cpr;
+                    ++j;
+                    rel += wrap_rel;
+                }
+            }
+        }
+    };
+    auto chunk_at = [&](int s_, int a, uint32_t soff) -> Chunk* {
+        return reinterpret_cast<Chunk*>(reinterpret_cast<char*>(buf(s_, a)) + soff);
     };
     // tile -> (offset of its first element, bound that key[] has to stay under)
     auto tile_base = [&](const TileCoord& tc, int& lim) -> long long {
@@ -627,37 +642,32 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
             const TileCoord tc = decode_ticket<T, ASC>(p, tk);
             int lim;
             const long long tb = tile_base(tc, lim);
-#pragma unroll
-            for (int k = 0; k < CPT; ++k) {
-                const int ci = tid + k * NT;
-                long long r;
-                int ky;
-                place(k, r, ky);
+            for_chunks([&](uint32_t soff, long long r, int ky) {
                 const long long off = tb + r;
-                Chunk* d0 = chunk_at(s, 0, ci);
-                Chunk* d1 = chunk_at(s, 1, ci);
+                Chunk* d0 = chunk_at(s, 0, soff);
+                Chunk* d1 = chunk_at(s, 1, soff);
                 if (ky < lim) {
                     if constexpr (CB == 16) {
                         ptx::cp_async_16(d0, gin0 + off);
                         ptx::cp_async_16(d1, gc + off);
-                        if (BWD) ptx::cp_async_16(chunk_at(s, 2, ci), gy + off);
+                        if (BWD) ptx::cp_async_16(chunk_at(s, 2, soff), gy + off);
                     } else {
                         ptx::cp_async_4(d0, gin0 + off);
                         ptx::cp_async_4(d1, gc + off);
-                        if (BWD) ptx::cp_async_4(chunk_at(s, 2, ci), gy + off);
+                        if (BWD) ptx::cp_async_4(chunk_at(s, 2, soff), gy + off);
                     }
                 } else {
                     if constexpr (CB == 16) {
                         *d0 = make_uint4(0u, 0u, 0u, 0u);
                         *d1 = p.logc ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(kOne, kOne, kOne, kOne);
-                        if (BWD) *chunk_at(s, 2, ci) = make_uint4(0u, 0u, 0u, 0u);
+                        if (BWD) *chunk_at(s, 2, soff) = make_uint4(0u, 0u, 0u, 0u);
                     } else {
                         *d0 = 0u;
                         *d1 = p.logc ? 0u : kOne;
-                        if (BWD) *chunk_at(s, 2, ci) = 0u;
+                        if (BWD) *chunk_at(s, 2, soff) = 0u;
                     }
                 }
-            }
+            });
             if (with_halo && tid < 2) {
                 const long long rb = tc.row * p.row_stride;
                 const long long lo = (long long)tc.piece * T - 1, hi = (long long)tc.piece * T + T;
@@ -746,18 +756,13 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
         {
             int lim;
             const long long tb = tile_base(tc, lim);
-#pragma unroll
-            for (int k = 0; k < CPT; ++k) {
-                long long r;
-                int ky;
-                place(k, r, ky);
+            for_chunks([&](uint32_t soff, long long r, int ky) {
                 if (ky < lim) {
-                    const int ci = tid + k * NT;
                     const long long off = tb + r;
-                    *reinterpret_cast<Chunk*>(gout0 + off) = *chunk_at(s, 0, ci);
-                    if (BWD) *reinterpret_cast<Chunk*>(gout1 + off) = *chunk_at(s, 2, ci);
+                    *reinterpret_cast<Chunk*>(gout0 + off) = *chunk_at(s, 0, soff);
+                    if (BWD) *reinterpret_cast<Chunk*>(gout1 + off) = *chunk_at(s, 2, soff);
                 }
-            }
+            });
         }
         __syncthreads();   // the slot has been read out: refill it
         issue(s, tile_of_stage[s]);
