@@ -182,6 +182,36 @@ def test_padded_rows_stay_inside_their_allocation(rev):
     linrec_b200.check_status()
 
 
+@pytest.mark.parametrize("rev", [False, True])
+def test_fixup_follows_a_carry_through_a_dip(rev):
+    """The operator does not restrict its coefficients: a carry may shrink below the normal range
+    (39 steps of c = 0.1) and grow back (39 steps of c = 10).  The fix-up walk must not give up while
+    the carried value is merely tiny -- only at exact zero.  The second shard has x = 0, so everything
+    it holds IS the correction."""
+    from linrec_b200.sharded import CudaShardKernels
+    k = CudaShardKernels()
+    dev = torch.device("cuda:0")
+    rows, Ls, G = 4, 256, 2
+    g = torch.Generator(device="cpu").manual_seed(3)
+    x = torch.randn(rows, G * Ls, generator=g)
+    c = 0.5 + 0.5 * torch.rand(rows, G * Ls, generator=g)
+    dip = torch.cat([torch.full((39,), 0.1), torch.full((39,), 10.0), torch.full((Ls - 78,), 0.9)])
+    second = slice(0, Ls) if rev else slice(Ls, 2 * Ls)          # the shard that comes second in scan order
+    x[:, second] = 0.0
+    c[:, second] = dip.flip(0) if rev else dip
+    cut = lambda t, s: t[:, s * Ls:(s + 1) * Ls].contiguous().to(dev)
+    ys, recs = zip(*[k.fwd_carry(cut(x, s), cut(c, s), rev, s, G) for s in range(G)])
+    gathered = torch.stack(recs).contiguous()
+    for s in range(G):
+        k.fwd_fixup(ys[s], cut(c, s), gathered, rev, s, G)
+    y = torch.cat([t.cpu() for t in ys], dim=1).numpy()
+    y64 = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
+    # at the bottom of the dip the values are subnormal and keep only ~19 bits: rtol 1e-4 holds, atol does not apply
+    np.testing.assert_allclose(y, y64, rtol=1e-4, atol=1e-37)
+    far = y[:, 0] if rev else y[:, -1]
+    assert np.all(np.abs(far) > 1e-12), "the carry was dropped inside the dip"
+
+
 def test_wait_for_a_peer_gives_up_with_status():
     """The fix-up phase of the peer-store path is run for shard 1 without anybody ever pushing shard
     0's records: its bounded waits (option peerWaitBudgetMs, 20 ms here) must run out by themselves,
