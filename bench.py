@@ -745,13 +745,13 @@ def _cfg5(ctx, linrec_b200, fwd, bwd, peak, steps):
             e[1].record()
             gathered = sharded._gather(rec, None)
             e[2].record()
-            kern.fwd_fixup(Y, Cc, gathered, False, rank, world)
+            kern.fwd_fixup(X, Y, Cc, gathered, False, rank, world)
             e[3].record()
-            _, _, rec, _, _ = kern.bwd_carry(DY, Cc, Y, False, rank, world, out=(DX, DC))
+            _, _, rec, _, _, _ = kern.bwd_carry(DY, Cc, Y, False, rank, world, out=(DX, DC))
             e[4].record()
             gathered = sharded._gather(rec, None)
             e[5].record()
-            kern.bwd_fixup(DX, DC, Cc, Y, gathered, False, rank, world)
+            kern.bwd_fixup(DY, DX, DC, Cc, Y, gathered, False, rank, world)
             e[6].record()
             ctx.barrier()
             for i, n in enumerate(ph):

@@ -135,16 +135,19 @@ LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
  *                                                y at the shard's scan-first element).
  *   2. the caller gathers the records of all shards in shard order into
  *      gathered[(s*numseq + r)*rec + k]   (one all-gather; rec = 2 forward, 4 backward);
- *   3. *_fixup   folds the records of the shards that come earlier in scan order and adds
- *                carry * running product of the coefficients to this shard's results in place.  The
- *                walk along a row stops once the carried value has underflowed to exactly zero.
+ *   3. *_fixup   folds the records of the shards that come earlier in scan order into the carry that
+ *                enters this shard and computes the head of the shard AGAIN from its operands and that
+ *                carry (x, c -> y; dy, c, y -> dx, dc), as far along each row as the carry can still
+ *                change a result: until carry * running product of the coefficients is exactly zero.
+ *                Recomputing instead of adding a correction rounds each result to the storage type
+ *                once, as the unsharded scan does.
  * `reverse` is the flag of the forward pass in all four. */
 LINREC_API int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
                                      int reverse, int dtype, int shard, int nshards,
                                      const linrec_opts* opts,
                                      void* workspace, size_t workspace_bytes, void* stream);
-LINREC_API int linrec_b200_fwd_fixup(void* y, const void* c, const float* gathered,
+LINREC_API int linrec_b200_fwd_fixup(const void* x, void* y, const void* c, const float* gathered,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
                                      int reverse, int dtype, int shard, int nshards, void* stream);
 LINREC_API int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx, void* dc,
@@ -153,7 +156,7 @@ LINREC_API int linrec_b200_bwd_carry(const void* dy, const void* c, const void* 
                                      int reverse, int dtype, int shard, int nshards,
                                      const linrec_opts* opts,
                                      void* workspace, size_t workspace_bytes, void* stream);
-LINREC_API int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y,
+LINREC_API int linrec_b200_bwd_fixup(const void* dy, void* dx, void* dc, const void* c, const void* y,
                                      const float* gathered,
                                      int64_t numseq, int64_t seqlen, int64_t row_stride,
                                      int reverse, int dtype, int shard, int nshards, void* stream);
@@ -268,7 +271,7 @@ LINREC_API const char* linrec_b200_last_cuda_error(void);
 /* Text for a status code. */
 LINREC_API const char* linrec_b200_strerror(int code);
 
-/* Library version, e.g. 100 for 0.1.0. */
+/* Library version, e.g. 200 for 0.2.0 (0.2.0 changed the fix-up entry points: they take the operands x / dy). */
 LINREC_API int linrec_b200_version(void);
 
 #ifdef __cplusplus

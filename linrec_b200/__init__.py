@@ -25,5 +25,5 @@ from .general import linrec_general  # noqa: E402,F401
 
 linrec = linrec_pipe
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 __all__ = ["linrec", "linrec_ref", "linrec_tile", "linrec_pipe", "linrec_general", "check_status"]

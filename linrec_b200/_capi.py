@@ -64,11 +64,11 @@ def _load() -> ctypes.CDLL:
     lib.linrec_b200_config_list.restype = i32
     lib.linrec_b200_fwd_carry.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, po, vp, sz, vp]
     lib.linrec_b200_fwd_carry.restype = i32
-    lib.linrec_b200_fwd_fixup.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
+    lib.linrec_b200_fwd_fixup.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
     lib.linrec_b200_fwd_fixup.restype = i32
     lib.linrec_b200_bwd_carry.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, po, vp, sz, vp]
     lib.linrec_b200_bwd_carry.restype = i32
-    lib.linrec_b200_bwd_fixup.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
+    lib.linrec_b200_bwd_fixup.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
     lib.linrec_b200_bwd_fixup.restype = i32
     pp = ctypes.POINTER(ctypes.c_void_p)
     lib.linrec_b200_exchange_size.argtypes = [i64, i32]

@@ -684,7 +684,7 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
     long long grid = fp.numseq < (long long)sm_count * 8 ? fp.numseq : (long long)sm_count * 8;
     // 16-byte accesses need aligned rows whose length is a multiple of the 8 elements a thread takes
     auto al = [](const void* q) { return q == nullptr || reinterpret_cast<uintptr_t>(q) % 16 == 0; };
-    const bool vec = al(fp.out0) && al(fp.out1) && al(fp.c) && al(fp.yin) && fp.seqlen % 8 == 0 &&
+    const bool vec = al(fp.out0) && al(fp.out1) && al(fp.in0) && al(fp.c) && al(fp.yin) && fp.seqlen % 8 == 0 &&
                      (fp.row_stride * (long long)sizeof(ST)) % 16 == 0;
     const unsigned g = (unsigned)grid;
 #define LINREC_FIXUP(B, A, V) linrec::linrec_fixup_kernel<ST, NT, B, A, V><<<g, NT, 0, stream>>>(fp)
@@ -700,15 +700,15 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
     return launch_result("kernel launch");
 }
 
-int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yin, const float* carries,
+int launch_fixup(bool bwd, const void* in0, void* out0, void* out1, const void* c, const void* yin, const float* carries,
                  const void* px, uint32_t px_epoch, uint32_t* status_word, int peer_wait_budget_ms, int64_t numseq,
                  int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream_,
                  int super_chunks = 0)
 {
-    const void* ptrs[5] = {out0, c, carries, bwd ? out1 : out0, bwd ? yin : c};
+    const void* ptrs[5] = {out0, c, in0, bwd ? out1 : out0, bwd ? yin : c};
     if (!carries && !px && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     if (dtype == LINREC_DTYPE_F64) return LINREC_ERR_NOT_IMPLEMENTED;
-    int rc = check_common(ptrs, 2, numseq, seqlen, row_stride, dtype);
+    int rc = check_common(ptrs, 3, numseq, seqlen, row_stride, dtype);
     if (rc != LINREC_OK) return rc;
     if (bwd && (!out1 || !yin) && numseq > 0 && seqlen > 0) return LINREC_ERR_INVALID_ARG;
     if (nshards < 1 || shard < 0 || shard >= nshards) return LINREC_ERR_INVALID_ARG;
@@ -721,7 +721,7 @@ int launch_fixup(bool bwd, void* out0, void* out1, const void* c, const void* yi
     rc = device_info(dev);
     if (rc != LINREC_OK) return rc;
     linrec::FixupParams fp{};
-    fp.out0 = out0; fp.out1 = out1; fp.c = c; fp.yin = yin; fp.carries = carries;
+    fp.out0 = out0; fp.out1 = out1; fp.in0 = in0; fp.c = c; fp.yin = yin; fp.carries = carries;
     fp.numseq = numseq; fp.seqlen = seqlen; fp.row_stride = row_stride;
     fp.shard = shard; fp.nshards = nshards; fp.rec = bwd ? 4 : 2;
     fp.super_chunks = super_chunks;
@@ -757,10 +757,7 @@ int pick_super_chunks(int kind, int dtype, int64_t numseq, int64_t seqlen, int64
                       int nptrs, const Options& opt, bool plain)
 {
     if (opt.super_chunks == 0 || opt.super_chunks == 1) return 1;
-    // fp32 only: the fix-up adds its correction to a result that has already been rounded to the
-    // storage type, and for 2-byte storage that second rounding shows where the correction cancels
-    // most of the local value
-    if (!plain || kind != LINREC_KIND_PIPE || opt.logc || dtype != LINREC_DTYPE_F32) return 1;
+    if (!plain || kind != LINREC_KIND_PIPE || opt.logc || dtype == LINREC_DTYPE_F64) return 1;
     if (opt.memcode >= 0 && opt.memcode != 1) return 1;
     if (numseq <= 0 || seqlen <= 0 || (row_stride != seqlen && numseq != 1)) return 1;
     int64_t V = 1;
@@ -797,8 +794,8 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
             const int rc = launch_scan_direct(kind, bwd, in0, c, yin, out0, out1, records, bwd ? 4 : 2, 0, nullptr, 0u, ns, len,
                                               len, reverse, dtype, opts, workspace, main_bytes, stream, V);
             if (rc == LINREC_OK)
-                return launch_fixup(bwd, out0, out1, c, yin, records, nullptr, 0u, nullptr, 0, ns, len, len, reverse, dtype, 0,
-                                    V, stream, V);
+                return launch_fixup(bwd, in0, out0, out1, c, yin, records, nullptr, 0u, nullptr, 0, ns, len, len, reverse, dtype,
+                                    0, V, stream, V);
             if (rc != LINREC_ERR_WORKSPACE) return rc;
             // the workspace holds the plain scan but not the records as well: scan the rows as they are
         }
@@ -1201,10 +1198,10 @@ int linrec_b200_fwd_carry(const void* x, const void* c, void* y, float* records,
                        reverse, dtype, opts, workspace, workspace_bytes, stream);
 }
 
-int linrec_b200_fwd_fixup(void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
+int linrec_b200_fwd_fixup(const void* x, void* y, const void* c, const float* records, int64_t numseq, int64_t seqlen,
                           int64_t row_stride, int reverse, int dtype, int shard, int nshards, void* stream)
 {
-    return launch_fixup(false, y, nullptr, c, nullptr, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype,
+    return launch_fixup(false, x, y, nullptr, c, nullptr, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype,
                         shard, nshards, stream);
 }
 
@@ -1221,11 +1218,11 @@ int linrec_b200_bwd_carry(const void* dy, const void* c, const void* y, void* dx
                        reverse, dtype, opts, workspace, workspace_bytes, stream_);
 }
 
-int linrec_b200_bwd_fixup(void* dx, void* dc, const void* c, const void* y, const float* records, int64_t numseq,
-                          int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
+int linrec_b200_bwd_fixup(const void* dy, void* dx, void* dc, const void* c, const void* y, const float* records,
+                          int64_t numseq, int64_t seqlen, int64_t row_stride, int reverse, int dtype, int shard, int nshards,
                           void* stream)
 {
-    return launch_fixup(true, dx, dc, c, y, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
+    return launch_fixup(true, dy, dx, dc, c, y, records, nullptr, 0u, nullptr, 0, numseq, seqlen, row_stride, reverse, dtype, shard, nshards,
                         stream);
 }
 
@@ -1271,7 +1268,7 @@ int linrec_b200_fwd_seq_p2p(const void* x, const void* c, void* y, int64_t numse
         rc = launch_scan(LINREC_KIND_PIPE, false, x, c, nullptr, y, nullptr, nullptr, 0, open, exchange, epoch, numseq, seqlen,
                          row_stride, reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(false, y, nullptr, c, nullptr, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
+    return launch_fixup(false, x, y, nullptr, c, nullptr, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
                         opt.peer_wait_budget_ms, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
 
@@ -1291,7 +1288,7 @@ int linrec_b200_bwd_seq_p2p(const void* dy, const void* c, const void* y, void* 
         rc = launch_scan(LINREC_KIND_PIPE, true, dy, c, y, dx, dc, nullptr, 0, open, exchange, epoch, numseq, seqlen, row_stride,
                          reverse, dtype, opts, workspace, workspace_bytes, stream);
     if (rc != LINREC_OK || numseq == 0 || seqlen == 0 || opt.p2p_phase == 1) return rc;
-    return launch_fixup(true, dx, dc, c, y, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
+    return launch_fixup(true, dy, dx, dc, c, y, nullptr, exchange, epoch, static_cast<uint32_t*>(workspace) + 1,
                         opt.peer_wait_budget_ms, numseq, seqlen, row_stride, reverse, dtype, shard, nshards, stream);
 }
 
@@ -1388,6 +1385,6 @@ const char* linrec_b200_strerror(int code)
     }
 }
 
-int linrec_b200_version(void) { return 100; }
+int linrec_b200_version(void) { return 200; }
 
 }  // extern "C"

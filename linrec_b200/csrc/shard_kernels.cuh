@@ -9,9 +9,9 @@
 //      need, c at the shard's scan-last element and y at its scan-first element;
 //   3. the records of all shards are all-gathered (NCCL) into local memory;
 //   4. a fix-up kernel folds the records of the shards that come earlier in scan order into the
-//      carry v that enters this shard, and adds v * (running product of the coefficients) to the
-//      shard's results.  The walk along a row stops as soon as the running value is exactly zero
-//      (underflow of carry * product): from there on every correction is zero.
+//      carry v that enters this shard, and computes the head of the shard again from that carry.
+//      The walk along a row stops as soon as v * (running product of the coefficients) is exactly
+//      zero: from there on the local results are the true ones.
 //
 // Carry records are fp32: forward 2 floats per row (P, Y); backward 4 floats (P, Y, c_edge, y_edge).
 #pragma once
@@ -20,8 +20,9 @@
 namespace linrec {
 
 struct FixupParams {
-    void* out0;          // forward: y        backward: dx      (updated in place)
-    void* out1;          // backward: dc      (updated in place)
+    void* out0;          // forward: y        backward: dx      (the head of every row is written again)
+    void* out1;          // backward: dc
+    const void* in0;     // forward: x        backward: dy
     const void* c;
     const void* yin;     // backward: forward outputs
     const float* carries;   // [nshards][numseq][rec] gathered records
@@ -110,21 +111,30 @@ __device__ __forceinline__ void store8(ST* row, long long m0, long long seqlen, 
 // What one thread needs for one step of the walk, in MEMORY order (8 consecutive elements).
 template <bool BWD>
 struct FixupStep {
+    float a[8];              // additive term: x (forward) / dy (backward)
     float c[8];              // forward: c of the element; backward: c of the scan predecessor
-    float o0[8];             // current y (forward) / dx (backward)
-    float o1[BWD ? 8 : 1];   // backward: dc (recomputed from the corrected dx, never read)
     float ys[BWD ? 8 : 1];   // backward: y of the scan successor
     long long m0;            // memory index of element 0
 };
 
-// One CTA per row (grid-stride over rows).  Every thread handles 8 consecutive elements per step,
-// a step covers NT*8 elements in scan order; the operands of the next step are requested before
-// the current step is worked on, so the walk runs at one DRAM round trip per step at most.
+// One CTA per row (grid-stride over rows).  The head of the row -- as far as the carry that enters it
+// can still change a result -- is COMPUTED AGAIN from its operands with the true carry, not patched:
+// every thread handles 8 consecutive elements per step, a step covers NT*8 elements in scan order and
+// is a block scan of (Y, P) pairs like a tile of the scan kernels (thread aggregate, warp scan by
+// shuffles, cross-warp fold through shared memory, rerun of the 8 elements from the true carry).  So
+// each result is rounded to the storage type once, exactly as the unsharded scan rounds it; adding a
+// correction to the stored local result would round 2-byte results twice, and where the correction
+// cancels most of the local value that shows.  Same traffic as patching: forward reads x, c and writes
+// y (patching read y, c), backward reads dy, c, y and writes dx, dc.  The operands of the next step are
+// requested before the current step is worked on, so the walk runs at one DRAM round trip per step.
+//
+// The walk ends once the DIFFERENCE between the true and the local carry, d = v_in * (product of c so
+// far), is exactly zero: from there on the local results are the true ones.
 template <typename ST, int NT, bool BWD, bool ASC, bool VEC>
 __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
 {
     constexpr int V = 8, NW = NT / 32, STEP = NT * V;
-    __shared__ float wprod[2][NW];
+    __shared__ Pair wagg[2][NW];
     __shared__ float v_in_s;
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
     const long long L = p.seqlen;
@@ -151,10 +161,12 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             v_in_s = v;
         }
         __syncthreads();
-        float v = v_in_s;
+        float v = v_in_s;    // true value that enters the next step
+        float d = v;         // what the local scan (which started from zero) is off by at that point
         const long long rb = row * p.row_stride;
         ST* o0 = reinterpret_cast<ST*>(p.out0) + rb;
         ST* o1 = BWD ? reinterpret_cast<ST*>(p.out1) + rb : nullptr;
+        const ST* in0 = reinterpret_cast<const ST*>(p.in0) + rb;
         const ST* c = reinterpret_cast<const ST*>(p.c) + rb;
         const ST* y = BWD ? reinterpret_cast<const ST*>(p.yin) + rb : nullptr;
 
@@ -163,7 +175,7 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             const long long n0 = base + (long long)tid * V;          // first scan position of the thread
             st.m0 = ASC ? n0 : L - n0 - V;                            // lowest memory index of its 8 elements
             if (n0 >= L) return;                                      // nothing of this thread is in range
-            load8<ST, VEC>(o0, st.m0, L, 0.0f, st.o0);
+            load8<ST, VEC>(in0, st.m0, L, 0.0f, st.a);
             float cr[8];
             load8<ST, VEC>(c, st.m0, L, 1.0f, cr);
             if constexpr (!BWD) {
@@ -193,54 +205,62 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
         };
 
         FixupStep<BWD> cur, nxt;
-        if (fixup_carry_alive(v)) fetch(0, cur);
+        if (fixup_carry_alive(d)) fetch(0, cur);
         int par = 0;
-        for (long long base = 0; base < L && fixup_carry_alive(v); base += STEP, par ^= 1) {
+        for (long long base = 0; base < L && fixup_carry_alive(d); base += STEP, par ^= 1) {
             if (base + STEP < L) fetch(base + STEP, nxt);
             const long long n0 = base + (long long)tid * V;
-            // coefficients in scan order; identity outside the shard
-            float cc[8];
+            // operands in scan order; identity elements outside the shard
+            float cc[8], xx[8];
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
                 const int j = ASC ? jj : 7 - jj;
-                cc[jj] = (n0 + jj < L) ? cur.c[j] : 1.0f;
+                const bool in = n0 + jj < L;
+                cc[jj] = in ? cur.c[j] : 1.0f;
+                xx[jj] = in ? cur.a[j] : 0.0f;
             }
-            float pr[8];
-            pr[0] = cc[0];
+            Pair inc = pair_identity();
 #pragma unroll
-            for (int jj = 1; jj < 8; ++jj) pr[jj] = pr[jj - 1] * cc[jj];
-            float incl = pr[7];
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const float t = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl *= t;
+            for (int jj = 0; jj < 8; ++jj) {
+                inc.y = fmaf(inc.y, cc[jj], xx[jj]);
+                inc.p *= cc[jj];
             }
-            float excl = __shfl_up_sync(0xffffffffu, incl, 1);
-            if (lane == 0) excl = 1.0f;
-            if (lane == 31) wprod[par][w] = incl;
-            __syncthreads();   // (the other half of wprod belongs to the previous step: no second barrier)
-            float before = 1.0f, total = 1.0f;
+#pragma unroll
+            for (int dd = 1; dd < 32; dd <<= 1) {
+                Pair far;
+                far.y = __shfl_up_sync(0xffffffffu, inc.y, dd);
+                far.p = __shfl_up_sync(0xffffffffu, inc.p, dd);
+                if (lane >= dd) inc = combine(far, inc);
+            }
+            Pair ex;
+            ex.y = __shfl_up_sync(0xffffffffu, inc.y, 1);
+            ex.p = __shfl_up_sync(0xffffffffu, inc.p, 1);
+            if (lane == 0) ex = pair_identity();
+            if (lane == 31) wagg[par][w] = inc;
+            __syncthreads();   // (the other half of wagg belongs to the previous step: no second barrier)
+            Pair before = pair_identity(), total = pair_identity();
 #pragma unroll
             for (int k = 0; k < NW; ++k) {
-                const float t = wprod[par][k];
-                if (k < w) before *= t;
-                total *= t;
+                const Pair t = wagg[par][k];
+                if (k < w) before = combine(before, t);
+                total = combine(total, t);
             }
-            const float zin = v * before * excl;   // value that enters this thread's first element
+            const Pair pre = combine(before, ex);        // what precedes this thread inside the step
             if (n0 < L) {
+                float val = fmaf(v, pre.p, pre.y);       // true value that enters the thread's first element
+                float r0[8], r1[BWD ? 8 : 1];
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
                     const int j = ASC ? jj : 7 - jj;
-                    const float z = zin * pr[jj];
-                    cur.o0[j] += z;
-                    // dc is dx * y at the scan successor by definition: formed again from the corrected dx
-                    // (exactly what the scan kernel computes; the stored dc need not be read)
-                    if constexpr (BWD) cur.o1[j] = cur.o0[j] * cur.ys[j];
+                    val = fmaf(val, cc[jj], xx[jj]);
+                    r0[j] = val;
+                    if constexpr (BWD) r1[j] = val * cur.ys[j];   // dc = dx * y at the scan successor
                 }
-                store8<ST, VEC>(o0, cur.m0, L, cur.o0);
-                if constexpr (BWD) store8<ST, VEC>(o1, cur.m0, L, cur.o1);
+                store8<ST, VEC>(o0, cur.m0, L, r0);
+                if constexpr (BWD) store8<ST, VEC>(o1, cur.m0, L, r1);
             }
-            v = v * total;
+            v = fmaf(v, total.p, total.y);
+            d *= total.p;
             cur = nxt;
         }
         if constexpr (BWD) {
@@ -254,7 +274,7 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
                 o1[last] = Storage<ST>::from_float(Storage<ST>::to_float(o0[last]) * y_edge);
             }
         }
-        __syncthreads();   // v_in_s and wprod are rewritten for the next row
+        __syncthreads();   // v_in_s and wagg are rewritten for the next row
     }
     // Peer exchange: once every CTA of this rank is done reading, tell all ranks that the slots of
     // this epoch may be reused (they will be, two epochs from now).

@@ -79,12 +79,12 @@ class CudaShardKernels:
         _capi.raise_for(rc, "linrec_b200_fwd_carry")
         return y, rec
 
-    def fwd_fixup(self, y, c, gathered, reverse, shard, nshards):
+    def fwd_fixup(self, x, y, c, gathered, reverse, shard, nshards):
         numseq, seqlen, stride = _row_layout(y)
         with torch.cuda.device(y.device):
             stream = torch.cuda.current_stream(y.device).cuda_stream
-            rc = _capi.lib.linrec_b200_fwd_fixup(y.data_ptr(), c.data_ptr(), gathered.data_ptr(), numseq, seqlen, stride,
-                                                 int(bool(reverse)), _DTYPES[y.dtype], shard, nshards, stream)
+            rc = _capi.lib.linrec_b200_fwd_fixup(x.data_ptr(), y.data_ptr(), c.data_ptr(), gathered.data_ptr(), numseq, seqlen,
+                                                 stride, int(bool(reverse)), _DTYPES[y.dtype], shard, nshards, stream)
         _capi.raise_for(rc, "linrec_b200_fwd_fixup")
 
     def bwd_carry(self, dy, c, y, reverse, shard, nshards, out=None):
@@ -97,13 +97,13 @@ class CudaShardKernels:
                                                  rec.data_ptr(), numseq, seqlen, stride, int(bool(reverse)), dtype,
                                                  shard, nshards, None, ws.data_ptr(), ws.numel(), stream)
         _capi.raise_for(rc, "linrec_b200_bwd_carry")
-        return dx, dc, rec, c, y
+        return dx, dc, rec, c, y, dy
 
-    def bwd_fixup(self, dx, dc, c, y, gathered, reverse, shard, nshards):
+    def bwd_fixup(self, dy, dx, dc, c, y, gathered, reverse, shard, nshards):
         numseq, seqlen, stride = _row_layout(dx)
         with torch.cuda.device(dx.device):
             stream = torch.cuda.current_stream(dx.device).cuda_stream
-            rc = _capi.lib.linrec_b200_bwd_fixup(dx.data_ptr(), dc.data_ptr(), c.data_ptr(), y.data_ptr(),
+            rc = _capi.lib.linrec_b200_bwd_fixup(dy.data_ptr(), dx.data_ptr(), dc.data_ptr(), c.data_ptr(), y.data_ptr(),
                                                  gathered.data_ptr(), numseq, seqlen, stride, int(bool(reverse)),
                                                  _DTYPES[dx.dtype], shard, nshards, stream)
         _capi.raise_for(rc, "linrec_b200_bwd_fixup")
@@ -240,7 +240,8 @@ def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, gro
     y, rec = k.fwd_carry(x, c, reverse, shard, nshards, **kw)
     if nshards > 1:
         gathered = _gather(rec, group)
-        k.fwd_fixup(y, c if c.stride() == y.stride() else c.contiguous(), gathered, reverse, shard, nshards)
+        same = lambda t: t if t.stride() == y.stride() else t.contiguous()
+        k.fwd_fixup(same(x), y, same(c), gathered, reverse, shard, nshards)
     return y
 
 
@@ -253,10 +254,10 @@ def seq_sharded_bwd(dy: torch.Tensor, c: torch.Tensor, y: torch.Tensor, reverse:
         return exchange.bwd(dy, c, y, reverse, **kw)
     k = kernels or _CUDA_KERNELS
     shard, nshards = dist.get_rank(group), dist.get_world_size(group)
-    dx, dc, rec, c2, y2 = k.bwd_carry(dy, c, y, reverse, shard, nshards, **kw)
+    dx, dc, rec, c2, y2, dy2 = k.bwd_carry(dy, c, y, reverse, shard, nshards, **kw)
     if nshards > 1:
         gathered = _gather(rec, group)
-        k.bwd_fixup(dx, dc, c2, y2, gathered, reverse, shard, nshards)
+        k.bwd_fixup(dy2, dx, dc, c2, y2, gathered, reverse, shard, nshards)
     return dx, dc
 
 

@@ -39,7 +39,7 @@ class NumpyShardKernels:
         y, P, Y = self._scan(x.numpy().astype(np.float64), c.numpy().astype(np.float64), asc, not holds_start)
         return torch.from_numpy(y), torch.from_numpy(np.stack([P, Y], -1).astype(np.float32))
 
-    def fwd_fixup(self, y, c, gathered, reverse, shard, nshards):
+    def fwd_fixup(self, x, y, c, gathered, reverse, shard, nshards):
         asc = not reverse
         order = list(range(nshards)) if asc else list(range(nshards - 1, -1, -1))
         g = gathered.numpy().astype(np.float64)
@@ -68,9 +68,9 @@ class NumpyShardKernels:
         dc = dx * ys
         first, last = (0, L - 1) if asc else (L - 1, 0)
         rec = np.stack([P, Y, cn[:, last], yn[:, first]], -1).astype(np.float32)
-        return torch.from_numpy(dx), torch.from_numpy(dc), torch.from_numpy(rec), c, y
+        return torch.from_numpy(dx), torch.from_numpy(dc), torch.from_numpy(rec), c, y, dy
 
-    def bwd_fixup(self, dx, dc, c, y, gathered, reverse, shard, nshards):
+    def bwd_fixup(self, dy, dx, dc, c, y, gathered, reverse, shard, nshards):
         asc = bool(reverse)
         order = list(range(nshards)) if asc else list(range(nshards - 1, -1, -1))
         pos = order.index(shard)

@@ -57,7 +57,7 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
     ys, recs = zip(*[k.fwd_carry(xs[s], cs[s], rev, s, G) for s in range(G)])
     gathered = torch.stack(recs).contiguous()
     for s in range(G):
-        k.fwd_fixup(ys[s], cs[s], gathered, rev, s, G)
+        k.fwd_fixup(xs[s], ys[s], cs[s], gathered, rev, s, G)
     y = torch.cat([t.cpu() for t in ys], dim=1).numpy()
     y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
     y64 = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
@@ -73,7 +73,7 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
     outs = [k.bwd_carry(dys[s], cs[s], yg[s], rev, s, G) for s in range(G)]
     gathered = torch.stack([o[2] for o in outs]).contiguous()
     for s in range(G):
-        k.bwd_fixup(outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
+        k.bwd_fixup(dys[s], outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
     dx = torch.cat([o[0].cpu() for o in outs], dim=1).numpy()
     dc = torch.cat([o[1].cpu() for o in outs], dim=1).numpy()
     if clo < 0.99:
@@ -165,7 +165,7 @@ def test_padded_rows_stay_inside_their_allocation(rev):
         assert y.stride() == (stride, 1) and y.untyped_storage().nbytes() >= ((rows - 1) * stride + Ls) * 4
     gathered = torch.stack(recs).contiguous()
     for s in range(G):
-        k.fwd_fixup(ys[s], cs[s], gathered, rev, s, G)
+        k.fwd_fixup(xs[s], ys[s], cs[s], gathered, rev, s, G)
     y_ref = oracle.fwd_f32(x.numpy(), c.numpy(), reverse=rev)
     np.testing.assert_allclose(torch.cat([t.cpu() for t in ys], dim=1).numpy(), y_ref, rtol=RTOL, atol=ATOL)
     yg = [padded(torch.from_numpy(y_ref[:, s * Ls:(s + 1) * Ls])) for s in range(G)]
@@ -173,7 +173,7 @@ def test_padded_rows_stay_inside_their_allocation(rev):
     gathered = torch.stack([o[2] for o in outs]).contiguous()
     for s in range(G):
         assert outs[s][0].stride() == (stride, 1) and outs[s][1].stride() == (stride, 1)
-        k.bwd_fixup(outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
+        k.bwd_fixup(dys[s], outs[s][0], outs[s][1], cs[s], yg[s], gathered, rev, s, G)
     dx_ref, dc_ref = oracle.bwd_f32(dy.numpy(), c.numpy(), y_ref, reverse=rev)
     np.testing.assert_allclose(torch.cat([o[0].cpu() for o in outs], dim=1).numpy(), dx_ref, rtol=RTOL, atol=ATOL)
     np.testing.assert_allclose(torch.cat([o[1].cpu() for o in outs], dim=1).numpy(), dc_ref, rtol=RTOL,
@@ -203,7 +203,7 @@ def test_fixup_follows_a_carry_through_a_dip(rev):
     ys, recs = zip(*[k.fwd_carry(cut(x, s), cut(c, s), rev, s, G) for s in range(G)])
     gathered = torch.stack(recs).contiguous()
     for s in range(G):
-        k.fwd_fixup(ys[s], cut(c, s), gathered, rev, s, G)
+        k.fwd_fixup(cut(x, s), ys[s], cut(c, s), gathered, rev, s, G)
     y = torch.cat([t.cpu() for t in ys], dim=1).numpy()
     y64 = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
     # at the bottom of the dip the values are subnormal and keep only ~19 bits: rtol 1e-4 holds, atol does not apply
