@@ -127,6 +127,8 @@ struct FixupStep {
 // cancels most of the local value that shows.  Same traffic as patching: forward reads x, c and writes
 // y (patching read y, c), backward reads dy, c, y and writes dx, dc.  The operands of the next step are
 // requested before the current step is worked on, so the walk runs at one DRAM round trip per step.
+// (Two steps ahead, with three operand sets taking turns, was measured and lost: the registers cost
+// more resident CTAs than the extra step in flight gives back; 128 threads per CTA beat 256.)
 //
 // The walk ends once the DIFFERENCE between the true and the local carry, d = v_in * (product of c so
 // far), is exactly zero: from there on the local results are the true ones.
