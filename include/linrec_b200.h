@@ -248,7 +248,12 @@ LINREC_API int linrec_b200_static_workspace(void** workspace, size_t* bytes);
  * (they are interchangeable), and hold linrec_b200_dim_workspace_size(...) bytes for the same
  * arguments and options; that size query returns 0 for options no compiled variant matches.
  * Options: kThreadsPerBlock, kRowsPerChunk, kStages pin a variant; kChunksPerJob (0 = a whole column
- * per job) sets how finely a column is cut into jobs that are linked by look-back carries. */
+ * per job) sets how finely a column is cut into jobs that are linked by look-back carries.
+ * Performance note: the kernel gets its parallelism from the columns (one column = 32 channel words of
+ * one batch entry).  With fewer than 64 columns the sequence axis has to supply it through per-thread
+ * look-back, which is latency-bound (0.7-1.5 TB/s on B200 against 6.5 TB/s with many columns); a caller
+ * that can afford transposed copies is better off with the last-axis entry points there (the Python
+ * wrapper linrec_general does that below 128 columns). */
 LINREC_API size_t linrec_b200_dim_workspace_size(int bwd, int64_t nb, int64_t seqlen, int64_t nchan,
                                                  int dtype, const linrec_opts* opts);
 LINREC_API int linrec_b200_fwd_dim(const void* x, const void* c, void* y,
