@@ -13,6 +13,7 @@
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 #include "../../include/linrec_b200.h"
@@ -41,6 +42,24 @@ int launch_result(const char* where)
     return LINREC_ERR_CUDA;
 }
 
+// Launch with (or without) the programmatic-stream-serialization attribute: the kernels that take it
+// call griddepcontrol.wait before their first access to global memory (ptx.cuh).
+template <typename... KArgs, typename... Args>
+void launch_kernel(void (*fn)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream, bool pdl, Args&&... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = pdl ? attr : nullptr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, fn, std::forward<Args>(args)...);   // the caller reads cudaGetLastError
+}
+
 // ---- options -------------------------------------------------------------------------------------
 // Compile-time configuration names (the counterpart of CONFIG_NAMES, linrec/impl/cuda/linrec.h:8).
 const char* const kConfigNames[] = {"kElemsPerThread", "kThreadsPerBlock", "kStages", "kOutBuffers", "memcode"};
@@ -63,6 +82,8 @@ struct Options {
     int logc = 0;                // 1: the coefficient tensor holds logarithms
     int super_chunks = -1;       // few very long rows: -1 = selector decides, 0/1 = off, N (a power of two) = cut every row into N
     int fixup_threads = 128;     // measurements only: threads per CTA of the fix-up kernel (128 or 256; 128 measured 1-10 % faster)
+    int pdl = 1;                 // programmatic dependent launch: the kernel may begin (up to its first access to
+                                 // global memory) while the kernel before it in the stream is draining
     int fixed_first = 0;         // measurements only: chained rows also start from fixed round-robin tickets
     int peer_wait_budget_ms = 30000;   // budget of a wait for ANOTHER RANK (its records, its acknowledgements)
 };
@@ -91,6 +112,7 @@ int parse_options(const linrec_opts* o, Options& out)
         else if (!strcmp(n, "l2Promotion")) out.l2_promotion = v;
         else if (!strcmp(n, "fixedFirstTickets")) out.fixed_first = v != 0;
         else if (!strcmp(n, "superChunks")) out.super_chunks = v;
+        else if (!strcmp(n, "programmaticLaunch")) out.pdl = v != 0;
         else if (!strcmp(n, "fixupThreads")) out.fixup_threads = v;
         else if (!strcmp(n, "peerWaitBudgetMs")) out.peer_wait_budget_ms = v;
         else return LINREC_ERR_NOT_IMPLEMENTED;
@@ -664,9 +686,10 @@ int launch_scan_direct(int kind, bool bwd, const void* in0, const void* c, const
             rc = cached_map(&m[i], src[i], dtype, numseq, seqlen, row_stride, box_lines, box_rows, opt.l2_promotion);
             if (rc != LINREC_OK) return rc;
         }
-        pl.tv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(m[0], m[1], m[2], m[3], m[4], p);
+        launch_kernel(pl.tv->fn[di][bwd][asc], (unsigned)grid, (unsigned)pl.NT, smem, stream, opt.pdl != 0, m[0], m[1], m[2], m[3],
+                      m[4], p);
     } else {
-        pl.gv->fn[di][bwd][asc]<<<(unsigned)grid, pl.NT, smem, stream>>>(p);
+        launch_kernel(pl.gv->fn[di][bwd][asc], (unsigned)grid, (unsigned)pl.NT, smem, stream, opt.pdl != 0, p);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return launch_result("kernel launch");
@@ -688,7 +711,7 @@ int launch_fixup_t(bool bwd, bool asc, const linrec::FixupParams& fp, cudaStream
     const bool vec = al(fp.out0) && al(fp.out1) && al(fp.in0) && al(fp.c) && al(fp.yin) && fp.seqlen % 8 == 0 &&
                      (fp.row_stride * (long long)sizeof(ST)) % 16 == 0;
     const unsigned g = (unsigned)grid;
-#define LINREC_FIXUP(B, A, V) linrec::linrec_fixup_kernel<ST, NT, B, A, V><<<g, NT, 0, stream>>>(fp)
+#define LINREC_FIXUP(B, A, V) launch_kernel(linrec::linrec_fixup_kernel<ST, NT, B, A, V>, g, (unsigned)NT, 0, stream, true, fp)
     if (!bwd) {
         if (asc) { if (vec) LINREC_FIXUP(false, true, true); else LINREC_FIXUP(false, true, false); }
         else     { if (vec) LINREC_FIXUP(false, false, true); else LINREC_FIXUP(false, false, false); }

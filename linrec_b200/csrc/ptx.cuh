@@ -144,6 +144,23 @@ __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar)
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// A kernel launched with the "programmatic stream serialization" attribute may start while the kernel
+// before it in the stream is still draining: its CTAs are scheduled as SMs free up and run their
+// prologue (shared-memory set-up, descriptor prefetch), then wait here until the previous kernel has
+// completed and its memory is visible.  Nothing that another kernel may have written -- and nothing
+// another kernel may still be reading -- is touched before this wait.  Without the attribute both
+// instructions do nothing.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel of the stream begin to be scheduled (it still waits for this one to complete).
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- acquire / release on global memory (look-back descriptors) ---------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p)
 {

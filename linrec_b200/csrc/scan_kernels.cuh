@@ -182,13 +182,12 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
     // them one after the other.
     constexpr int boss = ASC ? 0 : NT - 32;
     const uint32_t ntiles = (uint32_t)p.ntiles;
-    const uint32_t epoch = read_epoch(p.header);
     const bool with_halo = BWD && p.chain;
     const uint32_t stage_bytes =
         (uint32_t)NIN * (p.chain ? (uint32_t)L::kTileBytes
                                  : (uint32_t)(p.rows_per_tile * p.slots_per_row) * (uint32_t)sizeof(ST));
 
-    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
+    ptx::grid_launch_dependents();
     if (tid == boss) {
 #pragma unroll
         for (int s = 0; s < S; ++s) ptx::mbar_init(&full[s], with_halo ? 2u : 1u);
@@ -203,6 +202,10 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
         }
     }
     __syncthreads();
+    // everything above is this CTA's own; from here on global memory is read and written
+    ptx::grid_dependency_wait();
+    const uint32_t epoch = read_epoch(p.header);
+    if (p.px_epoch >= 3u && tid < 32) wait_for_slot_release(p.px, p.px_epoch, p.peer_wait_budget, p.header + 1, tid);
 
     // Issuing thread only: start the copies of ticket `tk` into ring slot `s`.
     auto issue = [&](int s, uint32_t tk) {
@@ -371,6 +374,8 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
     const Geometry g = make_geometry<E, NT, ASC>(p);
     const int tid = g.t;
     const uint32_t ntiles = (uint32_t)p.ntiles;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const uint32_t epoch = read_epoch(p.header);
     const ST* gin0 = reinterpret_cast<const ST*>(p.in0);
     const ST* gc = reinterpret_cast<const ST*>(p.c);
@@ -557,6 +562,8 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
     const Geometry g = make_geometry<E, NT, ASC>(p);
     const int tid = g.t;
     const uint32_t ntiles = (uint32_t)p.ntiles;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const uint32_t epoch = read_epoch(p.header);
     const ST* gin0 = reinterpret_cast<const ST*>(p.in0);
     const ST* gc = reinterpret_cast<const ST*>(p.c);

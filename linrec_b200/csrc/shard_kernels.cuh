@@ -140,6 +140,8 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
     __shared__ float v_in_s;
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
     const long long L = p.seqlen;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();   // the scan that left the local results and the records has completed
 
     for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
         const int shard = p.super_chunks > 1 ? (int)(row & (p.super_chunks - 1)) : p.shard;
