@@ -46,6 +46,14 @@ def test_workspace_size_rules():
     assert ws(0, 0, 0) == 256 and ws(10, 100, 0) == 256        # short rows: header only
     big = ws(8, 1 << 20, 0)
     assert big % 256 == 0 and big >= 256 + 8 * ((1 << 20) // 2048) * 16
+    # a handful of very long rows may be cut into super-chunks: room for their records on top of the
+    # descriptors (about 1024 records of 16 bytes), but only in that regime
+    many = ws(4096, 1 << 20, 0)
+    assert many == 256 + 4096 * ((1 << 20) // 1024) * 16          # the smallest tile any variant uses: 1024
+    assert big >= 256 + 8 * ((1 << 20) // 1024) * 16 + 1024 * 16
+    assert ws(8, 1 << 16, 0) == 256 + 8 * ((1 << 16) // 1024) * 16          # rows too short to be cut
+    # the entry points of version 0.2.0 (the fix-up calls take the operands) are there
+    assert _capi.lib.linrec_b200_version() >= 200
 
 
 def test_bad_arguments_are_refused_before_any_launch():
