@@ -289,6 +289,33 @@ def test_all_variants(shape, rev):
         _check_fwd_bwd(x, c, dy, rev, **dict(zip(names, cfg)))
 
 
+def test_programmatic_launch_on_and_off_agree():
+    """The scan kernels are launched so that their prologue may overlap the tail of the kernel before
+    them (they wait before their first access to global memory).  Back-to-back launches that depend on
+    each other -- forward, then backward on its output, repeated on one workspace, chained rows and rows
+    that share a tile, super-chunks with their fix-up kernel -- must give bit-identical results with the
+    overlap on (default) and off."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    for shape in [(300, 512), (64, 3 * 8192 + 64), (33, 1000), (7, 10001), (3, 1 << 18)]:
+        x, c, dy = (t.to(dev) for t in _data(shape, clo=0.8))
+        outs = {}
+        for pdl in (1, 0):
+            res = []
+            for _ in range(4):
+                y = lb._C.linrec_pipe_fwd(inputs=x, coeffs=c, reverse=False, programmaticLaunch=pdl)
+                dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy, coeffs=c, outputs=y, reverse=False, programmaticLaunch=pdl)
+                y2 = lb._C.linrec_pipe_fwd(inputs=dx, coeffs=c, reverse=True, programmaticLaunch=pdl)    # reads what was just written
+                res.append((y, dx, dc, y2))
+            torch.cuda.synchronize()
+            for r in res[1:]:
+                assert all(torch.equal(a, b) for a, b in zip(r, res[0]))
+            outs[pdl] = res[0]
+        assert all(torch.equal(a, b) for a, b in zip(outs[1], outs[0]))
+        np.testing.assert_allclose(outs[1][0].cpu().numpy(), oracle.fwd_f32(x.cpu().numpy(), c.cpu().numpy()), rtol=RTOL, atol=ATOL)
+    lb.check_status()
+
+
 # ---- layouts ---------------------------------------------------------------------------------------
 def test_unaligned_base_and_row_stride():
     """Views that start one element into an allocation and rows with padding between them."""
