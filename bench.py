@@ -621,8 +621,8 @@ def _cfg5(ctx, linrec_b200, fwd, bwd, peak, steps):
 
     channel  every rank scans its 8192/N rows; no communication.
     seq      every rank holds the columns [rank*L/N, (rank+1)*L/N) of all 8192 rows: local scan, one
-             all-gather of the per-row records, fused fix-up (and the same with the records pushed into
-             the peers' memory by the scan kernel instead of the all-gather).
+             all-gather of the per-row records, fused fix-up (and the same with the records read from
+             the peers' memory by the fix-up kernel instead of the all-gather).
 
     One GPU cannot hold the six tensors (192 GiB): there the problem is worked through in eight row
     slabs of (1024, 2^20) on one fixed set of device buffers, the same bytes per element through the
@@ -762,7 +762,7 @@ def _cfg5(ctx, linrec_b200, fwd, bwd, peak, steps):
             okp, detail_p = judge_rows(gather_cols(X), gather_cols(Cc), gather_cols(DY), tuple(gather_cols(t) for t in (Y, DX, DC)))
             exchange.poll(wait=True)
             linrec_b200.check_status()
-            seq["peer_store_exchange"] = block(ms_p, {"collective": "none: records pushed into the peers' memory by the scan kernel",
+            seq["peer_memory_exchange"] = block(ms_p, {"collective": "none: records read from the peers' memory by the fix-up kernel",
                                                       "matches_single_device": ctx.all_true(okp), "parity_rank0": detail_p})
     out["seq"] = seq
     del store, X, Cc, DY, Y, DX, DC

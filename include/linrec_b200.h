@@ -166,9 +166,10 @@ LINREC_API int linrec_b200_bwd_fixup(const void* dy, void* dx, void* dc, const v
  * address (peer-mapped / symmetric memory).  linrec_b200_exchange_init zeroes the local buffer and
  * stores in it the addresses of all ranks' buffers as mapped in the calling process
  * (peer_bufs[rank] must be the local buffer); the ranks must synchronise once after it (a barrier)
- * before the first exchange.  One *_seq_p2p call = local scan whose kernel stores each row's record
- * straight into every rank's buffer and releases a per-row flag there, followed by the fix-up kernel,
- * which waits (bounded) for the flags it needs in its own buffer.  No NCCL kernel, no host
+ * before the first exchange.  One *_seq_p2p call = local scan whose kernel leaves each row's record
+ * in the rank's own buffer and, when the launch is complete, releases one flag in every rank's
+ * buffer, followed by the fix-up kernel, which waits (bounded) for the flags it needs in its own
+ * buffer and reads the records from their owners' buffers.  No NCCL kernel, no host
  * synchronisation.  `epoch` must be 1 for the first exchange on these buffers and grow by one with
  * every call, identically on all ranks (the calls are collective: every rank makes the same sequence
  * of them, with numseq <= max_rows).  Slots are double-buffered by epoch parity and released by

@@ -64,13 +64,18 @@ __device__ __forceinline__ Pair combine(Pair far, Pair near)
 
 // ---- peer exchange (sequence sharding without a collective call) ------------------------------------
 // Every rank owns one exchange buffer that all ranks of the node can address (peer-mapped memory).
-// A rank's scan kernel stores each row's record directly into the buffer of EVERY rank and then
-// releases a per-row flag there; the fix-up kernel of a rank waits on the flags in its OWN buffer.
+// A rank's scan kernel leaves each row's record in its OWN buffer; the last of its CTAs to finish
+// releases one flag in the buffer of EVERY rank ("my records of this epoch are complete").  The fix-up
+// kernel of a rank waits on the flags in its own buffer and then READS the records it needs straight
+// from the owners' buffers (one 16-byte load over NVLink per row and earlier shard, all of a row's
+// loads in flight together, spread over all CTAs of the fix-up).  Pushing every record to every rank
+// instead was measured: per row it costs the emitting CTA a system-scope fence, i.e. an NVLink round
+// trip (8 % of the scan at 55 rows per CTA); in bulk from the last CTA it is a serial tail.
 // Slots are double-buffered by the parity of the exchange epoch, and a rank acknowledges an epoch to
 // all peers when its fix-up has finished, so that a slot is only overwritten (two epochs later)
 // after every reader is done with it.
-//   records [2][nranks][max_rows] x 16 B   (P, Y, c_edge, y_edge)
-//   flags   [2][nranks][max_rows] x 4 B    epoch of the record
+//   records [2][max_rows] x 16 B           (P, Y, c_edge, y_edge) of this rank's shard
+//   flags   [2][nranks] x 4 B              epoch up to which rank i's records are complete
 //   acks    [nranks] x 4 B                 last epoch rank i has finished reading
 //   done    4 B                            fix-up CTAs finished (local bookkeeping)
 // preceded by a 256-byte table of the peers' buffer addresses.
@@ -84,22 +89,21 @@ struct PeerTable {
     long long max_rows;
 };
 static_assert(sizeof(PeerTable) <= kPeerTableBytes, "peer table must fit its slot");
-__host__ __device__ inline size_t px_flags_offset(long long max_rows, int nranks) { return kPeerTableBytes + (size_t)2 * nranks * max_rows * 16; }
+__host__ __device__ inline size_t px_flags_offset(long long max_rows, int) { return kPeerTableBytes + (size_t)2 * max_rows * 16; }
 __host__ __device__ inline size_t px_acks_offset(long long max_rows, int nranks)
 {
-    return (px_flags_offset(max_rows, nranks) + (size_t)2 * nranks * max_rows * 4 + 255) / 256 * 256;
+    return (px_flags_offset(max_rows, nranks) + (size_t)2 * nranks * 4 + 255) / 256 * 256;
 }
 __host__ __device__ inline size_t px_done_offset(long long max_rows, int nranks) { return px_acks_offset(max_rows, nranks) + 256; }
 __host__ __device__ inline size_t px_total_bytes(long long max_rows, int nranks) { return px_done_offset(max_rows, nranks) + 256; }
-__device__ __forceinline__ float4* px_record(const PeerTable& t, int buf_of, int par, int from, long long row)
+__device__ __forceinline__ float4* px_record(const PeerTable& t, int buf_of, int par, long long row)
 {
-    return reinterpret_cast<float4*>(static_cast<char*>(t.base[buf_of]) + kPeerTableBytes) +
-           ((size_t)(par * t.nranks + from) * t.max_rows + row);
+    return reinterpret_cast<float4*>(static_cast<char*>(t.base[buf_of]) + kPeerTableBytes) + ((size_t)par * t.max_rows + row);
 }
-__device__ __forceinline__ uint32_t* px_flag(const PeerTable& t, int buf_of, int par, int from, long long row)
+__device__ __forceinline__ uint32_t* px_flag(const PeerTable& t, int buf_of, int par, int from)
 {
     return reinterpret_cast<uint32_t*>(static_cast<char*>(t.base[buf_of]) + px_flags_offset(t.max_rows, t.nranks)) +
-           ((size_t)(par * t.nranks + from) * t.max_rows + row);
+           (par * t.nranks + from);
 }
 __device__ __forceinline__ uint32_t* px_ack(const PeerTable& t, int buf_of, int of_rank)
 {
@@ -119,10 +123,11 @@ __device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v)
 {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys_f32x4(float4* p, float4 v)
+__device__ __forceinline__ float4 ld_relaxed_sys_f32x4(const float4* p)
 {
-    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                 : "memory");
+    float4 v;
+    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
 }
 // Bounded wait until *p has reached `target` (epochs only grow); false when the budget ran out.
 __device__ __forceinline__ bool wait_epoch_reached(const uint32_t* p, uint32_t target, long long budget)
@@ -166,7 +171,7 @@ struct ScanParams {
     int vec;                // any-alignment kernel: rows allow 16-byte global accesses
     int lazy;               // bulk-copy kernel: draw the next ticket only when the current tile is finished
     int fixed_first;        // measurements only: chained rows also start from fixed round-robin tickets
-    const PeerTable* px;    // sequence sharding: this rank's exchange buffer (records are pushed to all ranks)
+    const PeerTable* px;    // sequence sharding: this rank's exchange buffer (its records are left there for all ranks)
     uint32_t px_epoch;      // epoch of this exchange; 0: no peer exchange in this launch (real epochs start at 1)
     int logc;               // 1: `c` holds logarithms; the loaders apply exp, the backward pass returns the
                             //    gradient with respect to the logarithm (d_c * c)
@@ -279,7 +284,8 @@ struct Storage<__half> {
 
 // Sequence sharding: the record of one row of this shard -- (P, Y) of the whole shard and, for the
 // backward pass, c at the shard's scan-last element and y at its scan-first element (what the
-// neighbouring shards need).  Written to the local record array and/or pushed to every peer.
+// neighbouring shards need).  Written to the local record array and/or to this rank's exchange buffer,
+// where the other ranks read it once publish_records() has told them that the launch is complete.
 // (Deliberately NOT inlined and fed by value: it runs once per row; inlined into the tile loop its
 // peer loop cost the backward kernel 37 registers and with them one resident CTA per SM.)
 template <typename ST, bool BWD, bool ASC>
@@ -305,13 +311,19 @@ __device__ __noinline__ void emit_record(float* carry_out, int carry_stride, con
     if (px_epoch != 0u) {
         const PeerTable& t = *px;
         const int par = (int)(px_epoch & 1u);
-        const float4 rec = make_float4(tot_p, tot_y, ce, ye);
-        // all payloads, ONE system-scope fence, then all flags: a release store per peer would make this
-        // lane wait for a round trip over NVLink once per peer
-        for (int i = 0; i < t.nranks; ++i) st_relaxed_sys_f32x4(px_record(t, i, par, t.me, row), rec);
-        __threadfence_system();
-        for (int i = 0; i < t.nranks; ++i) st_relaxed_sys_u32(px_flag(t, i, par, t.me, row), px_epoch);
+        *px_record(t, t.me, par, row) = make_float4(tot_p, tot_y, ce, ye);
     }
+}
+
+// Run by the thread that found its CTA to be the last of the launch: every record of this rank is then
+// in its buffer (published by the writers' fences before they counted themselves done); one
+// system-scope fence, then the flag in every rank's buffer.
+static __device__ __noinline__ void publish_records(const PeerTable* px, uint32_t px_epoch)
+{
+    const PeerTable& t = *px;
+    const int par = (int)(px_epoch & 1u);
+    __threadfence_system();
+    for (int r = 0; r < t.nranks; ++r) st_release_sys_u32(px_flag(t, r, par, t.me), px_epoch);
 }
 
 template <typename ST, bool BWD, bool ASC>
@@ -321,7 +333,7 @@ __device__ __forceinline__ void emit_record(const ScanParams& p, long long row, 
                               reinterpret_cast<const ST*>(p.yin), p.seqlen, p.row_stride, row, tot.p, tot.y);
 }
 
-// Before a launch pushes records of epoch e it makes sure that every rank has acknowledged epoch
+// Before a launch writes records of epoch e it makes sure that every rank has acknowledged epoch
 // e-2, whose slots it is about to overwrite (lanes 0..nranks-1 of the calling warp check one rank each).
 static __device__ __noinline__ void wait_for_slot_release(const PeerTable* px, uint32_t px_epoch, long long budget,
                                                    uint32_t* status, int lane)
@@ -632,7 +644,7 @@ __device__ __forceinline__ void publish(TileDesc* d, Pair v, uint32_t state, uin
 
 // Launch epilogue, called by one thread of every CTA after the CTA's last access to the workspace:
 // the CTA that finishes last makes the workspace ready for the next launch.
-__device__ __forceinline__ void finish_launch(uint32_t* header, uint32_t epoch)
+__device__ __forceinline__ bool finish_launch(uint32_t* header, uint32_t epoch)
 {
     __threadfence();
     const uint32_t done = atomicAdd(header + 3, 1u);
@@ -640,7 +652,16 @@ __device__ __forceinline__ void finish_launch(uint32_t* header, uint32_t epoch)
         header[0] = 0u;
         header[3] = 0u;
         header[2] = (epoch + 1u) & 0x3fffffffu;
+        return true;
     }
+    return false;
+}
+
+// End of a scan kernel (one thread per CTA): count this CTA as done; in a launch that takes part in
+// a peer exchange the CTA that was last tells all ranks that this rank's records are complete.
+__device__ __forceinline__ void finish_scan(const ScanParams& p, uint32_t epoch)
+{
+    if (finish_launch(p.header, epoch) && p.px_epoch != 0u) publish_records(p.px, p.px_epoch);
 }
 
 __device__ __forceinline__ uint32_t read_epoch(const uint32_t* header)

@@ -352,7 +352,7 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             }
         }
         ptx::tma_wait_group<0>();
-        finish_launch(p.header, epoch);
+        finish_scan(p, epoch);
     }
 }
 
@@ -513,7 +513,7 @@ __global__ void __launch_bounds__(NT) linrec_generic_kernel(const ScanParams p)
             }
         }
     }
-    if (tid == 0) finish_launch(p.header, epoch);
+    if (tid == 0) finish_scan(p, epoch);
 }
 
 // =================================================================================================
@@ -775,7 +775,7 @@ __global__ void __launch_bounds__(NT, (AsyncLayout<ST, E, NT, S, BWD>::kMinBlock
         issue(s, tile_of_stage[s]);
     }
     ptx::cp_async_wait_group<0>();
-    if (tid == 0) finish_launch(p.header, epoch);
+    if (tid == 0) finish_scan(p, epoch);
 }
 
 // =================================================================================================

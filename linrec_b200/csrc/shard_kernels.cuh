@@ -29,8 +29,8 @@ struct FixupParams {
     long long numseq, seqlen, row_stride;
     int shard, nshards;
     int rec;             // floats per record: 2 forward, 4 backward
-    const PeerTable* px; // with px_epoch != 0: the records arrive in this rank's exchange buffer (16-byte
-    uint32_t px_epoch;   // records, one flag per row and sender) instead of `carries`
+    const PeerTable* px; // with px_epoch != 0: the records are read from the other ranks' exchange buffers
+    uint32_t px_epoch;   // (16-byte records; one flag per owner in this rank's buffer) instead of `carries`
     int super_chunks;    // > 1: the "shards" are consecutive rows of ONE tensor (a real row cut into this many
                          //      pieces, a power of two): row r is shard r % super_chunks of real row
                          //      r / super_chunks, and the records are indexed by row
@@ -38,17 +38,22 @@ struct FixupParams {
     uint32_t* status;    // status word that receives kStatusPeerTimeout
 };
 
-// Where the record of (shard s, row) is, once it is known to have arrived.
+// Where the record of (shard s, row) is in the gathered array.
 __device__ __forceinline__ const float* fixup_record(const FixupParams& p, int s, long long row)
 {
-    if (p.px_epoch != 0u) {
-        const PeerTable& t = *p.px;
-        const int par = (int)(p.px_epoch & 1u);
-        if (!wait_epoch_reached(px_flag(t, t.me, par, s, row), p.px_epoch, p.wait_budget)) atomicOr(p.status, kStatusPeerTimeout);
-        return reinterpret_cast<const float*>(px_record(t, t.me, par, s, row));
-    }
     if (p.super_chunks > 1) return p.carries + ((row & ~(long long)(p.super_chunks - 1)) + s) * p.rec;
     return p.carries + ((long long)s * p.numseq + row) * p.rec;
+}
+
+// Peer exchange: the record of (shard s, row), read from rank s's buffer once rank s has flagged its
+// records of this epoch as complete (a wait that runs out of its budget sets the status bit and reads
+// whatever is there).
+__device__ __forceinline__ float4 fixup_record_from_peer(const FixupParams& p, int s, long long row)
+{
+    const PeerTable& t = *p.px;
+    const int par = (int)(p.px_epoch & 1u);
+    if (!wait_epoch_reached(px_flag(t, t.me, par, s), p.px_epoch, p.wait_budget)) atomicOr(p.status, kStatusPeerTimeout);
+    return ld_relaxed_sys_f32x4(px_record(t, s, par, row));
 }
 
 // Writes the peer table into a (zeroed) exchange buffer.
@@ -137,7 +142,8 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
 {
     constexpr int V = 8, NW = NT / 32, STEP = NT * V;
     __shared__ Pair wagg[2][NW];
-    __shared__ float v_in_s;
+    __shared__ float v_in_s, y_edge_s;
+    __shared__ float4 rec_s[kMaxPeers];
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
     const long long L = p.seqlen;
     ptx::grid_launch_dependents();
@@ -153,7 +159,28 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
         // per row -- super-chunks -- the walk usually ends after one record).  Backward pass: between
         // two shards lies the coefficient at the earlier one's scan-last element (record word 2),
         // which the local scans treated as 1.
-        if (tid == 0) {
+        // Peer exchange: lane n of the first warp fetches the record of the shard at scan position n
+        // from its owner (all of a row's loads cross NVLink together), one more lane the record of
+        // the next shard (its y at the scan-first element, needed by the backward pass below).
+        if (p.px_epoch != 0u) {
+            if (w == 0) {
+                const bool earlier = lane < my_pos, next = BWD && lane == my_pos + 1 && lane < p.nshards;
+                if (earlier || next) rec_s[lane] = fixup_record_from_peer(p, shard_at<ASC>(lane, p.nshards), row);
+                __syncwarp();
+                if (lane == 0) {
+                    float v = 0.0f, m = 1.0f;
+                    for (int n = my_pos - 1; n >= 0; --n) {
+                        const float4 rec = rec_s[n];
+                        if (BWD) m *= rec.z;
+                        v = fmaf(rec.y, m, v);
+                        m *= rec.x;
+                        if (m == 0.0f) break;
+                    }
+                    v_in_s = v;
+                    if (BWD && my_pos + 1 < p.nshards) y_edge_s = rec_s[my_pos + 1].w;
+                }
+            }
+        } else if (tid == 0) {
             float v = 0.0f, m = 1.0f;
             for (int n = my_pos - 1; n >= 0; --n) {
                 const volatile float* rec = fixup_record(p, shard_at<ASC>(n, p.nshards), row);
@@ -163,6 +190,8 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
                 if (m == 0.0f) break;
             }
             v_in_s = v;
+            if (BWD && my_pos + 1 < p.nshards)
+                y_edge_s = reinterpret_cast<const volatile float*>(fixup_record(p, shard_at<ASC>(my_pos + 1, p.nshards), row))[3];
         }
         __syncthreads();
         float v = v_in_s;    // true value that enters the next step
@@ -272,10 +301,8 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
             // the local pass could not know
             __syncthreads();
             if (tid == 0 && my_pos + 1 < p.nshards) {
-                const int nxt_shard = shard_at<ASC>(my_pos + 1, p.nshards);
-                const float y_edge = reinterpret_cast<const volatile float*>(fixup_record(p, nxt_shard, row))[3];
                 const long long last = ASC ? L - 1 : 0;
-                o1[last] = Storage<ST>::from_float(Storage<ST>::to_float(o0[last]) * y_edge);
+                o1[last] = Storage<ST>::from_float(Storage<ST>::to_float(o0[last]) * y_edge_s);
             }
         }
         __syncthreads();   // v_in_s and wagg are rewritten for the next row

@@ -115,9 +115,10 @@ _CUDA_KERNELS = CudaShardKernels()
 class PeerExchange:
     """Exchange buffers for sequence sharding without a collective call.
 
-    Every rank allocates one buffer in symmetric (peer-mapped) memory; the scan kernels store each
-    row's record straight into all ranks' buffers over NVLink and the fix-up kernels wait on flags in
-    their own buffer, so a sharded scan is two kernel launches and nothing else.  Create one per
+    Every rank allocates one buffer in symmetric (peer-mapped) memory; the scan kernels leave each
+    row's record in their own buffer and flag all ranks when a launch is complete, and the fix-up
+    kernels wait on the flags in their own buffer and read the records over NVLink from their
+    owners, so a sharded scan is two kernel launches and nothing else.  Create one per
     process group and reuse it for every call (`linrec_seq_sharded(..., exchange=ex)`); calls are
     collective and must be made in the same order on all ranks.
     """
@@ -139,7 +140,7 @@ class PeerExchange:
                                                      torch.cuda.current_stream(dev).cuda_stream)
         _capi.raise_for(rc, "linrec_b200_exchange_init")
         torch.cuda.synchronize(dev)
-        handle.barrier()                   # every rank's buffer is initialised before anyone pushes into it
+        handle.barrier()                   # every rank's buffer is initialised before anyone writes a flag into it
         self.buffer = buf
         self._keep = handle
         self._pending = None               # (event, pinned copy of the status word, workspace, stream) of the last call
@@ -230,7 +231,7 @@ def _gather(records: torch.Tensor, group) -> torch.Tensor:
 def seq_sharded_fwd(x: torch.Tensor, c: torch.Tensor, reverse: bool = False, group=None, kernels=None, exchange=None,
                     out=None):
     """Forward scan of a row that is split over the ranks of `group` (this rank holds shard `rank`).
-    With `exchange` (a PeerExchange) the records travel by peer stores inside the kernels; without it
+    With `exchange` (a PeerExchange) the records are read from peer memory inside the kernels; without it
     by one all-gather.  `out` may hold a preallocated result with the layout of `x`."""
     kw = {} if out is None else {"out": out}
     if exchange is not None:

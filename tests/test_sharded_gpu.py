@@ -93,7 +93,7 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
 @pytest.mark.parametrize("rows,L,G,clo", [(6, 4 * 96, 4, 0.5), (3, 2 * 8192 * 3, 2, 0.9), (5, 3 * 2080, 3, 0.99), (40, 8 * 512, 8, 0.3)],
                          ids=["short", "chained", "ragged", "eight"])
 def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
-    """The peer-store path with every "rank" on one device: G exchange buffers in local memory, scan
+    """The peer-memory path with every "rank" on one device: G exchange buffers in local memory, scan
     phase of all ranks first, then the fix-up phase of all ranks (so no launch ever waits for a later
     one).  Four exchanges in a row (forward and backward, both directions) exercise slot reuse and the
     acknowledgements."""
@@ -213,8 +213,8 @@ def test_fixup_follows_a_carry_through_a_dip(rev):
 
 
 def test_wait_for_a_peer_gives_up_with_status():
-    """The fix-up phase of the peer-store path is run for shard 1 without anybody ever pushing shard
-    0's records: its bounded waits (option peerWaitBudgetMs, 20 ms here) must run out by themselves,
+    """The fix-up phase of the peer-memory path is run for shard 1 without anybody ever flagging shard
+    0's records as complete: its bounded waits (option peerWaitBudgetMs, 20 ms here) must run out by themselves,
     set the status word of the workspace and leave the context usable."""
     import ctypes
     from linrec_b200 import _capi
@@ -277,7 +277,7 @@ def _nccl_worker(rank, world, port, tmp):
             close(ys, y_full[:, sl], ymax)
             close(gx, gx_full[:, sl], gmax)
             close(gc, gc_full[:, sl], 4 * ymax * gmax)
-            # the same through peer stores instead of the all-gather (several exchanges in a row)
+            # the same through peer memory instead of the all-gather (several exchanges in a row)
             for _ in range(3):
                 xs2 = xs.detach().clone().requires_grad_(True)
                 cs2 = cs.detach().clone().requires_grad_(True)
