@@ -69,11 +69,23 @@ __global__ void linrec_exchange_init_kernel(PeerTable* dst, const PeerTableArg a
 template <bool ASC>
 __device__ __forceinline__ int shard_at(int n, int nshards) { return ASC ? n : nshards - 1 - n; }
 
-// The walk along a row goes on until the carried value is exactly zero: from there on every correction
-// is zero whatever the coefficients that follow are.  (Stopping earlier, once the value is subnormal,
-// would be safe only for |c| <= 1 from there on -- a later stretch of |c| > 1 lets the correction grow
-// back -- and the operator does not restrict its coefficients.)  NaN keeps walking.
-__device__ __forceinline__ bool fixup_carry_alive(float v) { return !(v == 0.0f); }
+// The walk along a row goes on while the deviation d of the local results from the true ones (the
+// entering carry times the product of the coefficients so far) still matters at a step boundary, where
+// the true value is v and the local scan's value v - d:
+//   * d exactly zero: every later correction is zero whatever the coefficients that follow are;
+//   * |d| <= 2^-26 |v| (a quarter of an ulp of v, v finite): the local value IS the true one up to less
+//     than the rounding error that any fp32 evaluation commits at that element (2^-24 |v|); whatever the
+//     later coefficients do to it -- a stretch of |c| > 1 lets it grow back -- they do to that rounding
+//     error as well.  For c ~ U(0.99, 1) this ends the walk after ~3.6 k elements instead of the ~20.6 k
+//     that the product needs to underflow.
+// A threshold on |d| alone (say, subnormal) would NOT do: it is safe only for |c| <= 1 from there on, and
+// where the true values are themselves tiny (the decaying tail behind an impulse) d is all there is.
+// NaN in d or v keeps walking.
+__device__ __forceinline__ bool fixup_carry_alive(float d, float v)
+{
+    if (d == 0.0f) return false;
+    return !(fabsf(v) <= 3.402823466e+38f && fabsf(d) <= 0x1p-26f * fabsf(v));
+}
 
 // Eight consecutive elements of a row as floats, memory order.  VEC: 16-byte loads (the caller has
 // checked alignment), else element loads.  `m0` may address elements outside [0, seqlen) only when
@@ -136,7 +148,7 @@ struct FixupStep {
 // more resident CTAs than the extra step in flight gives back; 128 threads per CTA beat 256.)
 //
 // The walk ends once the DIFFERENCE between the true and the local carry, d = v_in * (product of c so
-// far), is exactly zero: from there on the local results are the true ones.
+// far), no longer matters (fixup_carry_alive): from there on the local results are the true ones.
 template <typename ST, int NT, bool BWD, bool ASC, bool VEC>
 __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
 {
@@ -238,9 +250,9 @@ __global__ void __launch_bounds__(NT) linrec_fixup_kernel(const FixupParams p)
         };
 
         FixupStep<BWD> cur, nxt;
-        if (fixup_carry_alive(d)) fetch(0, cur);
+        if (fixup_carry_alive(d, v)) fetch(0, cur);
         int par = 0;
-        for (long long base = 0; base < L && fixup_carry_alive(d); base += STEP, par ^= 1) {
+        for (long long base = 0; base < L && fixup_carry_alive(d, v); base += STEP, par ^= 1) {
             if (base + STEP < L) fetch(base + STEP, nxt);
             const long long n0 = base + (long long)tid * V;
             // operands in scan order; identity elements outside the shard
