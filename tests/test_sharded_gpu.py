@@ -90,6 +90,75 @@ def test_all_shards_on_one_gpu(rows, L, G, clo, rev):
     linrec_b200.check_status()
 
 
+def _fwd_all_shards(x, c, G, rev=False):
+    from linrec_b200.sharded import CudaShardKernels
+    k = CudaShardKernels()
+    dev = torch.device("cuda:0")
+    Ls = x.shape[1] // G
+    xs = [x[:, s * Ls:(s + 1) * Ls].contiguous().to(dev) for s in range(G)]
+    cs = [c[:, s * Ls:(s + 1) * Ls].contiguous().to(dev) for s in range(G)]
+    ys, recs = zip(*[k.fwd_carry(xs[s], cs[s], rev, s, G) for s in range(G)])
+    gathered = torch.stack(recs).contiguous()
+    for s in range(G):
+        k.fwd_fixup(xs[s], ys[s], cs[s], gathered, rev, s, G)
+    return torch.cat([t.cpu() for t in ys], dim=1).numpy()
+
+
+@pytest.mark.parametrize("case", ["random", "impulse", "inf", "nan", "regrowth", "tiny_values"])
+def test_the_walk_may_end_early_only_where_nothing_is_lost(case):
+    """The fix-up walk along a row ends where the entering carry's remaining contribution is exactly zero or
+    below a quarter ulp of the true value.  Shards of 32768 elements with c ~ U(0.99, 1): the second rule
+    ends the walk after ~4 k elements.  The results must be as good as the unsharded operator's (judged
+    against fp64), an impulse's tail must keep its relative accuracy down to 1e-37, a non-finite
+    carry must travel on exactly as in the sequential evaluation, and a later stretch of c > 1 must not
+    bring back anything that was dropped."""
+    import linrec_b200
+    rows, G, Ls = 4, 2, 32768
+    L = G * Ls
+    x, c, _ = _data((rows, L), 0.99, seed=11)
+    rtol, atol = 1e-4, 1e-5
+    if case == "impulse":
+        x = torch.zeros_like(x)
+        x[:, 5] = 1.0
+        c = 0.998 + 0.1 * (c - 0.99)          # U(0.998, 0.999): the product over a row is ~ 2e-43, down in the subnormals,
+        atol = 1e-37                          # where an fp32 chain stalls (y * c rounds back to y): judged above them
+    elif case == "inf":
+        x[1, Ls - 7] = float("inf")
+    elif case == "nan":
+        x[2, 3] = float("nan")
+    elif case == "regrowth":
+        c[:, Ls + 8000:Ls + 16000] = 1.002     # e^16 ~ 9e6 after the walk has ended
+    elif case == "tiny_values":
+        x[:, Ls:] *= 1e-30                     # behind the boundary the carry's tail is all there is for a long while
+        atol = 1e-33
+    y = _fwd_all_shards(x, c, G)
+    y64 = oracle.fwd_f64(x.numpy(), c.numpy())
+    y32 = oracle.fwd_f32(x.numpy(), c.numpy())
+    if case in ("inf", "nan"):
+        np.testing.assert_array_equal(np.isfinite(y), np.isfinite(y32))
+        np.testing.assert_array_equal(np.isnan(y), np.isnan(y32))
+        ok = np.isfinite(y32)
+        _judge_against_f64(y[ok], y32[ok], y64[ok], "y (finite part)")
+    elif case == "impulse":
+        np.testing.assert_allclose(y, y64, rtol=rtol, atol=atol)
+    elif case == "tiny_values":
+        _judge_against_f64(y[:, :Ls], y32[:, :Ls], y64[:, :Ls], "y (first shard)")
+        # second shard: the carry's tail (from ~10 down to where the 1e-29-sized local values take over) at
+        # the relative tolerance all the way; 2048 elements behind the boundary are still dominated by
+        # values of ordinary size with their ordinary absolute error
+        np.testing.assert_allclose(y[:, Ls:Ls + 2048], y64[:, Ls:Ls + 2048], rtol=rtol, atol=1e-5)
+        np.testing.assert_allclose(y[:, Ls + 2048:], y64[:, Ls + 2048:], rtol=rtol, atol=atol)
+    else:
+        if case == "random":
+            _judge_against_f64(y, y32, y64, "y")
+        # no worse than the unsharded operator on the device (through a stretch of c > 1 every tiled
+        # evaluation loses more than the sequential one, sharded or not)
+        dev = torch.device("cuda:0")
+        y1 = linrec_b200._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev)).cpu().numpy()
+        assert np.abs(y - y64).max() <= 1.5 * np.abs(y1 - y64).max() + 1e-6 * np.abs(y64).max()
+    linrec_b200.check_status()
+
+
 @pytest.mark.parametrize("rows,L,G,clo", [(6, 4 * 96, 4, 0.5), (3, 2 * 8192 * 3, 2, 0.9), (5, 3 * 2080, 3, 0.99), (40, 8 * 512, 8, 0.3)],
                          ids=["short", "chained", "ragged", "eight"])
 def test_peer_exchange_all_ranks_on_one_gpu(rows, L, G, clo):
