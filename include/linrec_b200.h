@@ -138,7 +138,8 @@ LINREC_API int linrec_b200_config_list(int* values, int cap_rows);
  *   3. *_fixup   folds the records of the shards that come earlier in scan order into the carry that
  *                enters this shard and computes the head of the shard AGAIN from its operands and that
  *                carry (x, c -> y; dy, c, y -> dx, dc), as far along each row as the carry can still
- *                change a result: until carry * running product of the coefficients is exactly zero.
+ *                change a result: until carry * running product of the coefficients is exactly zero or
+ *                less than a quarter ulp (2^-26) of the true value at that element.
  *                Recomputing instead of adding a correction rounds each result to the storage type
  *                once, as the unsharded scan does.
  * `reverse` is the flag of the forward pass in all four. */
