@@ -75,9 +75,34 @@ def _translation_units():
                   if f.endswith(".cu") and (f == "capi.cu" or f.startswith("variants_")))
 
 
+class _BuildLock:
+    """One builder at a time per tree: the ranks of a multi-process job import the package together, and
+    if the library is stale every one of them would compile into the same object files."""
+
+    def __enter__(self):
+        import fcntl
+        os.makedirs(os.path.join(PKG, "_build"), exist_ok=True)
+        self.f = open(os.path.join(PKG, "_build", ".lock"), "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+        return False
+
+
 def build_library(force: bool = False, verbose: bool = False, jobs: int | None = None) -> str:
     if not force and not _stale(LIB_PATH, _all_deps()):
         return LIB_PATH
+    with _BuildLock():
+        if not force and not _stale(LIB_PATH, _all_deps()):   # another process built it while this one waited
+            return LIB_PATH
+        return _build_library_locked(verbose, jobs)
+
+
+def _build_library_locked(verbose: bool, jobs: int | None) -> str:
     nvcc = _nvcc()
     objdir = os.path.join(PKG, "_build", "obj")
     os.makedirs(objdir, exist_ok=True)
@@ -123,11 +148,14 @@ def build_executable(force: bool = False) -> str:
     src = os.path.join(CSRC, "linrec_cli.cu")
     if not force and not _stale(EXE_PATH, _all_deps()):
         return EXE_PATH
-    os.makedirs(os.path.dirname(EXE_PATH), exist_ok=True)
-    cmd = [_nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-I", INCLUDE, "-o", EXE_PATH, src,
-           lib, "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."]
-    subprocess.run(cmd, check=True)
-    _stamp(EXE_PATH, _all_deps())
+    with _BuildLock():
+        if not force and not _stale(EXE_PATH, _all_deps()):
+            return EXE_PATH
+        os.makedirs(os.path.dirname(EXE_PATH), exist_ok=True)
+        cmd = [_nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-I", INCLUDE, "-o", EXE_PATH, src,
+               lib, "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."]
+        subprocess.run(cmd, check=True)
+        _stamp(EXE_PATH, _all_deps())
     return EXE_PATH
 
 
