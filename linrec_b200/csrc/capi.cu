@@ -779,12 +779,15 @@ int launch_fixup(bool bwd, const void* in0, void* out0, void* out1, const void* 
 // that do not decay at all make it a full second pass).  The records live at the end of the workspace.
 namespace {
 constexpr int64_t kSuperChunkMaxRows = 128;       // regime: fewer rows than this ...
+constexpr int64_t kSuperChunkMaxRowsBwd = 592;    // ... (backward: fewer than 4 x 148 SMs, below which the selector has to take
+                                                  //     one large CTA per SM; cut until there are that many rows --
+                                                  //     (256, 2^20) backward fp32 6336 -> 6633, bf16 5898 -> 6234; forward loses) ...
 constexpr int64_t kSuperChunkMinRow = 1 << 17;    // ... each at least this long
 constexpr int64_t kSuperChunkMinLen = 1 << 15;    // a super-chunk is at least this long
 constexpr int64_t kSuperChunkTargetRows = 1024;   // cut until there are about this many independent rows
 constexpr size_t kSuperChunkRecordBytes = 2 * kSuperChunkTargetRows * 16 + 256;
 
-int pick_super_chunks(int kind, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride, const void* const* ptrs,
+int pick_super_chunks(int kind, bool bwd, int dtype, int64_t numseq, int64_t seqlen, int64_t row_stride, const void* const* ptrs,
                       int nptrs, const Options& opt, bool plain)
 {
     if (opt.super_chunks == 0 || opt.super_chunks == 1) return 1;
@@ -797,8 +800,14 @@ int pick_super_chunks(int kind, int dtype, int64_t numseq, int64_t seqlen, int64
         if (V & (V - 1)) return 1;                 // powers of two only
         if (numseq * V > 2 * kSuperChunkTargetRows) return 1;
     } else {
-        if (numseq >= kSuperChunkMaxRows || seqlen < kSuperChunkMinRow) return 1;
-        while (numseq * V < kSuperChunkTargetRows) V <<= 1;
+        if (seqlen < kSuperChunkMinRow) return 1;
+        if (numseq < kSuperChunkMaxRows) {
+            while (numseq * V < kSuperChunkTargetRows) V <<= 1;
+        } else if (bwd && numseq < kSuperChunkMaxRowsBwd) {
+            while (numseq * V < kSuperChunkMaxRowsBwd) V <<= 1;
+        } else {
+            return 1;
+        }
     }
     const int64_t line = 128 / (dtype == LINREC_DTYPE_F32 ? 4 : 2);
     while (V > 1 && (seqlen % V != 0 || seqlen / V < kSuperChunkMinLen || (seqlen / V) % line != 0)) V >>= 1;
@@ -816,7 +825,7 @@ int launch_scan(int kind, bool bwd, const void* in0, const void* c, const void* 
     if (parse_options(opts, opt) == LINREC_OK && numseq > 0 && seqlen > 0 && in0 && c && out0 && workspace) {
         const void* ptrs[5] = {in0, c, out0, bwd ? yin : in0, bwd ? out1 : out0};
         const bool plain = !carry_out && !exchange && !open_start;
-        const int V = (!bwd || (yin && out1)) ? pick_super_chunks(kind, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, plain) : 1;
+        const int V = (!bwd || (yin && out1)) ? pick_super_chunks(kind, bwd, dtype, numseq, seqlen, row_stride, ptrs, 5, opt, plain) : 1;
         const size_t rec_bytes = (size_t)round_up(numseq * V * 16, 256);
         if (V > 1 && workspace_bytes > rec_bytes + linrec::kHeaderBytes) {
             const size_t main_bytes = (workspace_bytes - rec_bytes) & ~(size_t)255;
@@ -1094,7 +1103,7 @@ size_t linrec_b200_workspace_size(int64_t numseq, int64_t seqlen, int dtype)
         for (const GenericVariant& v : word_variants()) tmin = v.E * v.NT < tmin ? v.E * v.NT : tmin;
         if (seqlen > tmin) n += (size_t)numseq * (size_t)ceil_div(seqlen, tmin) * sizeof(TileDesc);
         // few very long rows may be cut into super-chunks: their records and a few more descriptors
-        if (numseq < kSuperChunkMaxRows && seqlen >= kSuperChunkMinRow) n += 2 * kSuperChunkRecordBytes;
+        if (numseq < kSuperChunkMaxRowsBwd && seqlen >= kSuperChunkMinRow) n += 2 * kSuperChunkRecordBytes;
     }
     return (size_t)round_up((int64_t)n, 256);
 }

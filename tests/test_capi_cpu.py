@@ -52,6 +52,8 @@ def test_workspace_size_rules():
     assert many == 256 + 4096 * ((1 << 20) // 1024) * 16          # the smallest tile any variant uses: 1024
     assert big >= 256 + 8 * ((1 << 20) // 1024) * 16 + 1024 * 16
     assert ws(8, 1 << 16, 0) == 256 + 8 * ((1 << 16) // 1024) * 16          # rows too short to be cut
+    # (the backward operator cuts long rows while there are fewer than four per SM)
+    assert ws(256, 1 << 20, 0) >= 256 + 256 * ((1 << 20) // 1024) * 16 + 1024 * 16
     # the entry points of version 0.2.0 (the fix-up calls take the operands) are there
     assert _capi.lib.linrec_b200_version() >= 200
 

@@ -543,6 +543,36 @@ def test_handful_of_very_long_rows(rev):
     _check_fwd_bwd(x, c, dy, rev)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("rev", [False, True])
+def test_super_chunks_backward_with_fewer_rows_than_four_per_sm(rev, dtype):
+    """Between 128 rows and four per SM only the backward operator cuts its rows (two launches); the
+    forward operator scans them as they are (one launch).  (130, 2^17): four super-chunks per row."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    rows, L = 130, 1 << 17
+    x, c, dy = _data((rows, L), clo=0.9, seed=SEED + 77)
+    if dtype == "bf16":
+        x, c, dy = x.bfloat16(), c.bfloat16(), dy.bfloat16()
+    xf, cf, dyf = x.float().numpy(), c.float().numpy(), dy.float().numpy()
+    rtol = RTOL if dtype == "f32" else 2.0 ** -7
+    before = lb._C.launch_count()
+    y = lb._C.linrec_pipe_fwd(inputs=x.to(dev), coeffs=c.to(dev), reverse=rev)
+    assert lb._C.launch_count() - before == 1
+    y_ref = oracle.fwd_f32(xf, cf, reverse=rev)
+    np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=rtol, atol=ATOL)
+    yd = torch.from_numpy(y_ref).to(dev).to(x.dtype)
+    before = lb._C.launch_count()
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yd, reverse=rev)
+    assert lb._C.launch_count() - before == 2, "expected the super-chunk path (scan + fix-up)"
+    dx_ref, dc_ref = oracle.bwd_f32(dyf, cf, yd.float().cpu().numpy(), reverse=rev)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=rtol, atol=ATOL)
+    np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref, rtol=rtol, atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+    dx1, dc1 = lb._C.linrec_pipe_bwd(d_outputs=dy.to(dev), coeffs=c.to(dev), outputs=yd, reverse=rev, superChunks=0)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx1.float().cpu().numpy(), rtol=rtol, atol=ATOL)
+    lb.check_status()
+
+
 @pytest.mark.parametrize("rev", [False, True])
 @pytest.mark.parametrize("rows,L,clo,chi", [(3, 1 << 18, 0.0, 1.0), (1, 1 << 20, 0.9, 1.0), (5, 3 << 17, 0.999, 1.0),
                                             (2, 1 << 18, 1.0, 1.0), (7, 1 << 17, 0.5, 1.5)],
