@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -472,6 +473,7 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
             // so CTAs hold one ticket at a time (see the kernel's "lazy" mode)
             const bool handful = !short_rows && seqlen > 8192 && numseq < 32;
             pl.lazy_default = handful;
+            auto padded = [&](int64_t tile) { return ceil_div(seqlen, tile) * tile; };   // slots a row takes in tiles of this size
             if (handful) {
                 E = 16; NT = 512; S = 1; OB = 1;
             } else if (sz == 4) {
@@ -480,7 +482,16 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
                 // (a small forward problem of rows that fit the 4096-element tile: twice as many tiles
                 // balance better over the SMs -- (512, 4096): 10.6 instead of 12.5 us per launch)
                 const bool small = seqlen <= 4096 && numseq * seqlen < 4LL * sm_count * 8192;
-                if (!bwd)                          { E = 16; NT = small ? 256 : 512; S = 2; OB = 1; }
+                if (!bwd) {
+                    E = 16; NT = small ? 256 : 512; S = 2; OB = 1;
+                    // chained rows whose last 8192-element piece is mostly empty: a nearly empty tile costs
+                    // almost what a full one does, so take the tile that pads the row least
+                    // ((4096, 65568): 6094 -> 6450 GB/s, (26800, 10016): < 6000 -> 6500)
+                    if (seqlen > 8192 && !few_rows && padded(8192) * 100 > std::min(padded(4096), padded(2048)) * 101) {
+                        if (padded(4096) * 100 <= padded(2048) * 102) { NT = 256; S = 2; }
+                        else                                          { NT = 128; S = 3; }
+                    }
+                }
                 else if (seqlen <= 8192 || few_rows) { E = 16; NT = 512; S = 1; OB = 1; }
                 else                               { E = 16; NT = 128; S = 1; OB = 1; }
             } else {
@@ -492,7 +503,7 @@ int make_plan(Plan& pl, int kind, bool bwd, int dtype, int64_t numseq, int64_t s
                 // tile) keeps the predecessor a whole round back.
                 if (short_rows)     { E = 16; NT = 128; S = bwd ? 2 : 3; OB = 1; }
                 else if (few_rows)  { E = 32; NT = 512; S = bwd ? 1 : 2; OB = 1; }
-                else if (!bwd)      { E = 32; NT = 256; S = 2; OB = 1; }
+                else if (!bwd)      { E = 32; NT = (seqlen > 8192 && padded(8192) * 100 > padded(4096) * 101) ? 128 : 256; S = 2; OB = 1; }
                 else                { E = 32; NT = 128; S = 2; OB = 1; }
             }
         }

@@ -119,10 +119,6 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
 {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ float4 ld_relaxed_sys_f32x4(const float4* p)
 {
     float4 v;
