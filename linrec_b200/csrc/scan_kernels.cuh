@@ -300,44 +300,69 @@ linrec_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __grid_const
             !open && (p.chain ? (tc.q == 0 && (ASC ? g.t == 0 : g.t == tc.valid / E - 1)) : (g.k == 0));
 
         bool alive = true;
-        auto after_read = [&]() -> bool {
-            // the output buffer about to be reused must have been drained by its bulk store
-            if (tid == boss) ptx::tma_wait_group_read<OB - 1>();
-            __syncthreads();
-            if (abort_flag) {
-                alive = false;
-                return false;
-            }
-            if (tid == boss && !lazy) {   // ring slot s is free again: refill it with the ticket drawn earlier
-                tile_of_stage[s] = next_ticket;
-                if (next_ticket < ntiles) issue(s, next_ticket);
-                next_ticket = dyn_base + atomicAdd(p.header, 1u);
-            }
-            return true;
-        };
         const int ob = (int)(it % OB);
-        if (!p.chain && __all_sync(0xffffffffu, g.row_in_tile >= p.rows_per_tile)) {
-            // A whole warp in the fragment behind the last whole row of an unchained tile (rows a little
-            // longer than half a tile: almost half the warps) holds no element: it contributes the
-            // identity and keeps only its roles -- the barriers and, if it has the issuing thread, the
-            // copies.  The slots it leaves unwritten lie outside the box of the bulk store.
-            // (A separate path on purpose: guarding the steps of the common path with a flag instead
-            // cost chained forward scans a third of their speed.)
-            if (g.ls == 31) wagg[g.ws] = pair_identity();
-            (void)after_read();
-        } else {
+        if constexpr (!BWD) {
             Operands<E, BWD> op;
-            load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1),
-                                                     BWD ? in_buf(s, 2) : in_buf(s, 1), pred_c, succ_y,
+            load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1), in_buf(s, 1), pred_c, succ_y,
                                                      tc.valid, zero_first, p.logc != 0);
-            float o0[E], o1[BWD ? E : 1];
-            tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, after_read);
-            if (alive) {
-                store_run<ST, E>(out_buf(ob, 0), g.t, o0);
-                if constexpr (BWD) store_run<ST, E>(out_buf(ob, 1), g.t, o1);
+            float o0[E], o1[1];
+            tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, [&]() -> bool {
+                // the output buffer about to be reused must have been drained by its bulk store
+                if (tid == boss) ptx::tma_wait_group_read<OB - 1>();
+                __syncthreads();
+                if (abort_flag) {
+                    alive = false;
+                    return false;
+                }
+                if (tid == boss && !lazy) {   // ring slot s is free again: refill it with the ticket drawn earlier
+                    tile_of_stage[s] = next_ticket;
+                    if (next_ticket < ntiles) issue(s, next_ticket);
+                    next_ticket = dyn_base + atomicAdd(p.header, 1u);
+                }
+                return true;
+            });
+            if (!alive) break;
+            store_run<ST, E>(out_buf(ob, 0), g.t, o0);
+        } else {
+            // Backward kernels only.  A whole warp in the fragment behind the last whole row of an
+            // unchained tile (rows a little longer than half a tile: almost half the warps) holds no
+            // element: it contributes the identity and keeps only its roles -- the barriers and, if it
+            // has the issuing thread, the copies.  The slots it leaves unwritten lie outside the box of
+            // the bulk store.  It is a path of its own (guarding the steps of the common path with a
+            // flag instead cost chained scans a third of their speed), and the forward kernels keep
+            // their one straight path: with this shape the compiler schedules the common path of the
+            // backward kernels better (0-15 % over the length sweep, 2-byte storage most) and that of
+            // the forward kernels worse (up to 10 %).
+            auto after_read = [&]() -> bool {
+                if (tid == boss) ptx::tma_wait_group_read<OB - 1>();   // as above
+                __syncthreads();
+                if (abort_flag) {
+                    alive = false;
+                    return false;
+                }
+                if (tid == boss && !lazy) {
+                    tile_of_stage[s] = next_ticket;
+                    if (next_ticket < ntiles) issue(s, next_ticket);
+                    next_ticket = dyn_base + atomicAdd(p.header, 1u);
+                }
+                return true;
+            };
+            if (!p.chain && __all_sync(0xffffffffu, g.row_in_tile >= p.rows_per_tile)) {
+                if (g.ls == 31) wagg[g.ws] = pair_identity();
+                (void)after_read();
+            } else {
+                Operands<E, BWD> op;
+                load_operands<ST, E, NT, BWD, ASC, true>(op, g, in_buf(s, 0), in_buf(s, 1), in_buf(s, 2), pred_c, succ_y,
+                                                         tc.valid, zero_first, p.logc != 0);
+                float o0[E], o1[E];
+                tile_scan<ST, E, NT, BWD, ASC>(p, g, op, tc, tk, next_tk, epoch, probe, wagg, &chain_sh, o0, o1, after_read);
+                if (alive) {
+                    store_run<ST, E>(out_buf(ob, 0), g.t, o0);
+                    store_run<ST, E>(out_buf(ob, 1), g.t, o1);
+                }
             }
+            if (!alive) break;
         }
-        if (!alive) break;
         ptx::fence_proxy_async_smem();
         __syncthreads();
         if (tid == boss) {
