@@ -47,9 +47,11 @@ extern "C" {
 #define LINREC_DTYPE_F32   0
 #define LINREC_DTYPE_BF16  1
 #define LINREC_DTYPE_F16   2
-#define LINREC_DTYPE_F64   3   /* fp64 storage AND arithmetic; LINREC_KIND_REF only (the type dispatch the
-                                  reference leaves open, linrec/impl/cuda/linrec_pipe.cu:22); other kinds
-                                  and the sharding entry points answer LINREC_ERR_NOT_IMPLEMENTED */
+#define LINREC_DTYPE_F64   3   /* fp64 storage AND arithmetic (the type dispatch the reference leaves open,
+                                  linrec/impl/cuda/linrec_pipe.cu:22): LINREC_KIND_REF one thread per row,
+                                  the other kinds one CTA per row (no variants to pin: pinning options answer
+                                  LINREC_ERR_NOT_IMPLEMENTED, as do the middle-axis, static-buffer and
+                                  sharding entry points) */
 
 /* ---- which family of kernels a call may use --------------------------------------------------
  * The reference exposes three operator families with one signature

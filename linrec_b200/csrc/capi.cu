@@ -639,8 +639,22 @@ int launch_scan_direct(int kind, bool bwd, const void* in0, const void* c, const
     // the gradient scan runs against the direction of the forward pass
     const bool asc = bwd ? (reverse != 0) : (reverse == 0);
 
-    // double precision: the sequential operator only (fp64 storage and arithmetic)
-    if (dtype == LINREC_DTYPE_F64 && (kind != LINREC_KIND_REF || carry_out || exchange || open_start)) return LINREC_ERR_NOT_IMPLEMENTED;
+    // double precision (fp64 storage and arithmetic): the sequential operator, and for the tiled families
+    // one kernel that gives every row to one CTA (no look-back, no workspace, no variants to pin)
+    if (dtype == LINREC_DTYPE_F64 && (carry_out || exchange || open_start)) return LINREC_ERR_NOT_IMPLEMENTED;
+    if (dtype == LINREC_DTYPE_F64 && kind != LINREC_KIND_REF) {
+        if (opt.E >= 0 || opt.NT >= 0 || opt.S >= 0 || opt.OB >= 0 || opt.memcode >= 0) return LINREC_ERR_NOT_IMPLEMENTED;
+        const unsigned blocks = (unsigned)std::min<int64_t>(numseq, (int64_t)dev.sm_count * 8);
+        if (bwd) {
+            if (asc) linrec::linrec_row_f64_kernel<true, true><<<blocks, 256, 0, stream>>>(p);
+            else     linrec::linrec_row_f64_kernel<true, false><<<blocks, 256, 0, stream>>>(p);
+        } else {
+            if (asc) linrec::linrec_row_f64_kernel<false, true><<<blocks, 256, 0, stream>>>(p);
+            else     linrec::linrec_row_f64_kernel<false, false><<<blocks, 256, 0, stream>>>(p);
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return launch_result("kernel launch");
+    }
     if (kind == LINREC_KIND_REF) {
         if (carry_out) return LINREC_ERR_NOT_IMPLEMENTED;
         const int threads = dtype == LINREC_DTYPE_F64 ? 32 : 128;   // fp64 is the checker: spread few rows over many SMs

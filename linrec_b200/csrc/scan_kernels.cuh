@@ -10,6 +10,7 @@
 //                          checks: any length, any (element-aligned) pointer, any row stride.
 //   linrec_seq_kernel      one thread walks one row (the slow, obviously-right operator that the
 //                          reference exposes as linrec_ref: linrec/impl/cuda/linrec_ref.cuh:53-94).
+//   linrec_row_f64_kernel  double precision: one CTA per row, the carry kept by the CTA.
 //   linrec_fixup_kernel    sequence sharding: adds carry_in * running product of c to a shard.
 //
 // Replaces linrec/impl/cuda/linrec_pipe.cuh:8-143 and linrec/impl/cuda/linrec_tile.cuh:158-249.
@@ -902,6 +903,122 @@ __global__ void linrec_seq_f64_kernel(const ScanParams p, int reverse)
             double ys = (n == L - 1) ? 0.0 : y[is];
             if (p.logc) ys *= exp(c[i]);
             out1[i] = v * ys;
+        }
+    }
+}
+
+// =================================================================================================
+//  Double precision: one CTA walks one row
+// =================================================================================================
+// fp64 storage and arithmetic for linrec_pipe / linrec_tile (the dtype dispatch that the reference leaves
+// as a TODO, linrec/impl/cuda/linrec_pipe.cu:22) with the reference's own decomposition -- one CTA per
+// row, the row taken tile by tile with the carry kept by the CTA (linrec/impl/cuda/linrec_pipe.cuh:8-70)
+// -- so no look-back and no workspace: two doubles and a state would not fit the 16-byte descriptor word.
+// A tile is 256 threads x 4 consecutive elements; per tile a thread folds its elements into a (Y, P)
+// pair, the warp scans the pairs by shuffles, the warps' totals meet in shared memory (two sets taking
+// turns: one barrier per tile), and every thread reruns its elements from the true value that enters
+// them.  The next tile's operands are requested before the current tile is worked on.  Any row length,
+// any 8-byte aligned pointer, any row stride.  Rows are dealt to the CTAs round-robin: it needs a few
+// hundred rows to fill the GPU, and the sequential operator remains the one for a handful of rows.
+struct PairD {
+    double y, p;
+};
+__device__ __forceinline__ PairD combine_d(PairD far, PairD near) { return PairD{fma(far.y, near.p, near.y), far.p * near.p}; }
+
+template <bool BWD, bool ASC>
+__global__ void __launch_bounds__(256) linrec_row_f64_kernel(const ScanParams p)
+{
+    constexpr int NT = 256, E = 4, NW = NT / 32, T = NT * E;
+    __shared__ PairD wagg[2][NW];
+    const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const long long L = p.seqlen;
+    const bool logc = p.logc != 0;
+    int par = 0;   // runs on across rows, so that consecutive tiles never share a set of totals
+
+    struct Ops {
+        double x[E], c[E], ys[BWD ? E : 1];
+    };
+    for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
+        const long long rb = row * p.row_stride;
+        const double* in0 = reinterpret_cast<const double*>(p.in0) + rb;
+        const double* c = reinterpret_cast<const double*>(p.c) + rb;
+        const double* y = BWD ? reinterpret_cast<const double*>(p.yin) + rb : nullptr;
+        double* out0 = reinterpret_cast<double*>(p.out0) + rb;
+        double* out1 = BWD ? reinterpret_cast<double*>(p.out1) + rb : nullptr;
+
+        // operands of the tile that starts at scan position `base`, in scan order.  Forward: the
+        // coefficient of an element is its own (none for the row's first); backward: the coefficient
+        // at the scan PREDECESSOR's place and, for d_coeffs, the output at the scan SUCCESSOR's place
+        // (linrec/impl/python/ops.py:32-40).  Beyond the row: identity elements.
+        auto fetch = [&](long long base, Ops& o) {
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const long long n = base + (long long)tid * E + j;
+                o.x[j] = 0.0;
+                o.c[j] = 1.0;
+                if (BWD) o.ys[j] = 0.0;
+                if (n < L) {
+                    const long long m = ASC ? n : L - 1 - n;
+                    o.x[j] = in0[m];
+                    if (!BWD) {
+                        const double cc = logc ? exp(c[m]) : c[m];
+                        o.c[j] = n == 0 ? 0.0 : cc;
+                    } else {
+                        const long long mp = ASC ? m - 1 : m + 1, ms = ASC ? m + 1 : m - 1;
+                        o.c[j] = n == 0 ? 0.0 : (logc ? exp(c[mp]) : c[mp]);
+                        double yy = n == L - 1 ? 0.0 : y[ms];
+                        if (logc) yy *= exp(c[m]);   // gradient with respect to the logarithm
+                        o.ys[j] = yy;
+                    }
+                }
+            }
+        };
+
+        double carry = 0.0;   // the scan's value at the end of the previous tile
+        Ops cur, nxt;
+        fetch(0, cur);
+        for (long long base = 0; base < L; base += T, par ^= 1) {
+            if (base + T < L) fetch(base + T, nxt);
+            PairD inc{0.0, 1.0};
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                inc.y = fma(inc.y, cur.c[j], cur.x[j]);
+                inc.p *= cur.c[j];
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                PairD far;
+                far.y = __shfl_up_sync(0xffffffffu, inc.y, d);
+                far.p = __shfl_up_sync(0xffffffffu, inc.p, d);
+                if (lane >= d) inc = combine_d(far, inc);
+            }
+            PairD ex;
+            ex.y = __shfl_up_sync(0xffffffffu, inc.y, 1);
+            ex.p = __shfl_up_sync(0xffffffffu, inc.p, 1);
+            if (lane == 0) ex = PairD{0.0, 1.0};
+            if (lane == 31) wagg[par][w] = inc;
+            __syncthreads();
+            PairD pre{0.0, 1.0}, total{0.0, 1.0};
+#pragma unroll
+            for (int ww = 0; ww < NW; ++ww) {
+                const PairD g = wagg[par][ww];
+                if (ww < w) pre = combine_d(pre, g);
+                total = combine_d(total, g);
+            }
+            pre = combine_d(pre, ex);
+            double v = fma(carry, pre.p, pre.y);   // the true value that enters this thread's elements
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                v = fma(v, cur.c[j], cur.x[j]);
+                const long long n = base + (long long)tid * E + j;
+                if (n < L) {
+                    const long long m = ASC ? n : L - 1 - n;
+                    out0[m] = v;
+                    if (BWD) out1[m] = v * cur.ys[j];
+                }
+            }
+            carry = fma(carry, total.p, total.y);
+            cur = nxt;
         }
     }
 }

@@ -27,7 +27,7 @@ from . import _capi
 __all__ = ["linrec_ref", "linrec_tile", "linrec_pipe"]
 
 _DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16, torch.float16: _capi.DTYPE_F16,
-           torch.float64: _capi.DTYPE_F64}   # float64: the sequential family (linrec_ref) only
+           torch.float64: _capi.DTYPE_F64}   # float64: linrec_ref, and linrec_pipe / linrec_tile by one CTA per row
 _CHECK_EVERY_CALL = os.environ.get("LINREC_B200_CHECK", "0") not in ("0", "")
 
 # ---- workspace cache: one scratch buffer per (device, stream) --------------------------------------
@@ -86,7 +86,7 @@ def _check_same(*ts: torch.Tensor) -> None:
     if not all(t.is_cuda for t in ts):
         raise RuntimeError("linrec: tensors must be CUDA tensors (there is no CPU implementation)")
     if a.dtype not in _DTYPES:
-        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16, float16; float64 for linrec_ref)")
+        raise RuntimeError(f"linrec: dtype {a.dtype} is not supported (float32, bfloat16, float16, float64)")
     if a.dim() == 0:
         raise RuntimeError("linrec: need at least one dimension")
     if a.numel() > 0 and a.stride(-1) != 1:

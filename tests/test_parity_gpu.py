@@ -824,7 +824,7 @@ def test_call_from_a_fresh_host_thread():
 @pytest.mark.parametrize("rev", [False, True])
 def test_float64_sequential_operator(shape, rev):
     """fp64 storage and arithmetic through `linrec_ref` (the dtype dispatch the reference leaves as a
-    TODO, linrec_pipe.cu:22), against the fp64 oracle at rtol 1e-10; the tiled families refuse fp64."""
+    TODO, linrec_pipe.cu:22), against the fp64 oracle at rtol 1e-10."""
     lb = _ops()
     dev = torch.device("cuda:0")
     x, c, dy = _data(shape, clo=0.9)
@@ -842,8 +842,50 @@ def test_float64_sequential_operator(shape, rev):
     gx, gc = torch.autograd.grad(lb.linrec_ref(xd, cd, reverse=rev), (xd, cd), dy.double().to(dev))
     np.testing.assert_allclose(gx.cpu().numpy(), dx_ref, rtol=1e-10, atol=1e-12)
     np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=1e-10, atol=1e-12)
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (5, 17), (64, 1024), (3, 20000), (300, 5001), (2, 1025), (700, 4096)],
+                         ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("rev", [False, True])
+def test_float64_tiled_families(shape, rev):
+    """fp64 through `linrec_pipe` / `linrec_tile` / `linrec` (one CTA per row, the carry kept by the CTA),
+    forward, backward and autograd, against the fp64 oracle at rtol 1e-10; padded rows; coefficients
+    given as logarithms; a pinned variant is refused (there are none to pin for this type)."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    x, c, dy = _data(shape, clo=0.9)
+    xd, cd, dyd = x.double().to(dev), c.double().to(dev), dy.double().to(dev)
+    y_ref = oracle.fwd_f64(x.numpy(), c.numpy(), reverse=rev)
+    for op in (lb._C.linrec_pipe_fwd, lb._C.linrec_tile_fwd):
+        y = op(inputs=xd, coeffs=cd, reverse=rev)
+        assert y.dtype == torch.float64
+        np.testing.assert_allclose(y.cpu().numpy(), y_ref, rtol=1e-10, atol=1e-12)
+    dx_ref, dc_ref = oracle.bwd_f64(dy.numpy(), c.numpy(), y_ref, reverse=rev)
+    yd = torch.from_numpy(y_ref).to(dev)
+    for op in (lb._C.linrec_pipe_bwd, lb._C.linrec_tile_bwd):
+        dx, dc = op(d_outputs=dyd, coeffs=cd, outputs=yd, reverse=rev)
+        np.testing.assert_allclose(dx.cpu().numpy(), dx_ref, rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(dc.cpu().numpy(), dc_ref, rtol=1e-10, atol=1e-12)
+    xg, cg = xd.clone().requires_grad_(True), cd.clone().requires_grad_(True)
+    gx, gc = torch.autograd.grad(lb.linrec(xg, cg, reverse=rev), (xg, cg), dyd)
+    np.testing.assert_allclose(gx.cpu().numpy(), dx_ref, rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(gc.cpu().numpy(), dc_ref, rtol=1e-10, atol=1e-12)
+    # rows with a stride larger than their length, guard columns untouched
+    rows, L = shape
+    pad = 3
+    def padded(t, fill):
+        full = torch.full((rows, L + pad), fill, dtype=torch.float64, device=dev)
+        full[:, :L] = t
+        return full[:, :L]
+    yp = lb._C.linrec_pipe_fwd(inputs=padded(xd, 7.0), coeffs=padded(cd, 7.0), reverse=rev)
+    np.testing.assert_allclose(yp.cpu().numpy(), y_ref, rtol=1e-10, atol=1e-12)
+    # logarithmic coefficients: exp inside the kernel
+    from linrec_b200.general import linrec_general
+    yl = linrec_general(xd, cd.log(), logc=True, reverse=rev)
+    np.testing.assert_allclose(yl.cpu().numpy(), y_ref, rtol=1e-9, atol=1e-11)
     with pytest.raises(NotImplementedError):
-        lb._C.linrec_pipe_fwd(inputs=x.double().to(dev), coeffs=c.double().to(dev), reverse=rev)
+        lb._C.linrec_pipe_fwd(inputs=xd, coeffs=cd, reverse=rev, kThreadsPerBlock=256)
+    lb.check_status()
 
 
 # ---- bounded waits -----------------------------------------------------------------------------------
