@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 #include <utility>
 #include <vector>
@@ -645,13 +646,16 @@ int launch_scan_direct(int kind, bool bwd, const void* in0, const void* c, const
     if (dtype == LINREC_DTYPE_F64 && kind != LINREC_KIND_REF) {
         if (opt.E >= 0 || opt.NT >= 0 || opt.S >= 0 || opt.OB >= 0 || opt.memcode >= 0) return LINREC_ERR_NOT_IMPLEMENTED;
         const unsigned blocks = (unsigned)std::min<int64_t>(numseq, (int64_t)dev.sm_count * 8);
-        if (bwd) {
-            if (asc) linrec::linrec_row_f64_kernel<true, true><<<blocks, 256, 0, stream>>>(p);
-            else     linrec::linrec_row_f64_kernel<true, false><<<blocks, 256, 0, stream>>>(p);
-        } else {
-            if (asc) linrec::linrec_row_f64_kernel<false, true><<<blocks, 256, 0, stream>>>(p);
-            else     linrec::linrec_row_f64_kernel<false, false><<<blocks, 256, 0, stream>>>(p);
-        }
+        bool vec = row_stride % 2 == 0 && (asc || seqlen % 2 == 0);
+        for (const void* q : ptrs) vec = vec && reinterpret_cast<uintptr_t>(q) % 16 == 0;
+        auto launch = [&](auto kernel) { kernel<<<blocks, 256, 0, stream>>>(p); };
+        auto pick = [&](auto bwd_c, auto asc_c) {
+            constexpr bool B = decltype(bwd_c)::value, A = decltype(asc_c)::value;
+            if (vec) { if (opt.logc) launch(linrec::linrec_row_f64_kernel<B, A, true, true>); else launch(linrec::linrec_row_f64_kernel<B, A, true, false>); }
+            else     { if (opt.logc) launch(linrec::linrec_row_f64_kernel<B, A, false, true>); else launch(linrec::linrec_row_f64_kernel<B, A, false, false>); }
+        };
+        if (bwd) { if (asc) pick(std::true_type{}, std::true_type{}); else pick(std::true_type{}, std::false_type{}); }
+        else     { if (asc) pick(std::false_type{}, std::true_type{}); else pick(std::false_type{}, std::false_type{}); }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return launch_result("kernel launch");
     }

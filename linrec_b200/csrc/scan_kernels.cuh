@@ -918,25 +918,31 @@ __global__ void linrec_seq_f64_kernel(const ScanParams p, int reverse)
 // pair, the warp scans the pairs by shuffles, the warps' totals meet in shared memory (two sets taking
 // turns: one barrier per tile), and every thread reruns its elements from the true value that enters
 // them.  The next tile's operands are requested before the current tile is worked on.  Any row length,
-// any 8-byte aligned pointer, any row stride.  Rows are dealt to the CTAs round-robin: it needs a few
+// any 8-byte aligned pointer, any row stride (16-byte accesses where the layout allows them).  Rows are dealt to the CTAs round-robin: it needs a few
 // hundred rows to fill the GPU, and the sequential operator remains the one for a handful of rows.
 struct PairD {
     double y, p;
 };
 __device__ __forceinline__ PairD combine_d(PairD far, PairD near) { return PairD{fma(far.y, near.p, near.y), far.p * near.p}; }
 
-template <bool BWD, bool ASC>
-__global__ void __launch_bounds__(256) linrec_row_f64_kernel(const ScanParams p)
+template <bool BWD, bool ASC, bool VEC, bool LOGC>
+__global__ void __launch_bounds__(256, BWD ? 2 : 4) linrec_row_f64_kernel(const ScanParams p)
 {
+    // VEC: every row starts on a 16-byte boundary and a thread's four elements do too (the host has
+    // checked pointers, row stride and -- for descending scans -- an even row length): the unshifted
+    // operands and the results go as 16-byte accesses.  LOGC: coefficients are given as logarithms.
     constexpr int NT = 256, E = 4, NW = NT / 32, T = NT * E;
     __shared__ PairD wagg[2][NW];
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
     const long long L = p.seqlen;
-    const bool logc = p.logc != 0;
     int par = 0;   // runs on across rows, so that consecutive tiles never share a set of totals
 
+    // What a thread requests for one tile: its own four elements of every operand as they lie in memory
+    // (backward: plus the coefficient just before and the output just after its run in scan order, which
+    // only a warp's edge lanes load themselves).  Nothing is computed from them until the tile is worked
+    // on, so that the loads of the next tile stay in flight behind the arithmetic of the current one.
     struct Ops {
-        double x[E], c[E], ys[BWD ? E : 1];
+        double x[E], c[E], y[BWD ? E : 1], c_edge, y_edge;
     };
     for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
         const long long rb = row * p.row_stride;
@@ -946,30 +952,74 @@ __global__ void __launch_bounds__(256) linrec_row_f64_kernel(const ScanParams p)
         double* out0 = reinterpret_cast<double*>(p.out0) + rb;
         double* out1 = BWD ? reinterpret_cast<double*>(p.out1) + rb : nullptr;
 
-        // operands of the tile that starts at scan position `base`, in scan order.  Forward: the
-        // coefficient of an element is its own (none for the row's first); backward: the coefficient
-        // at the scan PREDECESSOR's place and, for d_coeffs, the output at the scan SUCCESSOR's place
-        // (linrec/impl/python/ops.py:32-40).  Beyond the row: identity elements.
-        auto fetch = [&](long long base, Ops& o) {
+        // four consecutive elements of an array in SCAN order, starting at scan position n0
+        auto load4 = [&](const double* a, long long n0, double (&v)[E], double fill) {
+            if (VEC && n0 + E <= L) {
+                const long long m0 = ASC ? n0 : L - n0 - E;
+                const double2 lo = *reinterpret_cast<const double2*>(a + m0);
+                const double2 hi = *reinterpret_cast<const double2*>(a + m0 + 2);
+                v[ASC ? 0 : 3] = lo.x; v[ASC ? 1 : 2] = lo.y; v[ASC ? 2 : 1] = hi.x; v[ASC ? 3 : 0] = hi.y;
+            } else {
 #pragma unroll
-            for (int j = 0; j < E; ++j) {
-                const long long n = base + (long long)tid * E + j;
-                o.x[j] = 0.0;
-                o.c[j] = 1.0;
-                if (BWD) o.ys[j] = 0.0;
-                if (n < L) {
-                    const long long m = ASC ? n : L - 1 - n;
-                    o.x[j] = in0[m];
-                    if (!BWD) {
-                        const double cc = logc ? exp(c[m]) : c[m];
-                        o.c[j] = n == 0 ? 0.0 : cc;
-                    } else {
-                        const long long mp = ASC ? m - 1 : m + 1, ms = ASC ? m + 1 : m - 1;
-                        o.c[j] = n == 0 ? 0.0 : (logc ? exp(c[mp]) : c[mp]);
-                        double yy = n == L - 1 ? 0.0 : y[ms];
-                        if (logc) yy *= exp(c[m]);   // gradient with respect to the logarithm
-                        o.ys[j] = yy;
-                    }
+                for (int j = 0; j < E; ++j) {
+                    const long long n = n0 + j;
+                    v[j] = n < L ? a[ASC ? n : L - 1 - n] : fill;
+                }
+            }
+        };
+        auto store4 = [&](double* a, long long n0, const double (&v)[E]) {
+            if (VEC && n0 + E <= L) {
+                const long long m0 = ASC ? n0 : L - n0 - E;
+                *reinterpret_cast<double2*>(a + m0) = make_double2(v[ASC ? 0 : 3], v[ASC ? 1 : 2]);
+                *reinterpret_cast<double2*>(a + m0 + 2) = make_double2(v[ASC ? 2 : 1], v[ASC ? 3 : 0]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    const long long n = n0 + j;
+                    if (n < L) a[ASC ? n : L - 1 - n] = v[j];
+                }
+            }
+        };
+
+        auto fetch = [&](long long base, Ops& o) {
+            const long long n0 = base + (long long)tid * E;
+            load4(in0, n0, o.x, 0.0);
+            load4(c, n0, o.c, LOGC ? 0.0 : 1.0);
+            if constexpr (BWD) {
+                load4(y, n0, o.y, 0.0);
+                o.c_edge = 1.0;
+                o.y_edge = 0.0;
+                if (lane == 0 && n0 >= 1 && n0 - 1 < L) o.c_edge = c[ASC ? n0 - 1 : L - n0];
+                if (lane == 31 && n0 + E < L) o.y_edge = y[ASC ? n0 + E : L - 1 - n0 - E];
+            }
+        };
+        // The operands of the scan proper, in scan order.  Forward: the coefficient of an element is its
+        // own (none for the row's first).  Backward: the coefficient at the scan PREDECESSOR's place and,
+        // for d_coeffs, the output at the scan SUCCESSOR's place (linrec/impl/python/ops.py:32-40); the
+        // neighbour just outside a thread's run comes from the adjacent lane by shuffle.  Beyond the
+        // row: identity elements.
+        auto prepare = [&](long long base, const Ops& o, double (&cc)[E], double (&ys)[BWD ? E : 1]) {
+            const long long n0 = base + (long long)tid * E;
+            if constexpr (!BWD) {
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    cc[j] = LOGC ? exp(o.c[j]) : o.c[j];
+                    if (n0 + j == 0) cc[j] = 0.0;
+                }
+            } else {
+                double c_pred = __shfl_up_sync(0xffffffffu, o.c[E - 1], 1);
+                double y_succ = __shfl_down_sync(0xffffffffu, o.y[0], 1);
+                if (lane == 0) c_pred = o.c_edge;
+                if (lane == 31) y_succ = o.y_edge;
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    const long long n = n0 + j;
+                    double cp = j == 0 ? c_pred : o.c[j - 1];
+                    if (LOGC) cp = exp(cp);
+                    cc[j] = n == 0 ? 0.0 : (n < L ? cp : 1.0);
+                    double yy = j == E - 1 ? y_succ : o.y[j + 1];
+                    if (LOGC) yy *= exp(o.c[j]);   // gradient with respect to the logarithm
+                    ys[j] = n < L - 1 ? yy : 0.0;
                 }
             }
         };
@@ -979,11 +1029,13 @@ __global__ void __launch_bounds__(256) linrec_row_f64_kernel(const ScanParams p)
         fetch(0, cur);
         for (long long base = 0; base < L; base += T, par ^= 1) {
             if (base + T < L) fetch(base + T, nxt);
+            double cc[E], ys[BWD ? E : 1];
+            prepare(base, cur, cc, ys);
             PairD inc{0.0, 1.0};
 #pragma unroll
             for (int j = 0; j < E; ++j) {
-                inc.y = fma(inc.y, cur.c[j], cur.x[j]);
-                inc.p *= cur.c[j];
+                inc.y = fma(inc.y, cc[j], cur.x[j]);
+                inc.p *= cc[j];
             }
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
@@ -1007,16 +1059,16 @@ __global__ void __launch_bounds__(256) linrec_row_f64_kernel(const ScanParams p)
             }
             pre = combine_d(pre, ex);
             double v = fma(carry, pre.p, pre.y);   // the true value that enters this thread's elements
+            double r0[E], r1[BWD ? E : 1];
 #pragma unroll
             for (int j = 0; j < E; ++j) {
-                v = fma(v, cur.c[j], cur.x[j]);
-                const long long n = base + (long long)tid * E + j;
-                if (n < L) {
-                    const long long m = ASC ? n : L - 1 - n;
-                    out0[m] = v;
-                    if (BWD) out1[m] = v * cur.ys[j];
-                }
+                v = fma(v, cc[j], cur.x[j]);
+                r0[j] = v;
+                if constexpr (BWD) r1[j] = v * ys[j];
             }
+            const long long n0 = base + (long long)tid * E;
+            store4(out0, n0, r0);
+            if constexpr (BWD) store4(out1, n0, r1);
             carry = fma(carry, total.p, total.y);
             cur = nxt;
         }
