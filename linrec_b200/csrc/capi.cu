@@ -69,7 +69,10 @@ constexpr int kNumConfigNames = 5;
 // memcode: 0 = plain coalesced loads/stores staged through shared memory (any alignment),
 //          1 = tiled bulk-tensor copies (TMA) through an mbarrier ring (rows of whole 128-byte lines),
 //          2 = 16-byte cp.async through a two-slot ring (16-byte aligned rows of whole 16-byte chunks),
-//          3 = 4-byte cp.async through a two-slot ring (4-byte aligned rows of whole 4-byte words).
+//          3 = 4-byte cp.async through a two-slot ring (4-byte aligned rows of whole 4-byte words),
+//          4 = one CTA per row with aligned 16-byte accesses (any length and offset; chosen by itself for
+//              rows that 1 and 2 cannot take when there are several rows per SM; not in the variant
+//              list: it has no tile parameters to pin).
 
 struct Options {
     int E = -1, NT = -1, S = -1, OB = -1, memcode = -1;
@@ -658,6 +661,45 @@ int launch_scan_direct(int kind, bool bwd, const void* in0, const void* c, const
         else     { if (asc) pick(std::false_type{}, std::true_type{}); else pick(std::false_type{}, std::false_type{}); }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return launch_result("kernel launch");
+    }
+    // Rows that neither the bulk copies nor the 16-byte chunk copies can take (odd lengths, rows that
+    // start off a 16-byte boundary): with enough rows to give every SM several, one CTA walks one row
+    // with aligned 16-byte accesses (`memcode` 4; not a member of the variant list: it has no tile
+    // parameters to pin).  (268167, 1001) fp32: 3.9 / 4.3 TB/s with the 4-byte copies.
+    if (kind != LINREC_KIND_REF && dtype != LINREC_DTYPE_F64 && !carry_out && !exchange && !open_start &&
+        (opt.memcode == 4 || (opt.memcode < 0 && opt.E < 0 && opt.NT < 0 && opt.S < 0 && opt.OB < 0))) {
+        bool same_offset = true;
+        for (const void* q : ptrs)
+            same_offset = same_offset && reinterpret_cast<uintptr_t>(q) % 16 == reinterpret_cast<uintptr_t>(in0) % 16;
+        const int sz = dtype == LINREC_DTYPE_F32 ? 4 : 2;
+        same_offset = same_offset && (reinterpret_cast<uintptr_t>(in0) % sz == 0);
+        const bool chunked = tma_eligible(dtype, numseq, seqlen, row_stride, ptrs, 5) || vec_eligible(dtype, seqlen, row_stride, ptrs, 5);
+        // (short rows leave most of a CTA idle: where the 4-byte copies can take them they win below
+        //  ~400 elements -- (1000000, 265) fp32: 3.8 against 1.9 TB/s with 128 threads; plain loads never do)
+        const bool word_ok = word_eligible(dtype, seqlen, row_stride, ptrs, 5);
+        const bool wanted = opt.memcode == 4 || (!chunked && numseq >= 4LL * dev.sm_count && seqlen >= (word_ok ? 384 : 48));
+        if (opt.memcode == 4 && (!same_offset || (kind == LINREC_KIND_TILE && seqlen > 8192))) return LINREC_ERR_UNALIGNED;
+        if (wanted && same_offset && !(kind == LINREC_KIND_TILE && seqlen > 8192)) {
+            if (opt.E >= 0 || opt.NT >= 0 || opt.S >= 0 || opt.OB >= 0) return LINREC_ERR_NOT_IMPLEMENTED;
+            // threads per CTA (x 8 elements = one tile): the smallest tile that holds the row, up to 2048 elements
+            const int threads = seqlen > 1024 ? 256 : (seqlen > 512 ? 128 : 64);
+            const unsigned blocks = (unsigned)std::min<int64_t>(numseq, (int64_t)dev.sm_count * std::min(2048 / threads, 24));
+            auto launch = [&](auto kernel) { kernel<<<blocks, threads, 0, stream>>>(p); };
+            auto pick = [&](auto st, auto bwd_c, auto asc_c) {
+                using ST = decltype(st);
+                constexpr bool B = decltype(bwd_c)::value, A = decltype(asc_c)::value;
+                if (threads == 256)      launch(linrec::linrec_row_kernel<ST, 256, B, A>);
+                else if (threads == 128) launch(linrec::linrec_row_kernel<ST, 128, B, A>);
+                else                     launch(linrec::linrec_row_kernel<ST, 64, B, A>);
+            };
+            auto by_dir = [&](auto st) {
+                if (bwd) { if (asc) pick(st, std::true_type{}, std::true_type{}); else pick(st, std::true_type{}, std::false_type{}); }
+                else     { if (asc) pick(st, std::false_type{}, std::true_type{}); else pick(st, std::false_type{}, std::false_type{}); }
+            };
+            if (di == 0) by_dir(float{}); else if (di == 1) by_dir(__nv_bfloat16{}); else by_dir(__half{});
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return launch_result("kernel launch");
+        }
     }
     if (kind == LINREC_KIND_REF) {
         if (carry_out) return LINREC_ERR_NOT_IMPLEMENTED;

@@ -11,6 +11,7 @@
 //   linrec_seq_kernel      one thread walks one row (the slow, obviously-right operator that the
 //                          reference exposes as linrec_ref: linrec/impl/cuda/linrec_ref.cuh:53-94).
 //   linrec_row_f64_kernel  double precision: one CTA per row, the carry kept by the CTA.
+//   linrec_row_kernel      rows of any alignment (odd lengths): one CTA per row, aligned 16-byte accesses.
 //   linrec_fixup_kernel    sequence sharding: adds carry_in * running product of c to a shard.
 //
 // Replaces linrec/impl/cuda/linrec_pipe.cuh:8-143 and linrec/impl/cuda/linrec_tile.cuh:158-249.
@@ -1070,6 +1071,195 @@ __global__ void __launch_bounds__(256, BWD ? 2 : 4) linrec_row_f64_kernel(const 
             store4(out0, n0, r0);
             if constexpr (BWD) store4(out1, n0, r1);
             carry = fma(carry, total.p, total.y);
+            cur = nxt;
+        }
+    }
+}
+
+// =================================================================================================
+//  Rows of any alignment: one CTA walks one row with 16-byte accesses
+// =================================================================================================
+// Rows that start anywhere (odd lengths, sliced tensors) still lie in memory that can be read in
+// aligned 16-byte chunks: a row is given to one CTA, which walks the aligned span around it -- `off`
+// elements lie between the 16-byte boundary below the row start and the row start -- in tiles of
+// NT threads x 8 elements with the carry kept by the CTA (the reference's decomposition,
+// linrec/impl/cuda/linrec_pipe.cuh:8-70; no look-back, no workspace).  Elements of the span outside the
+// row are identity elements and are never stored; a chunk none of whose elements belongs to the row is
+// not read at all, and one that holds at least one element of the row lies in the same 16-byte word as
+// that element, so no access leaves the memory of the tensor's own words.  All arrays of a call must
+// share the row start's offset from a 16-byte boundary (the host checks it).  Otherwise the kernel is
+// the double-precision one above with fp32 arithmetic: thread fold, warp scan by shuffles, totals
+// through two sets of shared words (one barrier per tile), rerun from the true value; the next tile's
+// chunks are requested before the current tile is worked on and nothing is computed from them until
+// then.  It needs a few hundred rows to fill the GPU.
+template <typename ST, int NT, bool BWD, bool ASC>
+__global__ void __launch_bounds__(NT) linrec_row_kernel(const ScanParams p)
+{
+    constexpr int E = 8, PC = Storage<ST>::kPerChunk, NCH = E / PC, NW = NT / 32, T = NT * E;
+    __shared__ Pair wagg[2][NW];
+    const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const long long L = p.seqlen;
+    const bool logc = p.logc != 0;
+    int par = 0;   // runs on across rows, so that consecutive tiles never share a set of totals
+
+    // What a thread requests for one tile, in MEMORY order: its eight elements of every operand and
+    // (backward, a warp's edge lanes only) the coefficient just before and the output just after its
+    // run in scan order.
+    struct Ops {
+        float x[E], c[E], y[BWD ? E : 1], c_edge, y_edge;
+    };
+    for (long long row = blockIdx.x; row < p.numseq; row += gridDim.x) {
+        const long long rb = row * p.row_stride;
+        const ST* in0 = reinterpret_cast<const ST*>(p.in0) + rb;
+        const ST* c = reinterpret_cast<const ST*>(p.c) + rb;
+        const ST* y = BWD ? reinterpret_cast<const ST*>(p.yin) + rb : nullptr;
+        ST* out0 = reinterpret_cast<ST*>(p.out0) + rb;
+        ST* out1 = BWD ? reinterpret_cast<ST*>(p.out1) + rb : nullptr;
+        // Positions v = 0, 1, ... count elements from the 16-byte boundary below the row start; element
+        // e = v - off of the row lives at v.  The span is walked in whole runs of E positions.
+        const int off = (int)((reinterpret_cast<uintptr_t>(in0) / sizeof(ST)) % PC);
+        const long long Lv = (off + L + E - 1) / E * E;
+        // lowest position of the run whose first element in scan order is scan position s0
+        auto run_low = [&](long long s0) { return ASC ? s0 : Lv - s0 - E; };
+
+        auto load_run = [&](const ST* a, long long v0, float fill, float (&o)[E]) {
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const long long vv = v0 + k * PC;
+                if (vv + PC > off && vv < off + L) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(a + (vv - off));
+                    Storage<ST>::unpack(q, &o[k * PC]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < PC; ++i) o[k * PC + i] = fill;
+                }
+            }
+        };
+        auto store_run = [&](ST* a, long long v0, const float (&o)[E]) {
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const long long vv = v0 + k * PC;
+                if (vv >= off && vv + PC <= off + L) {
+                    *reinterpret_cast<uint4*>(a + (vv - off)) = Storage<ST>::pack(&o[k * PC]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < PC; ++i) {
+                        const long long e = vv + i - off;
+                        if (e >= 0 && e < L) a[e] = Storage<ST>::from_float(o[k * PC + i]);
+                    }
+                }
+            }
+        };
+        auto fetch = [&](long long base, Ops& o) {
+            const long long v0 = run_low(base + (long long)tid * E);
+            load_run(in0, v0, 0.0f, o.x);
+            load_run(c, v0, 0.0f, o.c);
+            if constexpr (BWD) {
+                load_run(y, v0, 0.0f, o.y);
+                o.c_edge = 1.0f;
+                o.y_edge = 0.0f;
+                // the neighbours just outside the run, at positions v0 - 1 and v0 + E
+                const long long below = v0 - 1 - off, above = v0 + E - off;
+                const long long ec = ASC ? below : above;      // scan predecessor of the run's first element
+                const long long ey = ASC ? above : below;      // scan successor of its last element
+                // (threads are in scan order either way: lane 0 has no predecessor lane, lane 31 no successor)
+                if (lane == 0 && ec >= 0 && ec < L) o.c_edge = Storage<ST>::to_float(c[ec]);
+                if (lane == 31 && ey >= 0 && ey < L) o.y_edge = Storage<ST>::to_float(y[ey]);
+            }
+        };
+
+        float carry = 0.0f;   // the scan's value at the end of the previous tile
+        Ops cur, nxt;
+        fetch(0, cur);
+        for (long long base = 0; base < Lv; base += T, par ^= 1) {
+            if (base + T < Lv) fetch(base + T, nxt);
+            const long long v0 = run_low(base + (long long)tid * E);
+            // Operands of the scan proper, memory order: the coefficient applied to the carry that
+            // enters a slot (forward: the element's own; backward: the one at its scan predecessor) and,
+            // backward, the output at its scan successor (linrec/impl/python/ops.py:32-40).
+            float cc[E], ys[BWD ? E : 1];
+            if constexpr (!BWD) {
+#pragma unroll
+                for (int j = 0; j < E; ++j) cc[j] = logc ? expf(cur.c[j]) : cur.c[j];
+            } else {
+                // Threads are in scan order: lane - 1 holds the run that precedes in the scan (ascending:
+                // the run below in memory, whose highest element is the neighbour; descending: the run
+                // above, whose lowest element is), lane + 1 the run that follows.
+                const float c_prev = __shfl_up_sync(0xffffffffu, cur.c[ASC ? E - 1 : 0], 1);
+                const float y_next = __shfl_down_sync(0xffffffffu, cur.y[ASC ? 0 : E - 1], 1);
+                const float c_pred_out = lane == 0 ? cur.c_edge : c_prev;
+                const float y_succ_out = lane == 31 ? cur.y_edge : y_next;
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    float cp, yy;
+                    if (ASC) {
+                        cp = j == 0 ? c_pred_out : cur.c[j - 1];
+                        yy = j == E - 1 ? y_succ_out : cur.y[j + 1];
+                    } else {
+                        cp = j == E - 1 ? c_pred_out : cur.c[j + 1];
+                        yy = j == 0 ? y_succ_out : cur.y[j - 1];
+                    }
+                    if (logc) {
+                        cp = expf(cp);
+                        yy *= expf(cur.c[j]);   // gradient with respect to the logarithm
+                    }
+                    cc[j] = cp;
+                    ys[j] = yy;
+                }
+            }
+            // identity outside the row; nothing precedes the row's first element in scan order and
+            // nothing follows its last
+            float xx[E];
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const long long e = v0 + j - off;
+                const bool inside = e >= 0 && e < L;
+                const bool first = ASC ? e == 0 : e == L - 1, last = ASC ? e == L - 1 : e == 0;
+                xx[j] = inside ? cur.x[j] : 0.0f;   // (a chunk that straddles the row's end holds a neighbour's elements)
+                if (!inside) cc[j] = 1.0f;
+                if (first) cc[j] = 0.0f;
+                if (BWD && (!inside || last)) ys[j] = 0.0f;
+            }
+            Pair inc = pair_identity();
+#pragma unroll
+            for (int jj = 0; jj < E; ++jj) {
+                const int j = ASC ? jj : E - 1 - jj;
+                inc.y = fmaf(inc.y, cc[j], xx[j]);
+                inc.p *= cc[j];
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                Pair far;
+                far.y = __shfl_up_sync(0xffffffffu, inc.y, d);
+                far.p = __shfl_up_sync(0xffffffffu, inc.p, d);
+                if (lane >= d) inc = combine(far, inc);
+            }
+            Pair ex;
+            ex.y = __shfl_up_sync(0xffffffffu, inc.y, 1);
+            ex.p = __shfl_up_sync(0xffffffffu, inc.p, 1);
+            if (lane == 0) ex = pair_identity();
+            if (lane == 31) wagg[par][w] = inc;
+            __syncthreads();
+            Pair pre = pair_identity(), total = pair_identity();
+#pragma unroll
+            for (int ww = 0; ww < NW; ++ww) {
+                const Pair g = wagg[par][ww];
+                if (ww < w) pre = combine(pre, g);
+                total = combine(total, g);
+            }
+            pre = combine(pre, ex);
+            float v = fmaf(carry, pre.p, pre.y);   // the true value that enters this thread's elements
+            float r0[E], r1[BWD ? E : 1];
+#pragma unroll
+            for (int jj = 0; jj < E; ++jj) {
+                const int j = ASC ? jj : E - 1 - jj;
+                v = fmaf(v, cc[j], xx[j]);
+                r0[j] = v;
+                if constexpr (BWD) r1[j] = v * ys[j];
+            }
+            store_run(out0, v0, r0);
+            if constexpr (BWD) store_run(out1, v0, r1);
+            carry = fmaf(carry, total.p, total.y);
             cur = nxt;
         }
     }

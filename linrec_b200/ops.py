@@ -117,8 +117,20 @@ def _empty_like_rows(t: torch.Tensor) -> torch.Tensor:
     and a kernel that is handed one row stride for all its tensors would then write outside it.  Rows
     at one uniform stride keep their strides here; anything else gets a contiguous result."""
     if t.numel() and _row_layout(t) is not None:
-        return torch.empty_strided(t.size(), t.stride(), dtype=t.dtype, device=t.device)
+        return _empty_strided_like(t, t.size(), t.stride())
     return torch.empty(t.size(), dtype=t.dtype, device=t.device)
+
+
+def _empty_strided_like(ref: torch.Tensor, size, stride) -> torch.Tensor:
+    """`torch.empty_strided`, but starting as far from a 16-byte boundary as `ref` does: the kernel that
+    takes rows of any alignment walks all tensors of a call in the same 16-byte chunks, and a view that
+    starts inside a wider tensor would otherwise get a result that starts on a boundary."""
+    skew = ref.data_ptr() & 15
+    if skew == 0 or skew % ref.element_size():
+        return torch.empty_strided(size, stride, dtype=ref.dtype, device=ref.device)
+    skew //= ref.element_size()
+    n = 1 + sum((sz - 1) * st for sz, st in zip(size, stride))
+    return torch.empty(n + skew, dtype=ref.dtype, device=ref.device).as_strided(size, stride, skew)
 
 
 # Signature (shape, strides, dtype, device) of tensors that passed every check before -> their row
@@ -137,7 +149,7 @@ def _launch(kind: int, bwd: bool, ins, reverse: bool, kwargs: dict, outs=None):
     if layout is not None and all((t.shape, t.stride(), t.dtype, t.device) == sig for t in ins[1:]) and (
             outs is None or (len(outs) == n_out and all((t.shape, t.stride(), t.dtype, t.device) == sig for t in outs))):
         if outs is None:
-            outs = [torch.empty_strided(sig[0], sig[1], dtype=sig[2], device=sig[3]) for _ in range(n_out)]
+            outs = [_empty_strided_like(ref, sig[0], sig[1]) for _ in range(n_out)]
         work_ins, work_outs = ins, outs
     else:
         _check_same(*ins)

@@ -819,6 +819,80 @@ def test_call_from_a_fresh_host_thread():
     assert out["ok"]
 
 
+# ---- rows of any alignment: one CTA per row ------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("rev", [False, True])
+@pytest.mark.parametrize("shape,skew", [((700, 1001), 0), ((600, 10001), 0), ((1000, 77), 0), ((650, 2049), 0),
+                                        ((640, 4099), 1), ((5, 1001), 0), ((3, 20003), 3), ((2, 7), 1)],
+                         ids=lambda v: str(v).replace(" ", ""))
+def test_row_kernel_any_alignment(shape, skew, rev, dtype):
+    """`memcode` 4: one CTA walks one row with aligned 16-byte accesses, whatever the row's length and
+    wherever it starts (here also rows that start `skew` elements into a wider tensor, so that for
+    2-byte storage not even 4-byte alignment holds).  Forward and backward against the oracle, the
+    columns around the rows untouched, one launch; with several rows per SM it is chosen by itself."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    rows, L = shape
+    x, c, dy = _data(shape, clo=0.5, seed=SEED + L)
+    tt = torch.float32 if dtype == "f32" else torch.bfloat16
+    rtol = RTOL if dtype == "f32" else 2.0 ** -7
+    FILL = 123.0
+
+    def embed(t):
+        """The rows inside a wider tensor of guard columns."""
+        full = torch.full((rows, L + skew + 5), FILL, dtype=tt, device=dev)
+        full[:, skew:skew + L] = t.to(tt).to(dev)
+        return full, full[:, skew:skew + L]
+
+    (xf, xv), (cf, cv), (dyf, dyv) = embed(x), embed(c), embed(dy)
+    xr, cr, dyr = (t.float().cpu().numpy() for t in (xv, cv, dyv))
+    opts = {} if rows >= 600 else {"memcode": 4}
+    before = lb._C.launch_count()
+    y = lb._C.linrec_pipe_fwd(inputs=xv, coeffs=cv, reverse=rev, **opts)
+    assert lb._C.launch_count() - before == 1
+    y_ref = oracle.fwd_f32(xr, cr, reverse=rev)
+    np.testing.assert_allclose(y.float().cpu().numpy(), y_ref, rtol=rtol, atol=ATOL)
+    assert y.stride() == xv.stride()     # results keep the layout of the inputs
+    yfull, yv = embed(torch.from_numpy(y_ref))
+    dx, dc = lb._C.linrec_pipe_bwd(d_outputs=dyv, coeffs=cv, outputs=yv, reverse=rev, **opts)
+    dx_ref, dc_ref = oracle.bwd_f32(dyr, cr, yv.float().cpu().numpy(), reverse=rev)
+    np.testing.assert_allclose(dx.float().cpu().numpy(), dx_ref, rtol=rtol, atol=ATOL)
+    np.testing.assert_allclose(dc.float().cpu().numpy(), dc_ref, rtol=rtol, atol=2 * ATOL * max(1.0, float(np.abs(y_ref).max())))
+    for full in (xf, cf, dyf, yfull):
+        guard = torch.cat([full[:, :skew], full[:, skew + L:]], dim=1)
+        assert bool((guard == FILL).all()), "guard columns changed"
+    if rows >= 600:
+        # the loaders these rows used to take still give the same answer when pinned
+        y0 = lb._C.linrec_pipe_fwd(inputs=xv, coeffs=cv, reverse=rev, memcode=0)
+        np.testing.assert_allclose(y0.float().cpu().numpy(), y_ref, rtol=rtol, atol=ATOL)
+    lb.check_status()
+
+
+def test_row_kernel_first_coefficient_and_nonfinite_values():
+    """The coefficient of a row's first element in scan order is never used (linrec_ref.cuh:63), also
+    when it is inf or nan; a non-finite input travels along its own row and does not leak into the
+    neighbouring rows that share its 16-byte chunks."""
+    lb = _ops()
+    dev = torch.device("cuda:0")
+    rows, L = 700, 1001
+    x, c, _ = _data((rows, L), clo=0.5)
+    for rev in (False, True):
+        cc = c.clone()
+        cc[:, -1 if rev else 0] = float("inf")
+        cc[3, -1 if rev else 0] = float("nan")
+        xx = x.clone()
+        xx[10, L - 1] = float("inf")      # last element of row 10: shares a chunk with row 11's first
+        y = lb._C.linrec_pipe_fwd(inputs=xx.to(dev), coeffs=cc.to(dev), reverse=rev).cpu().numpy()
+        c0 = cc.clone()
+        c0[:, -1 if rev else 0] = 0.0
+        y_ref = oracle.fwd_f32(xx.numpy(), c0.numpy(), reverse=rev)
+        ok = np.isfinite(y_ref)
+        np.testing.assert_array_equal(np.isfinite(y), ok)
+        assert ok[9].all() and ok[11].all()
+        np.testing.assert_allclose(y[ok], y_ref[ok], rtol=RTOL, atol=ATOL)
+    lb.check_status()
+
+
 # ---- double precision: the sequential family ----------------------------------------------------------
 @pytest.mark.parametrize("shape", [(1, 1), (5, 17), (64, 512), (3, 20000)], ids=lambda s: f"{s[0]}x{s[1]}")
 @pytest.mark.parametrize("rev", [False, True])
