@@ -69,6 +69,11 @@ extern "C" {
  * names are listed by linrec_b200_config_names(); an unknown name or a value without a compiled
  * variant gives LINREC_ERR_NOT_IMPLEMENTED (the reference raises NotImplementedError from
  * dispatch.h:70-71).  n_opts may be 0, in which case the regime selector chooses.
+ * `memcode` names the way rows are brought in: 0 plain loads, 1 bulk-tensor copies (rows of whole
+ * 128-byte lines), 2 / 3 16-byte / 4-byte asynchronous copies, 4 one CTA per row with aligned 16-byte
+ * accesses (any row length and start; all tensors of the call must start equally far from a 16-byte
+ * boundary, else LINREC_ERR_UNALIGNED; it has no variants, so it cannot be combined with the other
+ * selectors).
  *
  * Besides the variant selectors there is one option that changes what is computed:
  *   logCoeffs = 1   the coefficient tensor holds logarithms (the `logc` argument of the reference's
