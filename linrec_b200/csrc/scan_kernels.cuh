@@ -1095,6 +1095,8 @@ __global__ void __launch_bounds__(256, BWD ? 2 : 4) linrec_row_f64_kernel(const 
 template <typename ST, int NT, bool BWD, bool ASC>
 __global__ void __launch_bounds__(NT) linrec_row_kernel(const ScanParams p)
 {
+    // a thread's run: 8 elements (two 16-byte chunks of fp32, one of 2-byte storage; 16 elements of 2-byte
+    // storage per thread were measured and lost a quarter)
     constexpr int E = 8, PC = Storage<ST>::kPerChunk, NCH = E / PC, NW = NT / 32, T = NT * E;
     __shared__ Pair wagg[2][NW];
     const int tid = (int)threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -1102,7 +1104,7 @@ __global__ void __launch_bounds__(NT) linrec_row_kernel(const ScanParams p)
     const bool logc = p.logc != 0;
     int par = 0;   // runs on across rows, so that consecutive tiles never share a set of totals
 
-    // What a thread requests for one tile, in MEMORY order: its eight elements of every operand and
+    // What a thread requests for one tile, in MEMORY order: its E elements of every operand and
     // (backward, a warp's edge lanes only) the coefficient just before and the output just after its
     // run in scan order.
     struct Ops {
@@ -1211,14 +1213,18 @@ __global__ void __launch_bounds__(NT) linrec_row_kernel(const ScanParams p)
             // nothing follows its last
             float xx[E];
 #pragma unroll
-            for (int j = 0; j < E; ++j) {
-                const long long e = v0 + j - off;
-                const bool inside = e >= 0 && e < L;
-                const bool first = ASC ? e == 0 : e == L - 1, last = ASC ? e == L - 1 : e == 0;
-                xx[j] = inside ? cur.x[j] : 0.0f;   // (a chunk that straddles the row's end holds a neighbour's elements)
-                if (!inside) cc[j] = 1.0f;
-                if (first) cc[j] = 0.0f;
-                if (BWD && (!inside || last)) ys[j] = 0.0f;
+            for (int j = 0; j < E; ++j) xx[j] = cur.x[j];
+            if (v0 - off <= 0 || v0 + E - off >= L) {   // only the runs at the ends of a row need any of this
+#pragma unroll
+                for (int j = 0; j < E; ++j) {
+                    const long long e = v0 + j - off;
+                    const bool inside = e >= 0 && e < L;
+                    const bool first = ASC ? e == 0 : e == L - 1, last = ASC ? e == L - 1 : e == 0;
+                    if (!inside) xx[j] = 0.0f;   // (a chunk that straddles the row's end holds a neighbour's elements)
+                    if (!inside) cc[j] = 1.0f;
+                    if (first) cc[j] = 0.0f;
+                    if (BWD && (!inside || last)) ys[j] = 0.0f;
+                }
             }
             Pair inc = pair_identity();
 #pragma unroll
