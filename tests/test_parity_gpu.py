@@ -820,7 +820,7 @@ def test_call_from_a_fresh_host_thread():
 
 
 # ---- rows of any alignment: one CTA per row ------------------------------------------------------------
-@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("rev", [False, True])
 @pytest.mark.parametrize("shape,skew", [((700, 1001), 0), ((600, 10001), 0), ((1000, 77), 0), ((650, 2049), 0),
                                         ((640, 4099), 1), ((5, 1001), 0), ((3, 20003), 3), ((2, 7), 1)],
@@ -834,8 +834,8 @@ def test_row_kernel_any_alignment(shape, skew, rev, dtype):
     dev = torch.device("cuda:0")
     rows, L = shape
     x, c, dy = _data(shape, clo=0.5, seed=SEED + L)
-    tt = torch.float32 if dtype == "f32" else torch.bfloat16
-    rtol = RTOL if dtype == "f32" else 2.0 ** -7
+    tt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    rtol = {"f32": RTOL, "bf16": 2.0 ** -7, "f16": 2.0 ** -9}[dtype]
     FILL = 123.0
 
     def embed(t):
