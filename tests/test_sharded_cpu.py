@@ -170,3 +170,25 @@ def test_results_follow_the_row_layout_of_padded_inputs(monkeypatch):
     # inputs with different (individually valid) strides end up with one layout
     (a, b), lay = sharded.CudaShardKernels._prep(x, torch.zeros(5, 256))
     assert lay == (5, 256, 256) and a.stride() == b.stride()
+
+
+def test_results_start_as_far_from_a_16_byte_boundary_as_their_inputs():
+    """The kernel for rows of any alignment walks all tensors of a call in the same 16-byte chunks, so
+    a result allocated for inputs that are views into a wider tensor has to start at the same offset
+    from a 16-byte boundary (inside its own storage); aligned inputs get a plain allocation."""
+    from linrec_b200 import ops
+    for dtype, skew in ((torch.float32, 3), (torch.float32, 1), (torch.bfloat16, 5), (torch.bfloat16, 1), (torch.float64, 1)):
+        wide = torch.zeros(6, 1000 + skew + 2, dtype=dtype)
+        view = wide[:, skew:skew + 1000]
+        if view.data_ptr() % 16 == 0:
+            continue            # the allocation itself happened to start off a boundary by the same amount
+        out = ops._empty_like_rows(view)
+        assert out.shape == view.shape and out.stride() == view.stride() and out.dtype == dtype
+        assert out.data_ptr() % 16 == view.data_ptr() % 16
+        assert 0 < out.storage_offset() < 16
+        out.fill_(1)            # every element is inside the allocation
+        assert float(out.double().sum()) == 6 * 1000
+    aligned = torch.zeros(6, 1000)
+    out = ops._empty_like_rows(aligned)
+    assert out.storage_offset() == 0 and out.stride() == aligned.stride()
+
